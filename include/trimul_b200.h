@@ -1,0 +1,196 @@
+/*
+ * trimul_b200 — C ABI of the B200 (sm_100a) TriangleMultiplication block.
+ *
+ * One block call computes, for a pair tensor z[B,N,N,c]:
+ *
+ *   x_n   = LayerNorm_in(z)                                   (over c, fp32 statistics)
+ *   a     = sigmoid(x_n Wlg^T) * (x_n Wl^T) * pairmask        (left operand)
+ *   b     = sigmoid(x_n Wrg^T) * (x_n Wr^T) * pairmask        (right operand)
+ *   tri   = outgoing: sum_k a[i,k,:] * b[j,k,:]    incoming: sum_k a[k,i,:] * b[k,j,:]
+ *   out   = sigmoid(x_n Wg^T) * (LayerNorm_out(tri) Wo^T)     (+ residual when asked)
+ *
+ * which is the arithmetic of the reference's ground truth,
+ * src/miniworld_engine/modules/triangle_multiplication/reference.py:62-83 (module form) and
+ * :86-122 (functional form, pair mask).  All Linear weights are [out,in] row-major
+ * (nn.Linear), bias-free; LayerNorm parameters are fp32 whatever the activation type
+ * (src/miniworld_engine/modules/primitives.py:70-88).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer owned by the caller; nothing here allocates,
+ *     frees, synchronises or throws;  work is enqueued on `stream` (a cudaStream_t);
+ *   - return value: 0 on success, a negative TRIMUL_E_* code otherwise (see
+ *     trimul_b200_strerror);  errors are detected before anything is enqueued;
+ *   - `status` (optional, may be NULL) points to 4 caller-owned int32 words on the device,
+ *     zeroed by the caller.  A kernel whose bounded wait expires writes
+ *     {TRIMUL_E_DEVICE_TIMEOUT, stage id, block index, detail} there and returns
+ *     early instead of hanging; the caller reads it after synchronising the stream;
+ *   - entry points are re-entrant across streams as long as workspaces are distinct.
+ *
+ * The functions replace, behind the reference's own module / functional interface, the
+ * launch sequence of its sm_100 fast path
+ * (src/miniworld_engine/modules/triangle_multiplication/module.py:399-459).
+ */
+#ifndef TRIMUL_B200_H_
+#define TRIMUL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define TRIMUL_B200_ABI_VERSION 1
+
+/* error codes */
+#define TRIMUL_OK                 0
+#define TRIMUL_E_INVALID         -1   /* NULL pointer, bad size, bad enum, misaligned buffer        */
+#define TRIMUL_E_UNSUPPORTED     -2   /* valid request that this build has no kernel for            */
+#define TRIMUL_E_WORKSPACE       -3   /* workspace smaller than trimul_b200_workspace_bytes says    */
+#define TRIMUL_E_CUDA            -4   /* a CUDA runtime/driver call failed (launch, tensor map)     */
+#define TRIMUL_E_DEVICE_TIMEOUT  -5   /* only ever written to the device status words               */
+
+/* dtype of activations and Linear weights */
+#define TRIMUL_DTYPE_BF16 0           /* bf16 storage, fp32 accumulate, tensor-core kernels         */
+#define TRIMUL_DTYPE_FP32 1           /* fp32 storage and arithmetic (no TF32), CUDA-core kernels   */
+
+/* direction: reference.py:77-80 */
+#define TRIMUL_OUTGOING 0
+#define TRIMUL_INCOMING 1
+
+/* mask kind */
+#define TRIMUL_MASK_NONE  0
+#define TRIMUL_MASK_TOKEN 1           /* uint8 [B,N];   pair mask = m[i] & m[k]  (reference.py:72-75)  */
+#define TRIMUL_MASK_PAIR  2           /* uint8 [B,N,N]; functional form          (reference.py:108-111) */
+
+/* flags */
+#define TRIMUL_FLAG_PLAIN_KERNELS 1u  /* run the CUDA-core kernels even where tensor-core ones exist
+                                         (cross-checking aid; same layouts, same rounding points)   */
+
+/*
+ * Problem description.  `rows`/`row0` select a horizontal slab of z for the row-sharded
+ * multi-GPU form: this call sees z rows [row0, row0+rows) of the N x N grid, as a dense
+ * [B, rows, N, c] tensor, and produces the matching [B, rows, N, c] slab of the output.
+ * The whole-block entry point requires rows == N and row0 == 0.
+ */
+typedef struct trimul_desc {
+    uint32_t struct_bytes;   /* sizeof(trimul_desc), for ABI evolution                              */
+    int32_t  B;              /* batch                                                               */
+    int32_t  N;              /* tokens: z is N x N positions per batch                              */
+    int32_t  c;              /* d_pair = channels of z and of the output                            */
+    int32_t  c_hidden;       /* width of a/b/tri; must equal c (reference.py:51-59 builds the four
+                                input projections c-wide regardless, so only c_hidden == c is
+                                self-consistent there)                                              */
+    int32_t  dtype;          /* TRIMUL_DTYPE_*                                                      */
+    int32_t  direction;      /* TRIMUL_OUTGOING / TRIMUL_INCOMING                                   */
+    int32_t  mask_kind;      /* TRIMUL_MASK_*                                                       */
+    float    eps_in;         /* LayerNorm_in epsilon  (1e-5 in the reference)                       */
+    float    eps_out;        /* LayerNorm_out epsilon                                               */
+    uint32_t flags;          /* TRIMUL_FLAG_*                                                       */
+    int32_t  rows;           /* z rows in this call (N for the unsharded block)                     */
+    int32_t  row0;           /* global index of the first of them                                   */
+} trimul_desc;
+
+/* Parameters, named as in reference.py:51-59.  Linear weights have the activation dtype;
+ * the four ln_* vectors are always fp32. */
+typedef struct trimul_weights {
+    const float* ln_in_weight;    /* ln_pair.weight  [c] */
+    const float* ln_in_bias;      /* ln_pair.bias    [c] */
+    const void*  w_left;          /* to_left.weight        [c,c] */
+    const void*  w_left_gate;     /* to_left_gate.weight   [c,c] */
+    const void*  w_right;         /* to_right.weight       [c,c] */
+    const void*  w_right_gate;    /* to_right_gate.weight  [c,c] */
+    const float* ln_out_weight;   /* ln_out.weight   [c] */
+    const float* ln_out_bias;     /* ln_out.bias     [c] */
+    const void*  w_gate;          /* to_gate.weight        [c,c] */
+    const void*  w_out;           /* to_out.weight         [c,c] */
+} trimul_weights;
+
+/*
+ * Channel-major operand planes: the layout of a, b and tri between the stages.
+ * Logical shape [planes = B*c][rows][cols]; element (p, r, q) lives at
+ *     base + (r / row_chunk) * chunk_stride + p * plane_stride + (r % row_chunk) * pitch + q       (row-chunked)
+ *     base + (q / col_chunk) * chunk_stride + p * plane_stride + r * pitch + (q % col_chunk)       (col-chunked)
+ * in elements.  row_chunk == rows and col_chunk == cols (chunk_stride ignored) is the plain
+ * single-GPU layout; at most one of the two may be chunked.  Chunked forms are what an
+ * all-gather / all-to-all of per-rank slabs leaves in memory, so the contraction can read the
+ * gathered operand in place.  pitch, plane_stride and chunk_stride must be multiples of 8
+ * elements and `base` 16-byte aligned (128 for the tensor-core kernels).
+ */
+typedef struct trimul_planes {
+    void*   base;
+    int64_t rows;
+    int64_t cols;
+    int64_t pitch;
+    int64_t plane_stride;
+    int64_t chunk_stride;
+    int64_t row_chunk;
+    int64_t col_chunk;
+} trimul_planes;
+
+/* ABI version of the loaded library (TRIMUL_B200_ABI_VERSION it was built with). */
+int trimul_b200_abi_version(void);
+
+/* Human-readable text for a TRIMUL_E_* code.  Never NULL. */
+const char* trimul_b200_strerror(int code);
+
+/*
+ * Bytes of device workspace trimul_b200_forward needs for `desc` (the a, b and tri planes),
+ * and — when the out-pointers are non-NULL — the three plane descriptors the block uses
+ * inside a workspace that starts at address 0 (add the real base to each `base`).
+ * Replaces the per-call torch.empty intermediates of the reference fast path
+ * (module.py:431-452).
+ */
+int trimul_b200_workspace_bytes(const trimul_desc* desc, size_t* bytes,
+                                trimul_planes* a, trimul_planes* b, trimul_planes* tri);
+
+/*
+ * The whole block.  z, out (and residual when non-NULL): [B,N,N,c] dense, activation dtype,
+ * 16-byte aligned; out must not alias z.  mask: per desc->mask_kind, or NULL.  residual
+ * non-NULL adds it to the result (the reference module's `out + pair`, module.py:453);
+ * NULL gives reference.py's output.  Drop-in for TriangleMultiplication._forward_cute_free
+ * (module.py:399-459) and for triangle_multiplicative_update_cute
+ * (src/miniworld_engine/modules/triangle_multiplication/interface.py:8-22).
+ */
+int trimul_b200_forward(const trimul_desc* desc, const void* z, const uint8_t* mask,
+                        const trimul_weights* w, void* out, const void* residual,
+                        void* workspace, size_t workspace_bytes,
+                        void* stream, int32_t* status);
+
+/*
+ * Stage 1: LayerNorm_in + mask + the two sigmoid-gated projections.  Reads the z slab
+ * [B, rows, N, c]; writes a and b as channel-major planes.  Outgoing: plane element
+ * (r, k) is position (row0+r, k), planes are [B*c][rows][N].  Incoming: the planes are
+ * stored transposed, element (i, k) is position (row0+k, i), planes are [B*c][N][rows],
+ * so that the contraction is "rows times rows over a contiguous k" in both directions.
+ * Replaces fused_ln_mask + tm1_cute_forward(out_layout="bdll_sm100")
+ * (module.py:422-438; kernels/tm1/cute/sm100_gate_gemm_collective.py:586-647).
+ */
+int trimul_b200_tm1(const trimul_desc* desc, const void* z, const uint8_t* mask,
+                    const trimul_weights* w, const trimul_planes* a, const trimul_planes* b,
+                    void* stream, int32_t* status);
+
+/*
+ * Stage 2: tri[p][i][j] = sum_k a[p][i][k] * b[p][j][k] for every plane p, fp32
+ * accumulation.  a: [planes][rows_a][K], b: [planes][rows_b][K], tri: [planes][rows_a][rows_b].
+ * `dtype` is TRIMUL_DTYPE_*.  Replaces the einsum / cuBLAS bmm of module.py:439-442.
+ */
+int trimul_b200_contract(int32_t dtype, uint32_t flags, int32_t planes,
+                         const trimul_planes* a, const trimul_planes* b, const trimul_planes* tri,
+                         void* stream, int32_t* status);
+
+/*
+ * Stage 3: LayerNorm_out over the channels of tri, the output projection, the output gate
+ * computed from a fresh LayerNorm_in of the z slab (unmasked, reference.py:83), optional
+ * residual; writes out [B, rows, N, c].  tri planes are [B*c][rows][N] for both directions.
+ * Replaces trimul_back_split_sm100 + the residual add (module.py:445-453;
+ * kernels/trimul_inproj/cute/back_split_sm100.py:26-34).
+ */
+int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes* tri,
+                    const trimul_weights* w, void* out, const void* residual,
+                    void* stream, int32_t* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TRIMUL_B200_H_ */

@@ -1,0 +1,456 @@
+// C-ABI of the B200 TriangleMultiplication block: argument validation, tensor-map
+// construction, workspace layout and kernel launches.  Declarations and the reference
+// interfaces each entry point replaces are in include/trimul_b200.h.
+//
+// Nothing here allocates device memory, synchronises or throws.  Tensor maps are built on the
+// host per call (a pure CPU encode) and passed by value as kernel parameters, so the entry
+// points can be captured in CUDA graphs.
+
+#include "../../include/trimul_b200.h"
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "contract_sm100.cuh"
+#include "plain_kernels.cuh"
+#include "tm1_sm100.cuh"
+#include "tm2_sm100.cuh"
+
+using namespace trimul;
+
+namespace {
+
+// ---------------------------------------------------------------------------------------
+// driver entry point for tensor-map encoding (resolved at run time: no link against libcuda)
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+    });
+    return fn;
+}
+
+// bf16 tensor of up to 4 dimensions, innermost first; strides in ELEMENTS for dims 1..3.
+bool encode_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_elems,
+                 const uint32_t* box, bool swizzle128) {
+    EncodeTiledFn fn = get_encode_fn();
+    if (fn == nullptr) return false;
+    cuuint64_t gdim[4];
+    cuuint64_t gstride[3];
+    cuuint32_t bdim[4];
+    cuuint32_t estr[4];
+    for (int i = 0; i < rank; ++i) {
+        gdim[i] = dims[i];
+        bdim[i] = box[i];
+        estr[i] = 1;
+    }
+    for (int i = 0; i + 1 < rank; ++i) gstride[i] = strides_elems[i] * 2;
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride,
+                    bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS;
+}
+
+// Channel-major planes as a 4-D tensor (col, row-in-chunk, plane, chunk) with the given box.
+bool encode_planes(CUtensorMap* map, const trimul_planes& pl, int planes, uint32_t box_cols, uint32_t box_rows,
+                   uint32_t box_planes) {
+    const bool row_chunked = pl.row_chunk < pl.rows;
+    const bool col_chunked = pl.col_chunk < pl.cols;
+    const uint64_t chunks = row_chunked ? (uint64_t)((pl.rows + pl.row_chunk - 1) / pl.row_chunk)
+                          : col_chunked ? (uint64_t)((pl.cols + pl.col_chunk - 1) / pl.col_chunk)
+                                        : 1;
+    const uint64_t dims[4] = {(uint64_t)(col_chunked ? pl.col_chunk : pl.cols),
+                              (uint64_t)(row_chunked ? pl.row_chunk : pl.rows), (uint64_t)planes, chunks};
+    const uint64_t chunk_stride = chunks > 1 ? (uint64_t)pl.chunk_stride : (uint64_t)pl.plane_stride * planes;
+    const uint64_t strides[3] = {(uint64_t)pl.pitch, (uint64_t)pl.plane_stride, chunk_stride};
+    const uint32_t box[4] = {box_cols, box_rows, box_planes, 1};
+    return encode_bf16(map, pl.base, 4, dims, strides, box, true);
+}
+
+int sm_count() {
+    static int n = 0;
+    if (n == 0) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess) return 148;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    }
+    return n;
+}
+
+template <typename K>
+bool ensure_smem(K kernel, int bytes) {
+    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+}
+
+inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
+
+// ---------------------------------------------------------------------------------------
+// validation
+// ---------------------------------------------------------------------------------------
+int check_desc(const trimul_desc* d) {
+    if (d == nullptr || d->struct_bytes != sizeof(trimul_desc)) return TRIMUL_E_INVALID;
+    if (d->B <= 0 || d->N <= 0 || d->c <= 0 || d->rows <= 0 || d->row0 < 0) return TRIMUL_E_INVALID;
+    if (d->row0 + d->rows > d->N) return TRIMUL_E_INVALID;
+    if (d->dtype != TRIMUL_DTYPE_BF16 && d->dtype != TRIMUL_DTYPE_FP32) return TRIMUL_E_INVALID;
+    if (d->direction != TRIMUL_OUTGOING && d->direction != TRIMUL_INCOMING) return TRIMUL_E_INVALID;
+    if (d->mask_kind < TRIMUL_MASK_NONE || d->mask_kind > TRIMUL_MASK_PAIR) return TRIMUL_E_INVALID;
+    if (!(d->eps_in > 0.f) || !(d->eps_out > 0.f)) return TRIMUL_E_INVALID;
+    if (d->c_hidden != d->c) return TRIMUL_E_UNSUPPORTED;
+    if (d->c > kPlainMaxC || (d->c % 8) != 0) return TRIMUL_E_UNSUPPORTED;
+    if ((int64_t)d->B * d->c > 65535) return TRIMUL_E_UNSUPPORTED;
+    if (d->N > 16384) return TRIMUL_E_UNSUPPORTED;
+    return TRIMUL_OK;
+}
+
+int check_weights(const trimul_weights* w) {
+    if (w == nullptr) return TRIMUL_E_INVALID;
+    if (!w->ln_in_weight || !w->ln_in_bias || !w->w_left || !w->w_left_gate || !w->w_right || !w->w_right_gate ||
+        !w->ln_out_weight || !w->ln_out_bias || !w->w_gate || !w->w_out)
+        return TRIMUL_E_INVALID;
+    const void* ws[6] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate, w->w_gate, w->w_out};
+    for (const void* p : ws)
+        if ((reinterpret_cast<uintptr_t>(p) & 15u) != 0) return TRIMUL_E_INVALID;
+    return TRIMUL_OK;
+}
+
+int check_planes(const trimul_planes* pl, int64_t rows, int64_t cols) {
+    if (pl == nullptr || pl->base == nullptr) return TRIMUL_E_INVALID;
+    if (pl->rows != rows || pl->cols != cols) return TRIMUL_E_INVALID;
+    if (pl->pitch < 0 || pl->plane_stride <= 0 || pl->row_chunk <= 0 || pl->col_chunk <= 0) return TRIMUL_E_INVALID;
+    if ((pl->pitch % 8) || (pl->plane_stride % 8) || (pl->chunk_stride % 8)) return TRIMUL_E_INVALID;
+    if ((reinterpret_cast<uintptr_t>(pl->base) & 15u) != 0) return TRIMUL_E_INVALID;
+    const bool rc = pl->row_chunk < rows, cc = pl->col_chunk < cols;
+    if (rc && cc) return TRIMUL_E_INVALID;
+    if (pl->pitch < (cc ? pl->col_chunk : cols)) return TRIMUL_E_INVALID;
+    if ((rc || cc) && pl->chunk_stride <= 0) return TRIMUL_E_INVALID;
+    return TRIMUL_OK;
+}
+
+PlaneView view_of(const trimul_planes& pl) {
+    PlaneView v;
+    v.base = pl.base;
+    v.rows = pl.rows;
+    v.cols = pl.cols;
+    v.pitch = pl.pitch;
+    v.plane_stride = pl.plane_stride;
+    v.chunk_stride = pl.chunk_stride;
+    v.row_chunk = pl.row_chunk < pl.rows ? pl.row_chunk : (pl.rows > 0 ? pl.rows : 1);
+    v.col_chunk = pl.col_chunk < pl.cols ? pl.col_chunk : (pl.cols > 0 ? pl.cols : 1);
+    return v;
+}
+
+// chunk sizes as the tensor-core kernels use them: the full extent when not chunked
+inline int eff_chunk(int64_t chunk, int64_t extent) { return (int)(chunk < extent ? chunk : extent); }
+
+bool tensor_core_path(const trimul_desc* d) {
+    return d->dtype == TRIMUL_DTYPE_BF16 && d->c == 128 && (d->flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0;
+}
+
+int launch_status() { return cudaGetLastError() == cudaSuccess ? TRIMUL_OK : TRIMUL_E_CUDA; }
+
+// ---------------------------------------------------------------------------------------
+// stage 1
+// ---------------------------------------------------------------------------------------
+template <typename T>
+int run_plain_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
+                  const trimul_planes* a, const trimul_planes* b, cudaStream_t st) {
+    PlainTm1Params p;
+    p.B = d->B; p.rows = d->rows; p.N = d->N; p.c = d->c; p.row0 = d->row0;
+    p.incoming = d->direction == TRIMUL_INCOMING;
+    p.mask_kind = mask ? d->mask_kind : 0;
+    p.mask = mask;
+    p.gamma = w->ln_in_weight; p.beta = w->ln_in_bias; p.eps = d->eps_in;
+    p.w_left = w->w_left; p.w_left_gate = w->w_left_gate; p.w_right = w->w_right; p.w_right_gate = w->w_right_gate;
+    p.a = view_of(*a); p.b = view_of(*b);
+    const int64_t grid = (int64_t)d->B * d->rows * ((d->N + kPlainPos - 1) / kPlainPos);
+    plain_tm1_kernel<T><<<(unsigned)grid, kPlainThreads, 0, st>>>(static_cast<const T*>(z), p);
+    return launch_status();
+}
+
+int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
+                 const trimul_planes* a, const trimul_planes* b, cudaStream_t st, int32_t* status) {
+    const bool inc = d->direction == TRIMUL_INCOMING;
+    CUtensorMap tmZ, tmW[4], tmA, tmB;
+    {
+        const uint64_t dims[4] = {128, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
+        const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
+        const uint32_t box_out[4] = {64, 128, 1, 1};
+        const uint32_t box_in[4] = {64, 1, 128, 1};
+        if (!encode_bf16(&tmZ, z, 4, dims, strides, inc ? box_in : box_out, true)) return TRIMUL_E_CUDA;
+    }
+    const void* ws[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
+    for (int m = 0; m < 4; ++m) {
+        const uint64_t dims[2] = {128, 128};
+        const uint64_t strides[1] = {128};
+        const uint32_t box[2] = {64, 128};
+        if (!encode_bf16(&tmW[m], ws[m], 2, dims, strides, box, true)) return TRIMUL_E_CUDA;
+    }
+    const int planes = d->B * 128;
+    if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+
+    Tm1Params p;
+    p.B = d->B; p.c = 128;
+    p.n_fixed = inc ? d->N : d->rows;
+    p.n_run = inc ? d->rows : d->N;
+    p.tiles_per_fixed = (p.n_run + kT1P - 1) / kT1P;
+    const int64_t total = (int64_t)d->B * p.n_fixed * p.tiles_per_fixed;
+    if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
+    p.total_tiles = (int)total;
+    p.incoming = inc;
+    p.N = d->N; p.row0 = d->row0;
+    p.mask_kind = mask ? d->mask_kind : 0;
+    p.mask = mask;
+    p.gamma = w->ln_in_weight; p.beta = w->ln_in_bias; p.eps = d->eps_in;
+    p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_col_chunk = eff_chunk(a->col_chunk, a->cols);
+    p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
+    p.status = status;
+    if (!ensure_smem(tm1_sm100_kernel, kT1SmemBytes)) return TRIMUL_E_CUDA;
+    const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+    tm1_sm100_kernel<<<grid, kT1Threads, kT1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// stage 2
+// ---------------------------------------------------------------------------------------
+template <typename T>
+int run_plain_contract(int planes, const trimul_planes* a, const trimul_planes* b, const trimul_planes* t,
+                       cudaStream_t st) {
+    dim3 grid((unsigned)((b->rows + 31) / 32), (unsigned)((a->rows + 31) / 32), (unsigned)planes);
+    plain_contract_kernel<T><<<grid, 256, 0, st>>>(view_of(*a), view_of(*b), view_of(*t));
+    return launch_status();
+}
+
+bool fast_contract_ok(const trimul_planes* a, const trimul_planes* b, const trimul_planes* t) {
+    // a chunk boundary must not cut through a tile or a K slice
+    if (a->row_chunk < a->rows && (a->row_chunk % kCtBM)) return false;
+    if (b->row_chunk < b->rows && (b->row_chunk % kCtBN)) return false;
+    if (a->col_chunk < a->cols && (a->col_chunk % kCtBK)) return false;
+    if (b->col_chunk < b->cols && (b->col_chunk % kCtBK)) return false;
+    if (t->row_chunk < t->rows && (t->row_chunk % kCtBM)) return false;
+    if (t->col_chunk < t->cols && (t->col_chunk % 64)) return false;
+    if ((reinterpret_cast<uintptr_t>(a->base) | reinterpret_cast<uintptr_t>(b->base) |
+         reinterpret_cast<uintptr_t>(t->base)) & 127u)
+        return false;
+    return true;
+}
+
+int run_fast_contract(int planes, const trimul_planes* a, const trimul_planes* b, const trimul_planes* t,
+                      cudaStream_t st, int32_t* status) {
+    CUtensorMap tmA, tmB, tmD;
+    if (!encode_planes(&tmA, *a, planes, kCtBK, kCtBM, 1)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmB, *b, planes, kCtBK, kCtBN, 1)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmD, *t, planes, 64, kCtBM, 1)) return TRIMUL_E_CUDA;
+    ContractParams p;
+    p.planes = planes;
+    p.rows_a = (int)a->rows; p.rows_b = (int)b->rows; p.K = (int)a->cols;
+    p.tiles_m = (p.rows_a + kCtBM - 1) / kCtBM;
+    p.tiles_n = (p.rows_b + kCtBN - 1) / kCtBN;
+    p.num_kb = (p.K + kCtBK - 1) / kCtBK;
+    p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_k_chunk = eff_chunk(a->col_chunk, a->cols);
+    p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_k_chunk = eff_chunk(b->col_chunk, b->cols);
+    p.d_row_chunk = eff_chunk(t->row_chunk, t->rows); p.d_col_chunk = eff_chunk(t->col_chunk, t->cols);
+    p.status = status;
+    const int64_t total = (int64_t)planes * p.tiles_m * p.tiles_n;
+    if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
+    if (!ensure_smem(contract_sm100_kernel, kCtSmemBytes)) return TRIMUL_E_CUDA;
+    const int grid = total < sm_count() ? (int)total : sm_count();
+    contract_sm100_kernel<<<grid, kCtThreads, kCtSmemBytes, st>>>(tmA, tmB, tmD, p);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------------------
+// stage 3
+// ---------------------------------------------------------------------------------------
+template <typename T>
+int run_plain_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
+                  const void* residual, cudaStream_t st) {
+    PlainTm2Params p;
+    p.B = d->B; p.rows = d->rows; p.N = d->N; p.c = d->c;
+    p.gamma_in = w->ln_in_weight; p.beta_in = w->ln_in_bias;
+    p.gamma_out = w->ln_out_weight; p.beta_out = w->ln_out_bias;
+    p.eps_in = d->eps_in; p.eps_out = d->eps_out;
+    p.w_gate = w->w_gate; p.w_out = w->w_out;
+    p.tri = view_of(*tri);
+    const int64_t grid = (int64_t)d->B * d->rows * ((d->N + kPlainPos - 1) / kPlainPos);
+    plain_tm2_kernel<T><<<(unsigned)grid, kPlainThreads, 0, st>>>(static_cast<const T*>(z), static_cast<T*>(out),
+                                                                   static_cast<const T*>(residual), p);
+    return launch_status();
+}
+
+int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
+                 const void* residual, cudaStream_t st, int32_t* status) {
+    CUtensorMap tmZ, tmWg, tmWo, tmOut, tmRes;
+    const uint64_t dims[4] = {128, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
+    const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    if (!encode_bf16(&tmZ, z, 4, dims, strides, box, true)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmOut, out, 4, dims, strides, box, true)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmRes, residual ? residual : z, 4, dims, strides, box, true)) return TRIMUL_E_CUDA;
+    const uint64_t wdims[2] = {128, 128};
+    const uint64_t wstrides[1] = {128};
+    const uint32_t wbox[2] = {64, 128};
+    if (!encode_bf16(&tmWg, w->w_gate, 2, wdims, wstrides, wbox, true)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmWo, w->w_out, 2, wdims, wstrides, wbox, true)) return TRIMUL_E_CUDA;
+    Tm2Params p;
+    p.B = d->B; p.rows = d->rows; p.N = d->N;
+    p.tiles_per_row = (d->N + kT2P - 1) / kT2P;
+    const int64_t total = (int64_t)d->B * d->rows * p.tiles_per_row;
+    if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
+    p.total_tiles = (int)total;
+    p.tri = static_cast<const __nv_bfloat16*>(tri->base);
+    p.tri_pitch = tri->pitch; p.tri_plane_stride = tri->plane_stride;
+    p.gamma_in = w->ln_in_weight; p.beta_in = w->ln_in_bias;
+    p.gamma_out = w->ln_out_weight; p.beta_out = w->ln_out_bias;
+    p.eps_in = d->eps_in; p.eps_out = d->eps_out;
+    p.has_residual = residual != nullptr;
+    p.status = status;
+    if (!ensure_smem(tm2_sm100_kernel, kT2SmemBytes)) return TRIMUL_E_CUDA;
+    const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+    tm2_sm100_kernel<<<grid, kT2Threads, kT2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmRes, p);
+    return launch_status();
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+}  // namespace
+
+// =========================================================================================
+// exported entry points
+// =========================================================================================
+extern "C" {
+
+int trimul_b200_abi_version(void) { return TRIMUL_B200_ABI_VERSION; }
+
+const char* trimul_b200_strerror(int code) {
+    switch (code) {
+        case TRIMUL_OK: return "success";
+        case TRIMUL_E_INVALID: return "invalid argument (null pointer, bad size or enum, misaligned buffer)";
+        case TRIMUL_E_UNSUPPORTED: return "unsupported configuration";
+        case TRIMUL_E_WORKSPACE: return "workspace too small";
+        case TRIMUL_E_CUDA: return "CUDA call failed (kernel launch or tensor-map encode)";
+        case TRIMUL_E_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+        default: return "unknown error code";
+    }
+}
+
+int trimul_b200_workspace_bytes(const trimul_desc* desc, size_t* bytes, trimul_planes* a, trimul_planes* b,
+                                trimul_planes* tri) {
+    int rc = check_desc(desc);
+    if (rc != TRIMUL_OK) return rc;
+    if (bytes == nullptr) return TRIMUL_E_INVALID;
+    const int64_t esz = desc->dtype == TRIMUL_DTYPE_BF16 ? 2 : 4;
+    const int64_t planes = (int64_t)desc->B * desc->c;
+    const bool inc = desc->direction == TRIMUL_INCOMING;
+    // a, b: outgoing [planes][rows][N], incoming [planes][N][rows];  tri: [planes][rows][N]
+    const int64_t ab_rows = inc ? desc->N : desc->rows, ab_cols = inc ? desc->rows : desc->N;
+    const int64_t ab_pitch = round_up(ab_cols, 8), t_pitch = round_up(desc->N, 8);
+    const int64_t ab_plane = ab_rows * ab_pitch, t_plane = (int64_t)desc->rows * t_pitch;
+    const int64_t ab_bytes = round_up(planes * ab_plane * esz, 1024), t_bytes = round_up(planes * t_plane * esz, 1024);
+    trimul_planes pa = {nullptr, ab_rows, ab_cols, ab_pitch, ab_plane, 0, ab_rows, ab_cols};
+    trimul_planes pb = pa;
+    pb.base = reinterpret_cast<void*>((uintptr_t)ab_bytes);
+    trimul_planes pt = {reinterpret_cast<void*>((uintptr_t)(2 * ab_bytes)), desc->rows, desc->N, t_pitch, t_plane, 0,
+                        desc->rows, desc->N};
+    if (a) *a = pa;
+    if (b) *b = pb;
+    if (tri) *tri = pt;
+    *bytes = (size_t)(2 * ab_bytes + t_bytes);
+    return TRIMUL_OK;
+}
+
+int trimul_b200_tm1(const trimul_desc* desc, const void* z, const uint8_t* mask, const trimul_weights* w,
+                    const trimul_planes* a, const trimul_planes* b, void* stream, int32_t* status) {
+    int rc = check_desc(desc);
+    if (rc != TRIMUL_OK) return rc;
+    if ((rc = check_weights(w)) != TRIMUL_OK) return rc;
+    if (z == nullptr || !aligned16(z)) return TRIMUL_E_INVALID;
+    if (desc->mask_kind != TRIMUL_MASK_NONE && mask == nullptr) return TRIMUL_E_INVALID;
+    const bool inc = desc->direction == TRIMUL_INCOMING;
+    const int64_t prow = inc ? desc->N : desc->rows, pcol = inc ? desc->rows : desc->N;
+    if ((rc = check_planes(a, prow, pcol)) != TRIMUL_OK) return rc;
+    if ((rc = check_planes(b, prow, pcol)) != TRIMUL_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == TRIMUL_DTYPE_FP32) return run_plain_tm1<float>(desc, z, mask, w, a, b, st);
+    const bool chunks_ok = (a->col_chunk >= a->cols || a->col_chunk % 64 == 0) &&
+                           (b->col_chunk >= b->cols || b->col_chunk % 64 == 0) &&
+                           ((reinterpret_cast<uintptr_t>(a->base) | reinterpret_cast<uintptr_t>(b->base)) & 127u) == 0;
+    if (tensor_core_path(desc) && chunks_ok) return run_fast_tm1(desc, z, mask, w, a, b, st, status);
+    return run_plain_tm1<__nv_bfloat16>(desc, z, mask, w, a, b, st);
+}
+
+int trimul_b200_contract(int32_t dtype, uint32_t flags, int32_t planes, const trimul_planes* a,
+                         const trimul_planes* b, const trimul_planes* tri, void* stream, int32_t* status) {
+    if (a == nullptr || b == nullptr || tri == nullptr) return TRIMUL_E_INVALID;
+    if (planes <= 0 || planes > 65535) return TRIMUL_E_INVALID;
+    if (dtype != TRIMUL_DTYPE_BF16 && dtype != TRIMUL_DTYPE_FP32) return TRIMUL_E_INVALID;
+    int rc;
+    if ((rc = check_planes(a, a->rows, a->cols)) != TRIMUL_OK) return rc;
+    if ((rc = check_planes(b, b->rows, a->cols)) != TRIMUL_OK) return rc;
+    if ((rc = check_planes(tri, a->rows, b->rows)) != TRIMUL_OK) return rc;
+    if (a->rows <= 0 || b->rows <= 0 || a->cols <= 0) return TRIMUL_E_INVALID;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (dtype == TRIMUL_DTYPE_FP32) return run_plain_contract<float>(planes, a, b, tri, st);
+    if ((flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0 && fast_contract_ok(a, b, tri))
+        return run_fast_contract(planes, a, b, tri, st, status);
+    return run_plain_contract<__nv_bfloat16>(planes, a, b, tri, st);
+}
+
+int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes* tri, const trimul_weights* w,
+                    void* out, const void* residual, void* stream, int32_t* status) {
+    int rc = check_desc(desc);
+    if (rc != TRIMUL_OK) return rc;
+    if ((rc = check_weights(w)) != TRIMUL_OK) return rc;
+    if (z == nullptr || out == nullptr || out == z || !aligned16(z) || !aligned16(out)) return TRIMUL_E_INVALID;
+    if (residual != nullptr && (!aligned16(residual) || residual == out)) return TRIMUL_E_INVALID;
+    if ((rc = check_planes(tri, desc->rows, desc->N)) != TRIMUL_OK) return rc;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (desc->dtype == TRIMUL_DTYPE_FP32) return run_plain_tm2<float>(desc, z, tri, w, out, residual, st);
+    const bool plain_layout = tri->row_chunk >= tri->rows && tri->col_chunk >= tri->cols;
+    if (tensor_core_path(desc) && plain_layout) return run_fast_tm2(desc, z, tri, w, out, residual, st, status);
+    return run_plain_tm2<__nv_bfloat16>(desc, z, tri, w, out, residual, st);
+}
+
+int trimul_b200_forward(const trimul_desc* desc, const void* z, const uint8_t* mask, const trimul_weights* w,
+                        void* out, const void* residual, void* workspace, size_t workspace_bytes, void* stream,
+                        int32_t* status) {
+    int rc = check_desc(desc);
+    if (rc != TRIMUL_OK) return rc;
+    if (desc->rows != desc->N || desc->row0 != 0) return TRIMUL_E_INVALID;
+    if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return TRIMUL_E_INVALID;
+    size_t need = 0;
+    trimul_planes a, b, t;
+    if ((rc = trimul_b200_workspace_bytes(desc, &need, &a, &b, &t)) != TRIMUL_OK) return rc;
+    if (workspace_bytes < need) return TRIMUL_E_WORKSPACE;
+    const uintptr_t base = reinterpret_cast<uintptr_t>(workspace);
+    a.base = reinterpret_cast<void*>(base + reinterpret_cast<uintptr_t>(a.base));
+    b.base = reinterpret_cast<void*>(base + reinterpret_cast<uintptr_t>(b.base));
+    t.base = reinterpret_cast<void*>(base + reinterpret_cast<uintptr_t>(t.base));
+    // validate everything before the first launch, so an error leaves nothing enqueued
+    if ((rc = check_weights(w)) != TRIMUL_OK) return rc;
+    if (z == nullptr || out == nullptr || out == z || !aligned16(z) || !aligned16(out)) return TRIMUL_E_INVALID;
+    if (residual != nullptr && (!aligned16(residual) || residual == out)) return TRIMUL_E_INVALID;
+    if (desc->mask_kind != TRIMUL_MASK_NONE && mask == nullptr) return TRIMUL_E_INVALID;
+    if ((rc = trimul_b200_tm1(desc, z, mask, w, &a, &b, stream, status)) != TRIMUL_OK) return rc;
+    if ((rc = trimul_b200_contract(desc->dtype, desc->flags, desc->B * desc->c, &a, &b, &t, stream, status)) !=
+        TRIMUL_OK)
+        return rc;
+    return trimul_b200_tm2(desc, z, &t, w, out, residual, stream, status);
+}
+
+}  // extern "C"

@@ -1,0 +1,213 @@
+"""Functional entry points of the B200 TriangleMultiplication block.
+
+``triangle_multiplicative_update_b200`` has the signature of the reference's
+functional interface (``src/miniworld_engine/modules/triangle_multiplication/interface.py:8-22``,
+ground truth ``reference.py:86-122``, shipped op ``kernels/trimul_inproj/whole_op.py:170-184``)
+and runs the three CUDA stages through the C-ABI library.  PyTorch is used for device
+memory, streams and nothing else.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+__all__ = [
+    "triangle_multiplicative_update_b200",
+    "trimul_forward",
+    "read_status",
+    "workspace_bytes",
+]
+
+_TORCH_DTYPES = {torch.bfloat16: _lib.DTYPE_BF16, torch.float32: _lib.DTYPE_FP32}
+
+_workspaces: dict = {}
+_status: dict = {}
+
+
+def _dtype_code(t: torch.Tensor) -> int:
+    try:
+        return _TORCH_DTYPES[t.dtype]
+    except KeyError:
+        raise NotImplementedError(
+            f"trimul_b200 supports torch.bfloat16 and torch.float32 activations, got {t.dtype}") from None
+
+
+def _require_cuda(t: torch.Tensor, name: str) -> None:
+    if not t.is_cuda:
+        raise RuntimeError(
+            f"{name} must live on a CUDA device: trimul_b200 has no CPU path (got device {t.device})")
+
+
+def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Grow-only per-(device, stream) scratch buffer for the a/b/tri planes."""
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    buf = _workspaces.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        _workspaces[key] = buf
+    return buf
+
+
+def _status_words(device: torch.device) -> torch.Tensor:
+    st = _status.get(device.index)
+    if st is None:
+        st = torch.zeros(4, dtype=torch.int32, device=device)
+        _status[device.index] = st
+    return st
+
+
+def read_status(device=None) -> tuple:
+    """Synchronise and return the 4 device status words ``(code, stage, block, detail)``.
+    ``code == 0`` means no bounded wait has expired since the words were created."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    st = _status_words(device)
+    torch.cuda.synchronize(device)
+    return tuple(int(v) for v in st.cpu())
+
+
+def workspace_bytes(B: int, N: int, c: int, dtype: torch.dtype, outgoing: bool = True) -> int:
+    d = _lib.make_desc(B, N, c, dtype=_TORCH_DTYPES[dtype],
+                       direction=_lib.OUTGOING if outgoing else _lib.INCOMING)
+    n = C.c_size_t()
+    _lib.check(_lib.load().trimul_b200_workspace_bytes(C.byref(d), C.byref(n), None, None, None),
+               "trimul_b200_workspace_bytes")
+    return n.value
+
+
+def _weights_struct(c, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_right_gate,
+                    ln_out_w, ln_out_b, w_gate, w_out, device):
+    """Validate and pin the parameter tensors; returns (struct, keep-alive list)."""
+    keep = []
+
+    def lin(t, name):
+        if tuple(t.shape) != (c, c):
+            raise ValueError(f"{name} must have shape ({c}, {c}), got {tuple(t.shape)}")
+        _require_cuda(t, name)
+        t = t.detach()
+        if t.dtype != dtype or not t.is_contiguous():
+            t = t.to(dtype).contiguous()
+        keep.append(t)
+        return t.data_ptr()
+
+    def vec(t, name):
+        if tuple(t.shape) != (c,):
+            raise ValueError(f"{name} must have shape ({c},), got {tuple(t.shape)}")
+        _require_cuda(t, name)
+        t = t.detach()
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            t = t.float().contiguous()
+        keep.append(t)
+        return t.data_ptr()
+
+    w = _lib.Weights(
+        vec(ln_in_w, "norm_in_weight"), vec(ln_in_b, "norm_in_bias"),
+        lin(w_left, "to_left.weight"), lin(w_left_gate, "to_left_gate.weight"),
+        lin(w_right, "to_right.weight"), lin(w_right_gate, "to_right_gate.weight"),
+        vec(ln_out_w, "norm_out_weight"), vec(ln_out_b, "norm_out_bias"),
+        lin(w_gate, "to_gate.weight"), lin(w_out, "to_out.weight"))
+    return w, keep
+
+
+def trimul_forward(
+    x: torch.Tensor,
+    mask: torch.Tensor | None,
+    *,
+    outgoing: bool,
+    ln_in_weight, ln_in_bias, w_left, w_left_gate, w_right, w_right_gate,
+    ln_out_weight, ln_out_bias, w_gate, w_out,
+    eps_in: float = 1e-5,
+    eps_out: float = 1e-5,
+    residual: torch.Tensor | None = None,
+    plain_kernels: bool = False,
+) -> torch.Tensor:
+    """One block call on the current CUDA stream.  ``mask`` is a ``[B,N]`` token mask, a
+    ``[B,N,N]`` pair mask or None; ``residual`` (same shape/dtype as ``x``) is added to the
+    result when given."""
+    if x.dim() != 4 or x.shape[1] != x.shape[2]:
+        raise ValueError(f"x must be [B, N, N, c], got {tuple(x.shape)}")
+    _require_cuda(x, "x")
+    B, N, _, c = x.shape
+    code = _dtype_code(x)
+    x = x.detach()
+    if not x.is_contiguous():
+        x = x.contiguous()
+    mask_kind, mask_u8 = _lib.MASK_NONE, None
+    if mask is not None:
+        if tuple(mask.shape) == (B, N):
+            mask_kind = _lib.MASK_TOKEN
+        elif tuple(mask.shape) == (B, N, N):
+            mask_kind = _lib.MASK_PAIR
+        else:
+            raise ValueError(f"mask must be [B,N] or [B,N,N], got {tuple(mask.shape)}")
+        _require_cuda(mask, "mask")
+        mask_u8 = (mask != 0).to(torch.uint8).contiguous()
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype:
+            raise ValueError("residual must match x in shape and dtype")
+        _require_cuda(residual, "residual")
+        residual = residual.detach().contiguous()
+
+    lib = _lib.load()
+    desc = _lib.make_desc(B, N, c, dtype=code, direction=_lib.OUTGOING if outgoing else _lib.INCOMING,
+                          mask_kind=mask_kind, eps_in=eps_in, eps_out=eps_out,
+                          flags=_lib.FLAG_PLAIN_KERNELS if plain_kernels else 0)
+    w, keep = _weights_struct(c, x.dtype, ln_in_weight, ln_in_bias, w_left, w_left_gate, w_right, w_right_gate,
+                              ln_out_weight, ln_out_bias, w_gate, w_out, x.device)
+    nbytes = C.c_size_t()
+    _lib.check(lib.trimul_b200_workspace_bytes(C.byref(desc), C.byref(nbytes), None, None, None),
+               "trimul_b200_workspace_bytes")
+    with torch.cuda.device(x.device):
+        ws = _workspace(x.device, nbytes.value)
+        out = torch.empty_like(x)
+        st = _status_words(x.device)
+        stream = torch.cuda.current_stream(x.device).cuda_stream
+        rc = lib.trimul_b200_forward(
+            C.byref(desc), x.data_ptr(), mask_u8.data_ptr() if mask_u8 is not None else None, C.byref(w),
+            out.data_ptr(), residual.data_ptr() if residual is not None else None,
+            ws.data_ptr(), ws.numel(), stream, st.data_ptr())
+    _lib.check(rc, "trimul_b200_forward")
+    # parameter copies made above must outlive the enqueued kernels
+    for t in keep:
+        t.record_stream(torch.cuda.current_stream(x.device))
+    return out
+
+
+def triangle_multiplicative_update_b200(
+    x: torch.Tensor,
+    direction: str,
+    mask: torch.Tensor | None,
+    norm_in_weight: torch.Tensor,
+    norm_in_bias: torch.Tensor,
+    p_in_weight: torch.Tensor,
+    g_in_weight: torch.Tensor,
+    norm_out_weight: torch.Tensor,
+    norm_out_bias: torch.Tensor,
+    p_out_weight: torch.Tensor,
+    g_out_weight: torch.Tensor,
+    eps: float = 1e-5,
+) -> torch.Tensor:
+    """Drop-in for ``triangle_multiplicative_update_cute`` (``interface.py:8-22``).
+
+    ``x (B,I,J,D)``; ``direction`` "outgoing" | "incoming" (anything else raises
+    ``ValueError`` like ``reference.py:118-119``); ``mask`` a ``(B,I,J)`` pair mask, a
+    ``(B,L)`` token mask (accepted by the shipped op, ``whole_op.py:56-58``) or None;
+    ``p_in_weight (2D,D) = [to_left; to_right]``, ``g_in_weight (2D,D) = [to_left_gate;
+    to_right_gate]``, ``p_out_weight = to_out.weight``, ``g_out_weight = to_gate.weight``.
+    No residual is added.
+    """
+    if direction not in ("outgoing", "incoming"):
+        raise ValueError(f"direction must be outgoing|incoming, got {direction!r}")
+    D = x.shape[-1]
+    if tuple(p_in_weight.shape) != (2 * D, D) or tuple(g_in_weight.shape) != (2 * D, D):
+        raise ValueError(f"p_in_weight and g_in_weight must be ({2 * D}, {D})")
+    return trimul_forward(
+        x, mask, outgoing=(direction == "outgoing"),
+        ln_in_weight=norm_in_weight, ln_in_bias=norm_in_bias,
+        w_left=p_in_weight[:D], w_left_gate=g_in_weight[:D],
+        w_right=p_in_weight[D:], w_right_gate=g_in_weight[D:],
+        ln_out_weight=norm_out_weight, ln_out_bias=norm_out_bias,
+        w_gate=g_out_weight, w_out=p_out_weight, eps_in=eps, eps_out=eps)

@@ -1,0 +1,187 @@
+"""GPU parity tests: the CUDA path, called through the C ABI, against the CPU oracle and the
+golden fixtures generated from the reference.
+
+Tolerances (relative RMS error, ``||y - ref|| / ||ref||``):
+  * fp32 path  <= 1e-5 against the fp32 oracle / fixture
+  * bf16 path  <= 1e-2 against the bf16 oracle / fixture
+"""
+
+import glob
+import os
+
+import pytest
+import torch
+
+from oracle import trimul_oracle as O
+from tests._util import forward_kwargs, oracle_out
+from tests.test_oracle_golden import FILES, load_case
+
+pytestmark = pytest.mark.gpu
+
+TOL_FP32 = 1e-5
+TOL_BF16 = 1e-2
+
+
+@pytest.fixture(scope="module")
+def dev():
+    import miniworld_engine_b200  # noqa: F401  (fails loudly if the package is broken)
+    from miniworld_engine_b200 import _lib
+    _lib.load()
+    return torch.device("cuda", 0)
+
+
+def run_block(z, mask, w, outgoing, dtype, dev, **kw):
+    from miniworld_engine_b200 import read_status, trimul_forward
+    y = trimul_forward(z.to(dtype).to(dev), None if mask is None else mask.to(dev), outgoing=outgoing,
+                       **forward_kwargs(w, dtype, dev), **kw)
+    st = read_status(dev)
+    assert st[0] == 0, f"device status {st}"
+    return y.cpu()
+
+
+@pytest.mark.parametrize("path", FILES, ids=[os.path.basename(f)[:-4] for f in FILES])
+def test_golden_fixture(path, dev):
+    name, z, mask, w, gold, dtype, direction, form = load_case(path)
+    if form == "module":
+        y = run_block(z, mask, w, direction == "outgoing", dtype, dev)
+    else:
+        from miniworld_engine_b200 import triangle_multiplicative_update_b200 as f
+        wd = w.to(dtype)
+        y = f(z.to(dtype).to(dev), direction, mask.to(dev),
+              wd.ln_pair_weight.to(dev), wd.ln_pair_bias.to(dev),
+              torch.cat([wd.to_left, wd.to_right]).to(dev), torch.cat([wd.to_left_gate, wd.to_right_gate]).to(dev),
+              wd.ln_out_weight.to(dev), wd.ln_out_bias.to(dev), wd.to_out.to(dev), wd.to_gate.to(dev), 1e-5).cpu()
+    assert y.dtype == dtype and tuple(y.shape) == tuple(gold.shape)
+    err = O.rel_rms(y.float(), gold)
+    tol = TOL_FP32 if dtype == torch.float32 else TOL_BF16
+    assert err <= tol, f"{name}: rel-RMS {err:.3e} > {tol}"
+
+
+def test_cfg1_outgoing_fp32_n32(dev):
+    w, z, m = O.make_weights(128, 0), O.make_input(1, 32, 128, 1), O.make_token_mask(1, 32, "ones")
+    y = run_block(z, m, w, True, torch.float32, dev)
+    err = O.rel_rms(y, O.trimul_forward(z, m, w, True))
+    assert err <= TOL_FP32, f"rel-RMS {err:.3e}"
+
+
+@pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
+@pytest.mark.parametrize("N,B,mask_kind,affine", [
+    (32, 1, "ones", "unit"),
+    (61, 1, "tail7", "random"),
+    (128, 2, "rand5", "random"),
+    (129, 1, "tail20", "random"),
+    (200, 1, None, "unit"),
+    (384, 1, "ones", "unit"),          # BASELINE config 2 (outgoing)
+])
+def test_bf16_c128_block_vs_oracle(N, B, mask_kind, affine, outgoing, dev):
+    w = O.make_weights(128, 0, affine=affine)
+    z = O.make_input(B, N, 128, 1)
+    m = None if mask_kind is None else O.make_token_mask(B, N, mask_kind)
+    y = run_block(z, m, w, outgoing, torch.bfloat16, dev)
+    ref16 = oracle_out(z, m, w, outgoing, torch.bfloat16)
+    ref32 = O.trimul_forward(z.bfloat16().float(), m, w.to(torch.bfloat16).to(torch.float32), outgoing)
+    e16, e32 = O.rel_rms(y.float(), ref16.float()), O.rel_rms(y.float(), ref32)
+    print(f"N={N} B={B} {'out' if outgoing else 'in'}: vs bf16 oracle {e16:.3e}, vs fp32 oracle {e32:.3e}")
+    assert e16 <= TOL_BF16 and e32 <= TOL_BF16
+
+
+def test_cfg3_incoming_bf16_n768_tail77(dev):
+    w, z, m = O.make_weights(128, 0), O.make_input(1, 768, 128, 1), O.make_token_mask(1, 768, "tail77")
+    y = run_block(z, m, w, False, torch.bfloat16, dev)
+    ref = oracle_out(z, m, w, False, torch.bfloat16)
+    err = O.rel_rms(y.float(), ref.float())
+    assert err <= TOL_BF16, f"rel-RMS {err:.3e}"
+    # padded rows/columns of a, b are exactly zero, so with beta_out = 0 the padded outputs
+    # equal sigmoid(.) * (Wo . 0) = 0 in the reference and here alike
+    assert float(y[:, 768 - 77:, 768 - 77:].float().abs().max()) == float(ref[:, 768 - 77:, 768 - 77:].float().abs().max())
+
+
+@pytest.mark.parametrize("c", [64, 128, 256])
+def test_cfg4_outgoing_bf16_b2_n512_dpair_sweep(c, dev):
+    w, z = O.make_weights(c, 0), O.make_input(2, 512, c, 1)
+    m = O.make_token_mask(2, 512, "ones")
+    y = run_block(z, m, w, True, torch.bfloat16, dev)
+    err = O.rel_rms(y.float(), oracle_out(z, m, w, True, torch.bfloat16).float())
+    assert err <= TOL_BF16, f"c={c}: rel-RMS {err:.3e}"
+
+
+def test_pair_mask_and_token_mask_agree(dev):
+    w, z = O.make_weights(128, 5, affine="random"), O.make_input(1, 96, 128, 6)
+    m = O.make_token_mask(1, 96, "rand5", seed=9)
+    pm = m.unsqueeze(-1) & m.unsqueeze(-2)
+    for outgoing in (True, False):
+        a = run_block(z, m, w, outgoing, torch.bfloat16, dev)
+        b = run_block(z, pm, w, outgoing, torch.bfloat16, dev)
+        assert torch.equal(a, b)
+
+
+def test_mask_none_equals_all_ones_and_batches_are_independent(dev):
+    w, z = O.make_weights(128, 0), O.make_input(2, 160, 128, 1)
+    ones = O.make_token_mask(2, 160, "ones")
+    a = run_block(z, None, w, True, torch.bfloat16, dev)
+    b = run_block(z, ones, w, True, torch.bfloat16, dev)
+    assert torch.equal(a, b)
+    c1 = run_block(z[1:2], None, w, True, torch.bfloat16, dev)
+    assert torch.equal(a[1:2], c1)
+
+
+def test_residual_matches_reference_module_semantics(dev):
+    w, z = O.make_weights(128, 0), O.make_input(1, 130, 128, 1)
+    zb = z.bfloat16()
+    y = run_block(z, None, w, True, torch.bfloat16, dev)
+    yr = run_block(z, None, w, True, torch.bfloat16, dev, residual=zb.to(dev))
+    assert torch.equal(yr, y + zb)       # bf16 add of the bf16-rounded block output, module.py:453
+
+
+def test_tensor_core_kernels_match_plain_kernels(dev):
+    """Same layouts, same rounding points: the tcgen05 path and the CUDA-core path agree to
+    within a few bf16 ulps of accumulated difference."""
+    w, z = O.make_weights(128, 0, affine="random"), O.make_input(1, 192, 128, 1)
+    m = O.make_token_mask(1, 192, "tail13")
+    for outgoing in (True, False):
+        fast = run_block(z, m, w, outgoing, torch.bfloat16, dev)
+        plain = run_block(z, m, w, outgoing, torch.bfloat16, dev, plain_kernels=True)
+        err = O.rel_rms(fast.float(), plain.float())
+        assert err <= 4e-3, f"rel-RMS {err:.3e}"
+
+
+def test_poisoned_workspace_gives_identical_result(dev):
+    """Nothing may depend on what the scratch planes held before the call (pitch padding,
+    out-of-range tile parts): NaN-filling the workspace must not change a single bit."""
+    from miniworld_engine_b200 import functional as Fn
+    w, z = O.make_weights(128, 0), O.make_input(1, 77, 128, 1)
+    m = O.make_token_mask(1, 77, "tail9")
+    a = run_block(z, m, w, False, torch.bfloat16, dev)
+    for buf in Fn._workspaces.values():
+        buf.view(torch.int16).fill_(0x7FC0)      # bf16 NaN pattern
+    b = run_block(z, m, w, False, torch.bfloat16, dev)
+    assert torch.equal(a, b) and not torch.isnan(b.float()).any()
+
+
+def test_errors_follow_the_reference_interface(dev):
+    from miniworld_engine_b200 import TriangleMultiplicationB200, triangle_multiplicative_update_b200 as f
+    x = torch.zeros(1, 8, 8, 128, device=dev, dtype=torch.bfloat16)
+    v, W2, W1 = torch.ones(128, device=dev), torch.zeros(256, 128, device=dev), torch.zeros(128, 128, device=dev)
+    with pytest.raises(ValueError):
+        f(x, "sideways", None, v, v, W2, W2, v, v, W1, W1)
+    with pytest.raises(ValueError):
+        TriangleMultiplicationB200(128, d_hidden=64)
+    with pytest.raises(NotImplementedError):
+        f(x.half(), "outgoing", None, v, v, W2, W2, v, v, W1, W1)
+    with pytest.raises(RuntimeError):
+        f(x.cpu(), "outgoing", None, v, v, W2, W2, v, v, W1, W1)
+
+
+def test_module_state_dict_roundtrip_and_forward(dev):
+    from miniworld_engine_b200 import TriangleMultiplicationB200
+    w = O.make_weights(128, 0, affine="random")
+    mod = TriangleMultiplicationB200(128, outgoing=False)
+    mod.load_state_dict(w.state_dict())
+    mod = mod.to(dev).to(torch.bfloat16).eval()
+    assert mod.ln_pair.weight.dtype == torch.float32 and mod.to_left.weight.dtype == torch.bfloat16
+    z = O.make_input(1, 64, 128, 1).bfloat16()
+    m = O.make_token_mask(1, 64, "tail5")
+    with torch.no_grad():
+        y = mod(z.to(dev), m.to(dev)).cpu()
+    ref = O.trimul_forward(z, m, w.to(torch.bfloat16), False) + z
+    assert O.rel_rms(y.float(), ref.float()) <= TOL_BF16
