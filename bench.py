@@ -1,0 +1,338 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 TriangleMultiplication block.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference] [--workload NAME]
+
+A step is one block call (LayerNorm_in + gated projections, contraction, LayerNorm_out +
+gated output projection) on seeded synthetic input of the named workload.  Rank 0 prints
+ONE JSON line:
+
+* ``value`` / ``metric``: whole-job TFLOP/s with inputs resident in HBM, algorithmic FLOPs
+  ``B*(2*N^3*c + 12*N^2*c^2)`` per call, timed with CUDA events around exactly K steps
+  (barrier + synchronize on both sides, max over ranks);
+* ``e2e``: the same metric through the public module call with HOST buffers: pinned
+  host->device copy of z and the mask and device->host copy of the result inside the
+  timed region, every step;
+* ``roofline``: the dominant kernel's achieved rate (CUDA events between the stage
+  launches of the timed region) against the measured peak in MEASURED_PEAKS.json;
+* ``cpu_baseline``: the CPU oracle (a port of the reference's reference.py) timed on this
+  box's host cores on a bounded sample (rank 0, N=1 only);
+* ``clocks``: SM clock and throttle reasons sampled with nvidia-smi during the timed region.
+
+Workloads
+  n768_outgoing (default)  bf16, B=1, N=768, c=128, all-ones token mask: the configuration
+                           the headline metric is quoted on.  With --gpus N > 1 every rank
+                           runs its own block on its own pair tensor (weak scaling, no
+                           collective in the data path: independent pair tensors).
+  n384_outgoing            BASELINE config 2.
+  n768_incoming_pad77      BASELINE config 3.
+
+``--impl reference`` times the CPU oracle on the host cores instead (rank 0 only).
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: (B, N, c, outgoing, mask kind)
+    "n768_outgoing": (1, 768, 128, True, "ones"),
+    "n384_outgoing": (1, 384, 128, True, "ones"),
+    "n768_incoming_pad77": (1, 768, 128, False, "tail77"),
+    "n1024_outgoing": (1, 1024, 128, True, "ones"),
+    "n2048_outgoing": (1, 2048, 128, True, "rand5"),
+}
+METRIC = "trimul_block_tflops"
+UNIT = "TFLOP/s"
+
+
+def block_flops(B, N, c):
+    return float(B) * (2.0 * N ** 3 * c + 12.0 * N ** 2 * c ** 2)
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_tflops_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples during the timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.tmp = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(gpu_index)], stdout=self.tmp, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.tmp.flush()
+        self.tmp.seek(0)
+        sm, smax, reasons = [], [], set()
+        for line in self.tmp.read().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        self.tmp.close()
+        os.unlink(self.tmp.name)
+        if sm:
+            out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(smax), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+def cpu_oracle_rate(B, N, c, outgoing, mask_kind, budget_s=25.0, max_calls=3):
+    """TFLOP/s of the CPU oracle on this host, all cores, bf16 like the GPU workload."""
+    import torch
+    from oracle import trimul_oracle as O
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    w = O.make_weights(c, 0).to(torch.bfloat16)
+    z = O.make_input(B, N, c, 1).to(torch.bfloat16)
+    m = O.make_token_mask(B, N, mask_kind)
+    t0 = time.perf_counter()
+    O.trimul_forward(z, m, w, outgoing)                      # warm-up (thread pools, allocator)
+    warm = time.perf_counter() - t0
+    best, calls = float("inf"), 0
+    while calls < max_calls and (calls == 0 or (time.perf_counter() - t0) + best < budget_s):
+        t1 = time.perf_counter()
+        O.trimul_forward(z, m, w, outgoing)
+        best = min(best, time.perf_counter() - t1)
+        calls += 1
+    return {"value": block_flops(B, N, c) / best / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
+            "seconds_per_call": best,
+            "sample": f"{calls} full block call(s) of the same workload (bf16 oracle, best of {calls}, "
+                      f"warm-up {warm:.2f}s)"}
+
+
+def run_reference(args):
+    """Reference arm: the reference's CPU algorithm (oracle port) on the host cores."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    from oracle import trimul_oracle as O
+    B, N, c, outgoing, mask_kind = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    w = O.make_weights(c, 0).to(torch.bfloat16)
+    z = O.make_input(B, N, c, 1).to(torch.bfloat16)
+    m = O.make_token_mask(B, N, mask_kind)
+    for _ in range(args.warmup):
+        O.trimul_forward(z, m, w, outgoing)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        O.trimul_forward(z, m, w, outgoing)
+    dt = time.perf_counter() - t0
+    val = block_flops(B, N, c) * args.steps / dt / 1e12
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "calls_per_s": args.steps / dt, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic (seeded randn, all on the host)",
+        "config": {"workload": args.workload, "B": B, "N": N, "c": c,
+                   "direction": "outgoing" if outgoing else "incoming", "mask": mask_kind},
+        "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
+                         "sample": f"{args.steps} full block calls per run (each step = one call of the workload)"},
+        "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def run_b200(args):
+    import torch
+    import torch.distributed as dist
+    from oracle import trimul_oracle as O
+    from miniworld_engine_b200 import TriangleMultiplicationB200, read_status, stages as S
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the b200 arm has no CPU path (use --impl reference)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    B, N, c, outgoing, mask_kind = WORKLOADS[args.workload]
+    flops = block_flops(B, N, c)
+    # synthetic inputs: weights seed 0, input seed 1 (+rank: every rank its own pair tensor)
+    w = O.make_weights(c, 0)
+    z_host = O.make_input(B, N, c, 1 + rank).to(torch.bfloat16).pin_memory()
+    m_host = O.make_token_mask(B, N, mask_kind).pin_memory()
+    mod = TriangleMultiplicationB200(c, outgoing=outgoing)
+    mod.load_state_dict(w.state_dict())
+    mod = mod.to(dev).to(torch.bfloat16).eval()
+    z = z_host.to(dev)
+    m = m_host.to(dev)
+    wd = dict(ln_in_w=mod.ln_pair.weight, ln_in_b=mod.ln_pair.bias, w_left=mod.to_left.weight,
+              w_left_gate=mod.to_left_gate.weight, w_right=mod.to_right.weight,
+              w_right_gate=mod.to_right_gate.weight, ln_out_w=mod.ln_out.weight, ln_out_b=mod.ln_out.bias,
+              w_gate=mod.to_gate.weight, w_out=mod.to_out.weight)
+    planes = B * c
+    a = S.alloc_planes(planes, N, N, torch.bfloat16, dev)
+    b = S.alloc_planes(planes, N, N, torch.bfloat16, dev)
+    tri = S.alloc_planes(planes, N, N, torch.bfloat16, dev)
+
+    def step(ev=None):
+        """One block call = the three stage launches of trimul_b200_forward, with optional
+        events between them (the events cost nothing measurable)."""
+        if ev is not None:
+            ev[0].record()
+        S.tm1(z, m, wd, a, b, outgoing=outgoing)
+        if ev is not None:
+            ev[1].record()
+        S.contract(a, b, tri)
+        if ev is not None:
+            ev[2].record()
+        out = S.tm2(z, tri, wd)
+        if ev is not None:
+            ev[3].record()
+        return out
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    barrier()
+    for k in range(args.steps):
+        step(evs[k])
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = evs[0][0].elapsed_time(evs[-1][3])
+    stage_ms = [sum(e[i].elapsed_time(e[i + 1]) for e in evs) / args.steps for i in range(3)]
+    st = read_status(dev)
+    if st[0] != 0:
+        raise SystemExit(f"bench.py: device status {st}: a bounded wait expired, timing is invalid")
+
+    # end to end through the public module call, host buffers in and out
+    out_host = torch.empty_like(z_host)
+    def e2e_step():
+        zd = z_host.to(dev, non_blocking=True)
+        md = m_host.to(dev, non_blocking=True)
+        y = mod.block(zd, md)
+        out_host.copy_(y, non_blocking=True)
+    for _ in range(2):
+        e2e_step()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e2e_steps = max(3, min(args.steps, 10))
+    e0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1) / e2e_steps
+
+    t = torch.tensor([total_ms, e2e_ms] + stage_ms, device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms, *stage_ms = [float(v) for v in t.cpu()]
+
+    if rank == 0:
+        peaks = measured_peaks()
+        ms_per_step = total_ms / args.steps
+        value = flops * world / (ms_per_step * 1e-3) / 1e12
+        S_bytes = B * N * N * c * 2
+        stage_info = {
+            "tm1": {"ms": stage_ms[0], "bound": "hbm", "achieved": 3 * S_bytes / (stage_ms[0] * 1e-3) / 1e9,
+                    "unit": "GB/s", "peak": peaks["hbm_gbs"]},
+            "contract": {"ms": stage_ms[1], "bound": "tensor",
+                         "achieved": 2.0 * B * N ** 3 * c / (stage_ms[1] * 1e-3) / 1e12, "unit": "TFLOP/s",
+                         "peak": peaks["bf16_tflops_sustained"]},
+            "tm2": {"ms": stage_ms[2], "bound": "hbm", "achieved": 3 * S_bytes / (stage_ms[2] * 1e-3) / 1e9,
+                    "unit": "GB/s", "peak": peaks["hbm_gbs"]},
+        }
+        for v in stage_info.values():
+            v["frac"] = v["achieved"] / v["peak"]
+        dom = max(stage_info, key=lambda k: stage_info[k]["ms"])
+        roof = dict(stage_info[dom])
+        roof.update(kernel=dom, traffic=None, peak_source=peaks["source"])
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "calls_per_s": world * 1e3 / ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded randn pair tensor and weights, all-ones LayerNorm gamma)",
+            "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
+            "config": {"workload": args.workload, "B": B, "N": N, "c": c,
+                       "direction": "outgoing" if outgoing else "incoming", "mask": mask_kind,
+                       "parallelism": "one block per GPU, no collective" if world > 1 else "single GPU",
+                       "l2": "working set 5 x %.0f MB per call exceeds the 126 MB L2; no flush" % (S_bytes / 1e6)},
+            "gpu_launches": 3 * args.steps,
+            "e2e": {"value": flops * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": z_host.numel() * 2 + m_host.numel(),
+                    "d2h_bytes_per_step": out_host.numel() * 2},
+            "roofline": roof, "stages": stage_info, "clocks": clocks,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_oracle_rate(B, N, c, outgoing, mask_kind)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=None)
+    ap.add_argument("--warmup", type=int, default=None)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default="n768_outgoing", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        args.steps = 3 if args.steps is None else args.steps
+        args.warmup = 1 if args.warmup is None else args.warmup
+        run_reference(args)
+    else:
+        args.steps = 50 if args.steps is None else args.steps
+        args.warmup = 5 if args.warmup is None else args.warmup
+        run_b200(args)
+
+
+if __name__ == "__main__":
+    main()
