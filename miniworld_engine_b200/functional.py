@@ -42,6 +42,15 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
             f"{name} must live on a CUDA device: trimul_b200 has no CPU path (got device {t.device})")
 
 
+def _mask_bytes(mask: torch.Tensor) -> torch.Tensor:
+    """Mask as one byte per element, without a kernel launch when it already is bool/uint8."""
+    if mask.dtype == torch.bool:
+        return mask.contiguous().view(torch.uint8)
+    if mask.dtype == torch.uint8:
+        return mask.contiguous()
+    return (mask != 0).contiguous().view(torch.uint8)
+
+
 def _workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     """Grow-only per-(device, stream) scratch buffer for the a/b/tri planes."""
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
@@ -144,7 +153,7 @@ def trimul_forward(
         else:
             raise ValueError(f"mask must be [B,N] or [B,N,N], got {tuple(mask.shape)}")
         _require_cuda(mask, "mask")
-        mask_u8 = (mask != 0).to(torch.uint8).contiguous()
+        mask_u8 = _mask_bytes(mask)
     if residual is not None:
         if residual.shape != x.shape or residual.dtype != x.dtype:
             raise ValueError("residual must match x in shape and dtype")

@@ -15,7 +15,7 @@ from dataclasses import dataclass
 import torch
 
 from . import _lib
-from .functional import _dtype_code, _require_cuda, _status_words, _weights_struct
+from .functional import _dtype_code, _mask_bytes, _require_cuda, _status_words, _weights_struct
 
 __all__ = ["PlaneSpec", "alloc_planes", "planes_to_dense", "tm1", "contract", "tm2", "round_up"]
 
@@ -98,7 +98,7 @@ def _mask_arg(mask, B, N):
         kind = _lib.MASK_PAIR
     else:
         raise ValueError(f"mask must be [B,N] or [B,N,N] over the FULL token range, got {tuple(mask.shape)}")
-    return kind, (mask != 0).to(torch.uint8).contiguous()
+    return kind, _mask_bytes(mask)
 
 
 def tm1(z_slab: torch.Tensor, mask, weights: dict, a: PlaneSpec, b: PlaneSpec, *, outgoing: bool,
