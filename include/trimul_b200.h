@@ -49,6 +49,7 @@ extern "C" {
 #define TRIMUL_E_WORKSPACE       -3   /* workspace smaller than trimul_b200_workspace_bytes says    */
 #define TRIMUL_E_CUDA            -4   /* a CUDA runtime/driver call failed (launch, tensor map)     */
 #define TRIMUL_E_DEVICE_TIMEOUT  -5   /* only ever written to the device status words               */
+#define TRIMUL_E_STATIC_SCRATCH  -6   /* problem too large for the library's built-in scratch array */
 
 /* dtype of activations and Linear weights */
 #define TRIMUL_DTYPE_BF16 0           /* bf16 storage, fp32 accumulate, tensor-core kernels         */
@@ -189,6 +190,38 @@ int trimul_b200_contract(int32_t dtype, uint32_t flags, int32_t planes,
 int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes* tri,
                     const trimul_weights* w, void* out, const void* residual,
                     void* stream, int32_t* status);
+
+/*
+ * The whole block for callers that have no device memory to offer as a workspace.
+ * (No counterpart in the reference: its launchers allocate their intermediates with torch.)
+ *
+ * Some hosts of this library cannot hand over a workspace: a serving process that gave all
+ * device memory to its own pool at start-up, where a cudaMalloc issued from a plugin fails
+ * or eats into someone else's budget; a latency-critical loop that must not hit cudaMalloc's
+ * device-wide synchronisation; a foreign-function boundary that passes inputs and outputs
+ * only.  For them the a/b/tri planes live in a fixed array that is part of the library's
+ * device image, TRIMUL_B200_STATIC_SCRATCH_BYTES large.  Every GPU on which the library is
+ * used holds that array from the moment the library's device code is loaded there until the
+ * process exits, whether or not this function is ever called.
+ *
+ * Same arguments and results as trimul_b200_forward, minus the workspace.  Differences:
+ *   - a problem whose planes need more than TRIMUL_B200_STATIC_SCRATCH_BYTES (see
+ *     trimul_b200_workspace_bytes; N <= 208 at c = 128 in bf16 with B = 1) is refused
+ *     with TRIMUL_E_STATIC_SCRATCH before anything is enqueued;
+ *   - the first call on each device looks up the array's device address (once per device,
+ *     with that device current).  Make that first call before any stream capture begins;
+ *   - there is ONE array per device, shared by every call and every stream, and it keeps
+ *     whatever the previous call left in it.  The kernels overwrite every element they later
+ *     read, so nothing needs clearing between calls, but two calls whose kernels overlap on
+ *     the GPU (different streams, no dependency between them) race on it and both results
+ *     are then undefined.  Order such calls yourself;
+ *   - it calls no cudaMalloc, cudaFree or other allocating routine, and needs no torch.
+ */
+#define TRIMUL_B200_STATIC_SCRATCH_BYTES (32u << 20)
+
+int trimul_b200_forward_static(const trimul_desc* desc, const void* z, const uint8_t* mask,
+                               const trimul_weights* w, void* out, const void* residual,
+                               void* stream, int32_t* status);
 
 #ifdef __cplusplus
 }

@@ -16,6 +16,8 @@ ABI_VERSION = 1
 
 OK = 0
 E_INVALID, E_UNSUPPORTED, E_WORKSPACE, E_CUDA, E_DEVICE_TIMEOUT = -1, -2, -3, -4, -5
+E_STATIC_SCRATCH = -6
+STATIC_SCRATCH_BYTES = 32 << 20
 DTYPE_BF16, DTYPE_FP32 = 0, 1
 OUTGOING, INCOMING = 0, 1
 MASK_NONE, MASK_TOKEN, MASK_PAIR = 0, 1, 2
@@ -29,6 +31,7 @@ EXPORTED_SYMBOLS = (
     "trimul_b200_tm1",
     "trimul_b200_contract",
     "trimul_b200_tm2",
+    "trimul_b200_forward_static",
 )
 
 
@@ -87,6 +90,9 @@ def load():
     lib.trimul_b200_contract.argtypes = [C.c_int32, C.c_uint32, C.c_int32, PP, PP, PP, C.c_void_p, C.c_void_p]
     lib.trimul_b200_tm2.restype = C.c_int
     lib.trimul_b200_tm2.argtypes = [PD, C.c_void_p, PP, PW, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.trimul_b200_forward_static.restype = C.c_int
+    lib.trimul_b200_forward_static.argtypes = [PD, C.c_void_p, C.c_void_p, PW, C.c_void_p, C.c_void_p,
+                                               C.c_void_p, C.c_void_p]
     if lib.trimul_b200_abi_version() != ABI_VERSION:
         raise TrimulLibraryError(
             f"ABI mismatch: library {lib.trimul_b200_abi_version()}, binding {ABI_VERSION}; rebuild the library")

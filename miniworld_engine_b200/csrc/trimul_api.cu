@@ -21,6 +21,12 @@
 
 using namespace trimul;
 
+// Scratch for trimul_b200_forward_static: the a/b/tri planes of callers that cannot allocate.
+// It is part of the device image, so every GPU that loads this library carries it until the
+// process exits.  In HOST code this name is only a handle for cudaGetSymbolAddress — it is not
+// a device address and must never be passed to a kernel as one.
+static __device__ __align__(256) unsigned char g_static_scratch[TRIMUL_B200_STATIC_SCRATCH_BYTES];
+
 namespace {
 
 // ---------------------------------------------------------------------------------------
@@ -345,6 +351,9 @@ const char* trimul_b200_strerror(int code) {
         case TRIMUL_E_WORKSPACE: return "workspace too small";
         case TRIMUL_E_CUDA: return "CUDA call failed (kernel launch or tensor-map encode)";
         case TRIMUL_E_DEVICE_TIMEOUT: return "a bounded device-side wait expired";
+        case TRIMUL_E_STATIC_SCRATCH:
+            return "problem needs more scratch than the library's built-in array holds "
+                   "(TRIMUL_B200_STATIC_SCRATCH_BYTES); use trimul_b200_forward with your own workspace";
         default: return "unknown error code";
     }
 }
@@ -451,6 +460,48 @@ int trimul_b200_forward(const trimul_desc* desc, const void* z, const uint8_t* m
         TRIMUL_OK)
         return rc;
     return trimul_b200_tm2(desc, z, &t, w, out, residual, stream, status);
+}
+
+// ---------------------------------------------------------------------------------------
+// built-in scratch: device address of g_static_scratch, looked up once per device
+// ---------------------------------------------------------------------------------------
+namespace {
+
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+void* g_scratch_addr[kMaxDevices] = {};
+
+// Device address of the static scratch array on the CURRENT device.  The first call per device
+// asks the runtime for it (which also loads the device image there); later calls hit the cache.
+int static_scratch_address(void** out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return TRIMUL_E_CUDA;
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return TRIMUL_E_CUDA;
+        }
+        g_scratch_addr[dev] = p;
+    }
+    *out = g_scratch_addr[dev];
+    return TRIMUL_OK;
+}
+
+}  // namespace
+
+int trimul_b200_forward_static(const trimul_desc* desc, const void* z, const uint8_t* mask, const trimul_weights* w,
+                               void* out, const void* residual, void* stream, int32_t* status) {
+    size_t need = 0;
+    int rc = trimul_b200_workspace_bytes(desc, &need, nullptr, nullptr, nullptr);
+    if (rc != TRIMUL_OK) return rc;
+    if (need > (size_t)TRIMUL_B200_STATIC_SCRATCH_BYTES) return TRIMUL_E_STATIC_SCRATCH;
+    void* scratch = nullptr;
+    if ((rc = static_scratch_address(&scratch)) != TRIMUL_OK) return rc;
+    return trimul_b200_forward(desc, z, mask, w, out, residual, scratch, (size_t)TRIMUL_B200_STATIC_SCRATCH_BYTES,
+                               stream, status);
 }
 
 }  // extern "C"
