@@ -2,7 +2,7 @@
 // mbarrier, TMA (cp.async.bulk.tensor, no multicast anywhere), tcgen05 (TMEM allocation,
 // UMMA issue/commit, TMEM loads) and the shared-memory / instruction descriptors.
 //
-// Every wait in this file is bounded: it gives up after a fixed number of polls, raises a
+// Every wait in this file is bounded: it gives up after a fixed time, raises a
 // CTA-wide abort flag and reports through the caller's status words, so a protocol bug
 // ends the kernel instead of hanging the device.
 #pragma once
@@ -282,6 +282,17 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
         : "memory");
 }
 
+// Same, 16 consecutive columns.
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // ---------------------------------------------------------------------------------------
@@ -301,6 +312,99 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
     float t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(0.5f * x));
     return fmaf(0.5f, t, 0.5f);
+}
+
+__device__ __forceinline__ float tanh_fast(float x) {
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
+    return t;
+}
+
+// p * sigmoid(g) from HALVED inputs hp = p/2, hg = g/2:  p*sigmoid(g) = hp*tanh(hg) + hp.
+// The kernels halve the weight matrices once in shared memory (exact in bf16), so the
+// accumulators already hold hp and hg and the gate costs one MUFU and one FMA per value.
+__device__ __forceinline__ float gate_from_halves(float hp, float hg) { return fmaf(hp, tanh_fast(hg), hp); }
+
+// Multiply `nbytes` of bf16 data in shared memory by 0.5 in place (exact: only the exponent
+// changes), work split over `nthreads` cooperating threads with rank `tid`.
+__device__ __forceinline__ void halve_bf16_smem(uint8_t* base, int nbytes, int tid, int nthreads) {
+    const __nv_bfloat162 half2 = __floats2bfloat162_rn(0.5f, 0.5f);
+    for (int i = tid; i < nbytes / 16; i += nthreads) {
+        uint4 v = *reinterpret_cast<uint4*>(base + i * 16);
+        __nv_bfloat162* e = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) e[k] = __hmul2(e[k], half2);
+        *reinterpret_cast<uint4*>(base + i * 16) = v;
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// LayerNorm of one 128-channel row of a tile pair stored as two [128 rows][64 ch] SWIZZLE_128B
+// sub-tiles (`sub_bytes` apart), done IN PLACE by two cooperating threads that sit in adjacent
+// lanes: thread h (0/1) owns 16-byte chunks 4h..4h+3 of each sub-tile, i.e. channels
+// [32h, 32h+32) and [64+32h, 64+32h+32).  Two passes over shared memory with small loop bodies:
+//   1. shifted sums (shift = the row's first element) -> mean, variance without cancellation
+//   2. normalise, affine, round to bf16, store back
+// `zero_row` stores zeros instead (masked position: the projections of a zero row are exactly 0);
+// such a thread still runs both passes, because the pair exchanges partial sums by warp shuffle.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void ln_half_row_inplace(uint8_t* tile, int sub_bytes, int row, int h,
+                                                    const float* sGamma, const float* sBeta, float eps,
+                                                    bool zero_row) {
+    const uint32_t swz = (uint32_t)(row & 7);
+    uint8_t* rowp = tile + row * 128;
+    // NOTE: no early exit for masked rows — the shuffles below need every lane of the warp.
+    // shift: channel 0 lives in chunk 0 of sub-tile 0, owned by the even lane of the pair
+    const uint32_t first = *reinterpret_cast<const uint32_t*>(rowp + (swz << 4));
+    const float shift = bf16_lo(first);
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll 1
+    for (int s = 0; s < 2; ++s) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const uint4 v = *reinterpret_cast<const uint4*>(rowp + s * sub_bytes + ((((uint32_t)(4 * h + jj)) ^ swz) << 4));
+            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float d0 = bf16_lo(w4[e]) - shift, d1 = bf16_hi(w4[e]) - shift;
+                s1 += d0;
+                s2 = fmaf(d0, d0, s2);
+                s1 += d1;
+                s2 = fmaf(d1, d1, s2);
+            }
+        }
+    }
+    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
+    const float m1 = s1 * (1.0f / 128.0f);
+    const float var = fmaxf(fmaf(-m1, m1, s2 * (1.0f / 128.0f)), 0.f);
+    const float rstd = rsqrtf(var + eps);
+    const float nmr = -(shift + m1) * rstd;   // y = x*rstd + nmr
+#pragma unroll 1
+    for (int s = 0; s < 2; ++s) {
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+            const int j = 4 * h + jj;
+            uint4* p = reinterpret_cast<uint4*>(rowp + s * sub_bytes + ((((uint32_t)j) ^ swz) << 4));
+            const uint4 v = *p;
+            const int ch = s * 64 + j * 8;
+            const float4 g0 = *reinterpret_cast<const float4*>(sGamma + ch);
+            const float4 g1 = *reinterpret_cast<const float4*>(sGamma + ch + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(sBeta + ch);
+            const float4 b1 = *reinterpret_cast<const float4*>(sBeta + ch + 4);
+            uint4 o;
+            o.x = pack_bf16x2(fmaf(fmaf(bf16_lo(v.x), rstd, nmr), g0.x, b0.x),
+                              fmaf(fmaf(bf16_hi(v.x), rstd, nmr), g0.y, b0.y));
+            o.y = pack_bf16x2(fmaf(fmaf(bf16_lo(v.y), rstd, nmr), g0.z, b0.z),
+                              fmaf(fmaf(bf16_hi(v.y), rstd, nmr), g0.w, b0.w));
+            o.z = pack_bf16x2(fmaf(fmaf(bf16_lo(v.z), rstd, nmr), g1.x, b1.x),
+                              fmaf(fmaf(bf16_hi(v.z), rstd, nmr), g1.y, b1.y));
+            o.w = pack_bf16x2(fmaf(fmaf(bf16_lo(v.w), rstd, nmr), g1.z, b1.z),
+                              fmaf(fmaf(bf16_hi(v.w), rstd, nmr), g1.w, b1.w));
+            if (zero_row) o = make_uint4(0u, 0u, 0u, 0u);
+            *p = o;
+        }
+    }
 }
 
 }  // namespace trimul

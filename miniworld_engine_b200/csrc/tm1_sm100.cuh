@@ -8,15 +8,18 @@
 // channel: each epilogue thread owns one channel and a run of consecutive positions, which is
 // exactly a row of the channel-major destination.
 //
-// Persistent kernel, one CTA per SM, 320 threads, 128-position tiles:
-//   warp 0       TMA producer: the four weight matrices once, then z tiles into a 2-stage ring
-//   warp 1       UMMA issuer: per tile, left pair (proj, gate) then right pair, 128x128x16 each,
-//                into four 128-column TMEM accumulators (left pair / right pair alternate, so the
-//                epilogue of one side overlaps the UMMAs of the other)
-//   warps 2..5   LayerNorm: one thread per position normalises its 128 channels in place inside
-//                the swizzled tile (the TMA SWIZZLE_128B image is the UMMA K-major layout), rounds
-//                to bf16 and computes the position's pair-mask bit
-//   warps 6..9   epilogue: TMEM -> p * sigmoid(g) * mask -> bf16 -> swizzled staging -> TMA store
+// Persistent kernel, one CTA per SM, 576 threads, 128-position tiles:
+//   warp 0        TMA producer: the four weight matrices once, then z tiles into a 2-stage ring
+//   warp 1        UMMA issuer: per tile, left pair (proj, gate) then right pair, 128x128x16 each,
+//                 into four 128-column TMEM accumulators
+//   warps 2..9    LayerNorm: two threads per position normalise its 128 channels in place inside
+//                 the swizzled tile (the TMA SWIZZLE_128B image is the UMMA K-major layout) and
+//                 round to bf16; a masked position is written as a zero row, which makes both
+//                 projections of that position exactly zero, so the epilogue needs no mask
+//   warps 10..13  epilogue of the left side, warps 14..17 of the right side:
+//                 TMEM -> p * sigmoid(g) -> bf16 -> swizzled staging -> TMA store
+// All worker warps first halve the weight matrices in shared memory (exact in bf16), so the
+// accumulators hold p/2 and g/2 and p*sigmoid(g) = (p/2)*tanh(g/2) + p/2 is one MUFU + one FMA.
 //
 // A tile is 128 consecutive positions along the index that becomes the contraction's k: for the
 // outgoing direction z row f, columns t0..t0+127; for the incoming direction z column f, rows
@@ -29,20 +32,21 @@ namespace trimul {
 
 constexpr int kT1C = 128;                 // channels
 constexpr int kT1P = 128;                 // positions per tile
-constexpr int kT1Threads = 320;
+constexpr int kT1Threads = 576;
+constexpr int kT1LnThreads = 256;      // warps 2..9
+constexpr int kT1EpiThreads = 128;     // per side
 constexpr int kT1SubTile = 128 * 64 * 2;  // 16 KB: 128 rows x 64 bf16, one swizzle-row wide
 constexpr int kT1WBytes = 8 * kT1SubTile;         // 4 matrices x 2 K halves
 constexpr int kT1XBytes = 2 * kT1SubTile;         // one z tile
 constexpr int kT1XStages = 2;
-constexpr int kT1StagingBytes = 2 * kT1SubTile;   // [128 channels][128 positions] as two 64-wide boxes
+constexpr int kT1StagingBytes = 2 * kT1SubTile;   // one [128 channels][64 positions] store box per side
 constexpr int kT1OffX = kT1WBytes;
 constexpr int kT1OffStaging = kT1OffX + kT1XStages * kT1XBytes;
 constexpr int kT1OffAffine = kT1OffStaging + kT1StagingBytes;      // gamma[128], beta[128] fp32
-constexpr int kT1OffMaskBits = kT1OffAffine + 2 * kT1C * 4;        // 4 slots x 4 words
-constexpr int kT1OffBars = kT1OffMaskBits + 64;
+constexpr int kT1OffBars = kT1OffAffine + 2 * kT1C * 4;
 constexpr int kT1SmemBytes = kT1OffBars + 192;
 constexpr int kT1LnBarrier = 2;
-constexpr int kT1EpiBarrier = 3;
+constexpr int kT1EpiBarrier = 3;       // 3: left side, 4: right side
 constexpr int kStageIdTm1 = 1;
 
 struct Tm1Params {
@@ -77,15 +81,15 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     uint8_t* sOut = smem + kT1OffStaging;
     float* sGamma = reinterpret_cast<float*>(smem + kT1OffAffine);
     float* sBeta = sGamma + kT1C;
-    uint32_t* sMaskBits = reinterpret_cast<uint32_t*>(smem + kT1OffMaskBits);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kT1OffBars);
     uint64_t* w_full = bars;            // weights landed
     uint64_t* x_full = bars + 1;        // [2] z tile landed
-    uint64_t* xn_ready = bars + 3;      // [2] tile normalised (128 arrivals)
+    uint64_t* xn_ready = bars + 3;      // [2] tile normalised (256 arrivals)
     uint64_t* x_empty = bars + 5;       // [2] UMMAs that read the tile retired
     uint64_t* acc_full = bars + 7;      // [2] side's accumulators complete
     uint64_t* acc_empty = bars + 9;     // [2] side's accumulators drained (4 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
+    uint64_t* w_ready = bars + 11;      // weights halved (512 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -93,9 +97,10 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
 
     if (threadIdx.x == 0) {
         mbar_init(w_full, 1);
+        mbar_init(w_ready, kT1LnThreads + 2 * kT1EpiThreads);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&x_full[s], 1);
-            mbar_init(&xn_ready[s], 128);
+            mbar_init(&xn_ready[s], kT1LnThreads);
             mbar_init(&x_empty[s], 1);
             mbar_init(&acc_full[s], 1);
             mbar_init(&acc_empty[s], 4);
@@ -118,6 +123,15 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= 2) {
+        // every worker thread: halve its share of the weights once they have landed
+        if (mbar_wait(w_full, 0, abort_flag, p.status, kStageIdTm1, 150)) {
+            halve_bf16_smem(sW, kT1WBytes, threadIdx.x - 64, kT1LnThreads + 2 * kT1EpiThreads);
+            fence_proxy_async_smem();
+        }
+        mbar_arrive(w_ready);
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -151,7 +165,8 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         // ------------------------------------------------------------------ UMMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(128, kT1P);
-            bool ok = mbar_wait(w_full, 0, abort_flag, p.status, kStageIdTm1, 200);
+            bool ok = mbar_wait(w_ready, 0, abort_flag, p.status, kStageIdTm1, 200);
+            tcgen05_fence_after();
             uint32_t it = 0;
             for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1;
@@ -185,63 +200,16 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             }
         }
         __syncwarp();
-    } else if (warp < 6) {
-        // ------------------------------------------------------------------ LayerNorm + mask bits
-        const int pos = threadIdx.x - 64;                  // 0..127, row of the tile
-        const int lwarp = warp - 2;
-        const float inv_c = 1.0f / (float)kT1C;
+    } else if (warp < 10) {
+        // ------------------------------------------------------------------ LayerNorm (+ mask)
+        const int lt = threadIdx.x - 64;      // 0..255
+        const int pos = lt >> 1;              // row of the tile
+        const int h = lt & 1;
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
             const uint32_t ph = (it >> 1) & 1u;
-            bool ok = mbar_wait(&x_full[s], ph, abort_flag, p.status, kStageIdTm1, 300 + s);
-            ok = named_barrier_all(kT1LnBarrier, 128, ok);
-            if (!ok) break;
-            uint8_t* xrow = sX + s * kT1XBytes + pos * 128;
-            uint4 v[16];
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    v[h * 8 + j] = *reinterpret_cast<const uint4*>(xrow + h * kT1SubTile + ((j ^ (pos & 7)) << 4));
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                sum += bf16_lo(v[i].x) + bf16_hi(v[i].x) + bf16_lo(v[i].y) + bf16_hi(v[i].y);
-                sum += bf16_lo(v[i].z) + bf16_hi(v[i].z) + bf16_lo(v[i].w) + bf16_hi(v[i].w);
-            }
-            const float mean = sum * inv_c;
-            float sq = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float d0 = bf16_lo(w4[e]) - mean, d1 = bf16_hi(w4[e]) - mean;
-                    sq = fmaf(d0, d0, sq);
-                    sq = fmaf(d1, d1, sq);
-                }
-            }
-            const float rstd = rsqrtf(sq * inv_c + p.eps);
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int i = h * 8 + j;
-                    const int ch = h * 64 + j * 8;
-                    const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-                    uint32_t o4[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float y0 = fmaf((bf16_lo(w4[e]) - mean) * rstd, sGamma[ch + 2 * e], sBeta[ch + 2 * e]);
-                        const float y1 =
-                            fmaf((bf16_hi(w4[e]) - mean) * rstd, sGamma[ch + 2 * e + 1], sBeta[ch + 2 * e + 1]);
-                        o4[e] = pack_bf16x2(y0, y1);
-                    }
-                    *reinterpret_cast<uint4*>(xrow + h * kT1SubTile + ((j ^ (pos & 7)) << 4)) =
-                        make_uint4(o4[0], o4[1], o4[2], o4[3]);
-                }
-            // pair-mask bit of this position
+            // pair-mask value of this position (independent of the tile data: do it first)
             bool keep = true;
             if (p.mask_kind != 0) {
                 const int t0 = (tile % p.tiles_per_fixed) * kT1P;
@@ -259,75 +227,74 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                         keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
                 }
             }
-            const uint32_t bits = __ballot_sync(0xffffffffu, keep);
-            if (lane == 0) sMaskBits[(it & 3u) * 4 + lwarp] = bits;
+            bool ok = mbar_wait(&x_full[s], ph, abort_flag, p.status, kStageIdTm1, 300 + s);
+            ok = named_barrier_all(kT1LnBarrier, kT1LnThreads, ok);
+            if (!ok) break;
+            ln_half_row_inplace(sX + s * kT1XBytes, kT1SubTile, pos, h, sGamma, sBeta, p.eps, !keep);
             fence_proxy_async_smem();   // normalised tile -> visible to the UMMA (async proxy)
-            mbar_arrive(&xn_ready[s]);  // release: also publishes the mask words
+            mbar_arrive(&xn_ready[s]);
         }
     } else {
-        // ------------------------------------------------------------------ epilogue
+        // ------------------------------------------------------------------ epilogue, one side per group
+        const int side = (warp - 10) >> 2;
         const int q = warp & 3;
         const int ch = q * 32 + lane;                 // output channel == TMEM lane
-        const bool leader = (threadIdx.x == 192);
+        const bool leader = ((warp - 10) & 3) == 0 && lane == 0;
+        const int bar_id = kT1EpiBarrier + side;
+        uint8_t* stg = sOut + side * kT1SubTile;
+        const CUtensorMap* om = side == 0 ? &tmA : &tmB;
+        const int rc = side == 0 ? p.a_row_chunk : p.b_row_chunk;
+        const int cc = side == 0 ? p.a_col_chunk : p.b_col_chunk;
+        const uint32_t t_p = tmem_base + side * 256 + ((uint32_t)(q * 32) << 16);
         uint32_t it = 0;
-        bool ok = true;
-        for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
+        for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int t0 = (tile % p.tiles_per_fixed) * kT1P;
             const int bf = tile / p.tiles_per_fixed;
             const int f = bf % p.n_fixed;
             const int b = bf / p.n_fixed;
-            for (int side = 0; side < 2; ++side) {
-                ok = mbar_wait(&acc_full[side], it & 1u, abort_flag, p.status, kStageIdTm1, 400 + side);
-                ok = named_barrier_all(kT1EpiBarrier, 128, ok);
-                if (!ok) break;
-                tcgen05_fence_after();
-                uint32_t mbits[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    mbits[i] = p.mask_kind != 0 ? sMaskBits[(it & 3u) * 4 + i] : 0xffffffffu;
-                if (leader) tma_store_wait_read<0>();          // previous side's store has read the staging
-                named_barrier_sync(kT1EpiBarrier, 128);
-                const uint32_t t_p = tmem_base + side * 256 + ((uint32_t)(q * 32) << 16);
+            bool ok = mbar_wait(&acc_full[side], it & 1u, abort_flag, p.status, kStageIdTm1, 400 + side);
+            ok = named_barrier_all(bar_id, kT1EpiThreads, ok);
+            if (!ok) break;
+            tcgen05_fence_after();
 #pragma unroll 1
-                for (int c32 = 0; c32 < 4; ++c32) {
+            for (int half = 0; half < 2; ++half) {
+                if (leader) tma_store_wait_read<0>();      // the previous store has read the staging box
+                named_barrier_sync(bar_id, kT1EpiThreads);
+#pragma unroll 1
+                for (int c = 0; c < 2; ++c) {
+                    const int c32 = half * 2 + c;
                     uint32_t rp[32], rg[32];
                     tmem_ld_32x32(t_p + c32 * 32, rp);
                     tmem_ld_32x32(t_p + 128 + c32 * 32, rg);
                     tmem_ld_wait();
-                    const uint32_t mb = mbits[c32];
-                    uint8_t* base = sOut + (c32 >> 1) * kT1SubTile + ch * 128;
 #pragma unroll
-                    for (int cc = 0; cc < 4; ++cc) {
+                    for (int k = 0; k < 4; ++k) {
                         uint32_t o[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const int i0 = cc * 8 + 2 * e;
-                            float v0 = __uint_as_float(rp[i0]) * sigmoid_fast(__uint_as_float(rg[i0]));
-                            float v1 = __uint_as_float(rp[i0 + 1]) * sigmoid_fast(__uint_as_float(rg[i0 + 1]));
-                            v0 = ((mb >> i0) & 1u) ? v0 : 0.f;
-                            v1 = ((mb >> (i0 + 1)) & 1u) ? v1 : 0.f;
-                            o[e] = pack_bf16x2(v0, v1);
+                            const int i0 = k * 8 + 2 * e;
+                            o[e] = pack_bf16x2(
+                                gate_from_halves(__uint_as_float(rp[i0]), __uint_as_float(rg[i0])),
+                                gate_from_halves(__uint_as_float(rp[i0 + 1]), __uint_as_float(rg[i0 + 1])));
                         }
-                        const int chunk = ((c32 & 1) * 4 + cc) ^ (ch & 7);
-                        *reinterpret_cast<uint4*>(base + (chunk << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                        const int chunk = (c * 4 + k) ^ (ch & 7);
+                        *reinterpret_cast<uint4*>(stg + ch * 128 + (chunk << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                     }
                 }
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[side]);
+                if (half == 1) {
+                    // every TMEM read of this side's accumulators has completed
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[side]);
+                }
                 fence_proxy_async_smem();
-                named_barrier_sync(kT1EpiBarrier, 128);
+                named_barrier_sync(bar_id, kT1EpiThreads);
                 if (leader) {
-                    const CUtensorMap* om = side == 0 ? &tmA : &tmB;
-                    const int rc = side == 0 ? p.a_row_chunk : p.b_row_chunk;
-                    const int cc = side == 0 ? p.a_col_chunk : p.b_col_chunk;
-                    for (int box = 0; box < 2; ++box) {
-                        const int col0 = t0 + box * 64;
-                        if (col0 < p.n_run)
-                            tma_store_4d(om, sOut + box * kT1SubTile, col0 % cc, f % rc, b * kT1C,
-                                         col0 / cc + f / rc);
+                    const int col0 = t0 + half * 64;
+                    if (col0 < p.n_run) {
+                        tma_store_4d(om, stg, col0 % cc, f % rc, b * kT1C, col0 / cc + f / rc);
+                        tma_store_commit();
                     }
-                    tma_store_commit();
                 }
             }
         }

@@ -2,16 +2,20 @@
 // contraction result, the output projection, the output gate from a fresh LayerNorm_in of z
 // (unmasked, reference.py:82-83), optional residual — one pass, row-major bf16 result.
 //
-// Persistent kernel, one CTA per SM, 448 threads, 128-position tiles (z row r, columns j0..j0+127):
+// Persistent kernel, one CTA per SM, 704 threads, 128-position tiles (z row r, columns j0..j0+127):
 //   warp 0        TMA producer: Wg, Wo once; z tiles (and residual tiles) into a 2-stage ring
 //   warp 1        UMMA issuer: gate = x_n . Wg^T and proj = tri_n . Wo^T, 128x128x16 each, into a
 //                 double-buffered pair of 128-column TMEM accumulators (TMEM lane = position)
-//   warps 2..5    LayerNorm_in: one thread per position, in place in the swizzled z tile
-//   warps 6..9    LayerNorm_out: read tri straight from global memory along the contiguous
-//                 position axis of each channel plane (coalesced 4-byte pairs), keep the 64x2
-//                 values in registers, normalise, and write them TRANSPOSED into the K-major
-//                 swizzled operand tile — the channel-major -> row-major turn costs no extra pass
-//   warps 10..13  epilogue: TMEM -> sigmoid(g) * p (+ residual) -> bf16 -> swizzled staging -> TMA store
+//   warps 2..9    LayerNorm_in: two threads per position, in place in the swizzled z tile
+//   warps 10..17  LayerNorm_out, two groups of four warps that take alternate tiles (one group per
+//                 stage): read tri straight from global memory along the contiguous position axis
+//                 of each channel plane (coalesced 4-byte pairs), accumulate the statistics while
+//                 parking the raw values TRANSPOSED in the K-major swizzled operand tile, then
+//                 normalise that tile in place — the channel-major -> row-major turn costs no
+//                 extra pass over memory
+//   warps 18..21  epilogue: TMEM -> sigmoid(g) * p (+ residual) -> bf16 -> swizzled staging -> TMA store
+// The worker warps first halve Wg and Wo in shared memory (exact in bf16) so that
+// p*sigmoid(g) = (p/2)*tanh(g/2) + p/2 costs one MUFU and one FMA.
 #pragma once
 
 #include "ptx_sm100.cuh"
@@ -20,7 +24,11 @@ namespace trimul {
 
 constexpr int kT2C = 128;
 constexpr int kT2P = 128;
-constexpr int kT2Threads = 448;
+constexpr int kT2Threads = 704;
+constexpr int kT2LnThreads = 256;       // warps 2..9
+constexpr int kT2TriThreads = 128;      // per group, warps 10..13 and 14..17
+constexpr int kT2EpiThreads = 128;      // warps 18..21
+constexpr int kT2Workers = kT2LnThreads + 2 * kT2TriThreads + kT2EpiThreads;
 constexpr int kT2SubTile = 128 * 64 * 2;          // 16 KB
 constexpr int kT2WBytes = 4 * kT2SubTile;         // Wg, Wo: 2 K halves each
 constexpr int kT2XBytes = 2 * kT2SubTile;         // z tile  -> x_n operand
@@ -33,8 +41,8 @@ constexpr int kT2OffAffine = kT2OffStaging + kT2StagingBytes;   // gamma_in, bet
 constexpr int kT2OffBars = kT2OffAffine + 4 * kT2C * 4;
 constexpr int kT2SmemBytes = kT2OffBars + 192;
 constexpr int kT2LnBarrier = 2;
-constexpr int kT2TriBarrier = 3;
-constexpr int kT2EpiBarrier = 4;
+constexpr int kT2TriBarrier = 3;        // 3, 4: the two LayerNorm_out groups
+constexpr int kT2EpiBarrier = 5;
 constexpr int kStageIdTm2 = 3;
 
 struct Tm2Params {
@@ -68,14 +76,15 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kT2OffBars);
     uint64_t* w_full = bars;            // weights landed
     uint64_t* x_full = bars + 1;        // [2] z tile landed
-    uint64_t* xn_ready = bars + 3;      // [2] x_n operand ready (128 arrivals)
+    uint64_t* xn_ready = bars + 3;      // [2] x_n operand ready (256 arrivals)
     uint64_t* tn_ready = bars + 5;      // [2] tri_n operand ready (128 arrivals)
     uint64_t* s_empty = bars + 7;       // [2] UMMAs that read the stage retired
     uint64_t* acc_full = bars + 9;      // [2]
     uint64_t* acc_empty = bars + 11;    // [2] (4 arrivals)
     uint64_t* res_full = bars + 13;     // residual tile landed in the staging buffer
     uint64_t* out_free = bars + 14;     // staging buffer released by the epilogue (1 arrival)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 15);
+    uint64_t* w_ready = bars + 15;      // weights halved (all worker threads)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -83,10 +92,11 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
 
     if (threadIdx.x == 0) {
         mbar_init(w_full, 1);
+        mbar_init(w_ready, kT2Workers);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&x_full[s], 1);
-            mbar_init(&xn_ready[s], 128);
-            mbar_init(&tn_ready[s], 128);
+            mbar_init(&xn_ready[s], kT2LnThreads);
+            mbar_init(&tn_ready[s], kT2TriThreads);
             mbar_init(&s_empty[s], 1);
             mbar_init(&acc_full[s], 1);
             mbar_init(&acc_empty[s], 4);
@@ -113,6 +123,14 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= 2) {
+        if (mbar_wait(w_full, 0, abort_flag, p.status, kStageIdTm2, 150)) {
+            halve_bf16_smem(sW, kT2WBytes, threadIdx.x - 64, kT2Workers);
+            fence_proxy_async_smem();
+        }
+        mbar_arrive(w_ready);
+    }
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -150,7 +168,8 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         // ------------------------------------------------------------------ UMMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(kT2P, kT2C);
-            bool ok = mbar_wait(w_full, 0, abort_flag, p.status, kStageIdTm2, 200);
+            bool ok = mbar_wait(w_ready, 0, abort_flag, p.status, kStageIdTm2, 200);
+            tcgen05_fence_after();
             uint32_t it = 0;
             for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1;
@@ -180,78 +199,38 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             }
         }
         __syncwarp();
-    } else if (warp < 6) {
+    } else if (warp < 10) {
         // ------------------------------------------------------------------ LayerNorm_in, in place
-        const int pos = threadIdx.x - 64;
-        const float inv_c = 1.0f / (float)kT2C;
-        const float* sGamma = sAff;
-        const float* sBeta = sAff + kT2C;
+        const int lt = threadIdx.x - 64;
+        const int pos = lt >> 1;
+        const int h = lt & 1;
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
             const uint32_t ph = (it >> 1) & 1u;
             bool ok = mbar_wait(&x_full[s], ph, abort_flag, p.status, kStageIdTm2, 300 + s);
-            ok = named_barrier_all(kT2LnBarrier, 128, ok);
+            ok = named_barrier_all(kT2LnBarrier, kT2LnThreads, ok);
             if (!ok) break;
-            uint8_t* xrow = sStage + s * kT2StageBytes + pos * 128;
-            uint4 v[16];
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                    v[h * 8 + j] = *reinterpret_cast<const uint4*>(xrow + h * kT2SubTile + ((j ^ (pos & 7)) << 4));
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                sum += bf16_lo(v[i].x) + bf16_hi(v[i].x) + bf16_lo(v[i].y) + bf16_hi(v[i].y);
-                sum += bf16_lo(v[i].z) + bf16_hi(v[i].z) + bf16_lo(v[i].w) + bf16_hi(v[i].w);
-            }
-            const float mean = sum * inv_c;
-            float sq = 0.f;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const float d0 = bf16_lo(w4[e]) - mean, d1 = bf16_hi(w4[e]) - mean;
-                    sq = fmaf(d0, d0, sq);
-                    sq = fmaf(d1, d1, sq);
-                }
-            }
-            const float rstd = rsqrtf(sq * inv_c + p.eps_in);
-#pragma unroll
-            for (int h = 0; h < 2; ++h)
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    const int i = h * 8 + j;
-                    const int ch = h * 64 + j * 8;
-                    const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-                    uint32_t o4[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float y0 = fmaf((bf16_lo(w4[e]) - mean) * rstd, sGamma[ch + 2 * e], sBeta[ch + 2 * e]);
-                        const float y1 =
-                            fmaf((bf16_hi(w4[e]) - mean) * rstd, sGamma[ch + 2 * e + 1], sBeta[ch + 2 * e + 1]);
-                        o4[e] = pack_bf16x2(y0, y1);
-                    }
-                    *reinterpret_cast<uint4*>(xrow + h * kT2SubTile + ((j ^ (pos & 7)) << 4)) =
-                        make_uint4(o4[0], o4[1], o4[2], o4[3]);
-                }
+            ln_half_row_inplace(sStage + s * kT2StageBytes, kT2SubTile, pos, h, sAff, sAff + kT2C, p.eps_in, false);
             fence_proxy_async_smem();
             mbar_arrive(&xn_ready[s]);
         }
-    } else if (warp < 10) {
+    } else if (warp < 18) {
         // ------------------------------------------------------------------ LayerNorm_out + transpose
-        // lane l of warp w: positions 2*pp, 2*pp+1 with pp = 16*w + (l & 15); channel half h = l >> 4
-        const int tw = warp - 6;
+        // group g owns stage g and the tiles with (local tile index & 1) == g.
+        // lane l of group-warp w: positions 2*pp, 2*pp+1 with pp = 16*w + (l & 15); channel half h = l >> 4
+        const int g = (warp - 10) >> 2;
+        const int tw = (warp - 10) & 3;
         const int pp = tw * 16 + (lane & 15);
         const int h = lane >> 4;
-        const float inv_c = 1.0f / (float)kT2C;
+        const int bar_id = kT2TriBarrier + g;
         const float* sGamma = sAff + 2 * kT2C + h * 64;
         const float* sBeta = sAff + 3 * kT2C + h * 64;
-        uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
-            const int s = it & 1;
+        uint8_t* trow0 = sStage + g * kT2StageBytes + kT2XBytes + h * kT2SubTile + (2 * pp) * 128;
+        uint8_t* trow1 = trow0 + 128;
+        const uint32_t swz0 = (uint32_t)((2 * pp) & 7), swz1 = (uint32_t)((2 * pp + 1) & 7);
+        uint32_t it = g;
+        for (int tile = blockIdx.x + g * gridDim.x; tile < p.total_tiles; tile += 2 * gridDim.x, it += 2) {
             const uint32_t ph = (it >> 1) & 1u;
             const int j0 = (tile % p.tiles_per_row) * kT2P;
             const int br = tile / p.tiles_per_row;
@@ -262,63 +241,83 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             const uint32_t keep = (v0ok ? 0x0000FFFFu : 0u) | (v1ok ? 0xFFFF0000u : 0u);
             const __nv_bfloat16* src =
                 p.tri + ((long long)b * kT2C + h * 64) * p.tri_plane_stride + (long long)r * p.tri_pitch + j;
-            uint32_t v[64];
+            // the operand tile of this stage is free once the UMMAs of the group's previous tile retired
+            bool ok = mbar_wait(&s_empty[g], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 500 + g);
+            ok = named_barrier_all(bar_id, kT2TriThreads, ok);
+            if (!ok) break;
+            // pass 1: global -> (statistics, raw transposed copy in the operand tile)
+            float sh0 = 0.f, sh1 = 0.f, a0 = 0.f, a1 = 0.f, q0 = 0.f, q1 = 0.f;
+#pragma unroll 1
+            for (int jc = 0; jc < 8; ++jc) {
+                uint32_t v[8];
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                uint32_t x = 0;
-                if (v0ok) x = __ldg(reinterpret_cast<const unsigned int*>(src + (long long)i * p.tri_plane_stride));
-                v[i] = x & keep;
-            }
-            float s0 = 0.f, s1 = 0.f;
+                for (int i = 0; i < 8; ++i) {
+                    uint32_t x = 0;
+                    if (v0ok)
+                        x = __ldg(reinterpret_cast<const unsigned int*>(src + (long long)(jc * 8 + i) * p.tri_plane_stride));
+                    v[i] = x & keep;
+                }
+                if (jc == 0) {
+                    // common shift of the row: channel 0, held by the h = 0 lane of the pair
+                    sh0 = __shfl_sync(0xffffffffu, bf16_lo(v[0]), lane & 15);
+                    sh1 = __shfl_sync(0xffffffffu, bf16_hi(v[0]), lane & 15);
+                }
 #pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                s0 += bf16_lo(v[i]);
-                s1 += bf16_hi(v[i]);
+                for (int i = 0; i < 8; ++i) {
+                    const float d0 = bf16_lo(v[i]) - sh0, d1 = bf16_hi(v[i]) - sh1;
+                    a0 += d0;
+                    q0 = fmaf(d0, d0, q0);
+                    a1 += d1;
+                    q1 = fmaf(d1, d1, q1);
+                }
+                // transpose 8 (position-pair) words into one 16-byte chunk per position
+                uint4 c0, c1;
+                c0.x = __byte_perm(v[0], v[1], 0x5410); c1.x = __byte_perm(v[0], v[1], 0x7632);
+                c0.y = __byte_perm(v[2], v[3], 0x5410); c1.y = __byte_perm(v[2], v[3], 0x7632);
+                c0.z = __byte_perm(v[4], v[5], 0x5410); c1.z = __byte_perm(v[4], v[5], 0x7632);
+                c0.w = __byte_perm(v[6], v[7], 0x5410); c1.w = __byte_perm(v[6], v[7], 0x7632);
+                *reinterpret_cast<uint4*>(trow0 + ((((uint32_t)jc) ^ swz0) << 4)) = c0;
+                *reinterpret_cast<uint4*>(trow1 + ((((uint32_t)jc) ^ swz1) << 4)) = c1;
             }
-            s0 += __shfl_xor_sync(0xffffffffu, s0, 16);
-            s1 += __shfl_xor_sync(0xffffffffu, s1, 16);
-            const float m0 = s0 * inv_c, m1 = s1 * inv_c;
-            float q0 = 0.f, q1 = 0.f;
-#pragma unroll
-            for (int i = 0; i < 64; ++i) {
-                const float d0 = bf16_lo(v[i]) - m0, d1 = bf16_hi(v[i]) - m1;
-                q0 = fmaf(d0, d0, q0);
-                q1 = fmaf(d1, d1, q1);
-            }
+            a0 += __shfl_xor_sync(0xffffffffu, a0, 16);
+            a1 += __shfl_xor_sync(0xffffffffu, a1, 16);
             q0 += __shfl_xor_sync(0xffffffffu, q0, 16);
             q1 += __shfl_xor_sync(0xffffffffu, q1, 16);
-            const float r0 = rsqrtf(q0 * inv_c + p.eps_out), r1 = rsqrtf(q1 * inv_c + p.eps_out);
-
-            // the operand tile of this stage is free once the UMMAs of tile it-2 have retired
-            bool ok = mbar_wait(&s_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 500 + s);
-            ok = named_barrier_all(kT2TriBarrier, 128, ok);
-            if (!ok) break;
-            uint8_t* trow0 = sStage + s * kT2StageBytes + kT2XBytes + h * kT2SubTile + (2 * pp) * 128;
-            uint8_t* trow1 = trow0 + 128;
-#pragma unroll
+            const float inv_c = 1.0f / (float)kT2C;
+            const float m0 = a0 * inv_c, m1 = a1 * inv_c;
+            const float r0 = rsqrtf(fmaxf(fmaf(-m0, m0, q0 * inv_c), 0.f) + p.eps_out);
+            const float r1 = rsqrtf(fmaxf(fmaf(-m1, m1, q1 * inv_c), 0.f) + p.eps_out);
+            const float n0 = -(sh0 + m0) * r0, n1 = -(sh1 + m1) * r1;
+            // pass 2: normalise the parked values in place (each thread re-reads only what it wrote)
+#pragma unroll 1
             for (int jc = 0; jc < 8; ++jc) {
-                uint32_t o0[4], o1[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int i = jc * 8 + 2 * e;
-                    const float g0 = sGamma[i], g1 = sGamma[i + 1], be0 = sBeta[i], be1 = sBeta[i + 1];
-                    o0[e] = pack_bf16x2(fmaf((bf16_lo(v[i]) - m0) * r0, g0, be0),
-                                        fmaf((bf16_lo(v[i + 1]) - m0) * r0, g1, be1));
-                    o1[e] = pack_bf16x2(fmaf((bf16_hi(v[i]) - m1) * r1, g0, be0),
-                                        fmaf((bf16_hi(v[i + 1]) - m1) * r1, g1, be1));
-                }
-                *reinterpret_cast<uint4*>(trow0 + ((jc ^ ((2 * pp) & 7)) << 4)) = make_uint4(o0[0], o0[1], o0[2], o0[3]);
-                *reinterpret_cast<uint4*>(trow1 + ((jc ^ ((2 * pp + 1) & 7)) << 4)) =
-                    make_uint4(o1[0], o1[1], o1[2], o1[3]);
+                const float4 g0 = *reinterpret_cast<const float4*>(sGamma + jc * 8);
+                const float4 g1 = *reinterpret_cast<const float4*>(sGamma + jc * 8 + 4);
+                const float4 b0 = *reinterpret_cast<const float4*>(sBeta + jc * 8);
+                const float4 b1 = *reinterpret_cast<const float4*>(sBeta + jc * 8 + 4);
+                uint4* p0 = reinterpret_cast<uint4*>(trow0 + ((((uint32_t)jc) ^ swz0) << 4));
+                uint4* p1 = reinterpret_cast<uint4*>(trow1 + ((((uint32_t)jc) ^ swz1) << 4));
+                const uint4 x0 = *p0, x1 = *p1;
+                uint4 o0, o1;
+                o0.x = pack_bf16x2(fmaf(fmaf(bf16_lo(x0.x), r0, n0), g0.x, b0.x), fmaf(fmaf(bf16_hi(x0.x), r0, n0), g0.y, b0.y));
+                o0.y = pack_bf16x2(fmaf(fmaf(bf16_lo(x0.y), r0, n0), g0.z, b0.z), fmaf(fmaf(bf16_hi(x0.y), r0, n0), g0.w, b0.w));
+                o0.z = pack_bf16x2(fmaf(fmaf(bf16_lo(x0.z), r0, n0), g1.x, b1.x), fmaf(fmaf(bf16_hi(x0.z), r0, n0), g1.y, b1.y));
+                o0.w = pack_bf16x2(fmaf(fmaf(bf16_lo(x0.w), r0, n0), g1.z, b1.z), fmaf(fmaf(bf16_hi(x0.w), r0, n0), g1.w, b1.w));
+                o1.x = pack_bf16x2(fmaf(fmaf(bf16_lo(x1.x), r1, n1), g0.x, b0.x), fmaf(fmaf(bf16_hi(x1.x), r1, n1), g0.y, b0.y));
+                o1.y = pack_bf16x2(fmaf(fmaf(bf16_lo(x1.y), r1, n1), g0.z, b0.z), fmaf(fmaf(bf16_hi(x1.y), r1, n1), g0.w, b0.w));
+                o1.z = pack_bf16x2(fmaf(fmaf(bf16_lo(x1.z), r1, n1), g1.x, b1.x), fmaf(fmaf(bf16_hi(x1.z), r1, n1), g1.y, b1.y));
+                o1.w = pack_bf16x2(fmaf(fmaf(bf16_lo(x1.w), r1, n1), g1.z, b1.z), fmaf(fmaf(bf16_hi(x1.w), r1, n1), g1.w, b1.w));
+                *p0 = o0;
+                *p1 = o1;
             }
             fence_proxy_async_smem();
-            mbar_arrive(&tn_ready[s]);
+            mbar_arrive(&tn_ready[g]);
         }
     } else {
         // ------------------------------------------------------------------ epilogue
         const int q = warp & 3;
         const int row = q * 32 + lane;                 // position inside the tile == TMEM lane
-        const bool leader = (threadIdx.x == 320);
+        const bool leader = (warp == 18 && lane == 0);
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
@@ -329,24 +328,24 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             const int b = br / p.rows;
             bool ok = mbar_wait(&acc_full[s], ph, abort_flag, p.status, kStageIdTm2, 400 + s);
             if (ok && p.has_residual) ok = mbar_wait(res_full, it & 1u, abort_flag, p.status, kStageIdTm2, 410);
-            ok = named_barrier_all(kT2EpiBarrier, 128, ok);
+            ok = named_barrier_all(kT2EpiBarrier, kT2EpiThreads, ok);
             if (!ok) break;
             tcgen05_fence_after();
             if (!p.has_residual) {
                 if (leader) tma_store_wait_read<0>();      // previous tile's store has read the staging
-                named_barrier_sync(kT2EpiBarrier, 128);
+                named_barrier_sync(kT2EpiBarrier, kT2EpiThreads);
             }
             const uint32_t t_g = tmem_base + s * 256 + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-            for (int c32 = 0; c32 < 4; ++c32) {
-                uint32_t rg[32], rp[32];
-                tmem_ld_32x32(t_g + c32 * 32, rg);
-                tmem_ld_32x32(t_g + 128 + c32 * 32, rp);
+            for (int c16 = 0; c16 < 8; ++c16) {
+                uint32_t rg[16], rp[16];
+                tmem_ld_32x16(t_g + c16 * 16, rg);
+                tmem_ld_32x16(t_g + 128 + c16 * 16, rp);
                 tmem_ld_wait();
-                uint8_t* base = sOut + (c32 >> 1) * kT2SubTile + row * 128;
+                uint8_t* base = sOut + (c16 >> 2) * kT2SubTile + row * 128;
 #pragma unroll
-                for (int cc = 0; cc < 4; ++cc) {
-                    const int chunk = ((c32 & 1) * 4 + cc) ^ (row & 7);
+                for (int cc = 0; cc < 2; ++cc) {
+                    const int chunk = ((c16 & 3) * 2 + cc) ^ (row & 7);
                     uint4* dst = reinterpret_cast<uint4*>(base + (chunk << 4));
                     uint32_t res[4] = {0u, 0u, 0u, 0u};
                     if (p.has_residual) {
@@ -357,8 +356,8 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int i0 = cc * 8 + 2 * e;
-                        float v0 = __uint_as_float(rp[i0]) * sigmoid_fast(__uint_as_float(rg[i0]));
-                        float v1 = __uint_as_float(rp[i0 + 1]) * sigmoid_fast(__uint_as_float(rg[i0 + 1]));
+                        float v0 = gate_from_halves(__uint_as_float(rp[i0]), __uint_as_float(rg[i0]));
+                        float v1 = gate_from_halves(__uint_as_float(rp[i0 + 1]), __uint_as_float(rg[i0 + 1]));
                         if (p.has_residual) {
                             // the reference rounds the block output to bf16 before `out + pair`
                             v0 = __bfloat162float(__float2bfloat16_rn(v0)) + bf16_lo(res[e]);
@@ -373,7 +372,7 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[s]);
             fence_proxy_async_smem();
-            named_barrier_sync(kT2EpiBarrier, 128);
+            named_barrier_sync(kT2EpiBarrier, kT2EpiThreads);
             if (leader) {
                 tma_store_4d(&tmOut, sOut, 0, j0, r, b);
                 tma_store_4d(&tmOut, sOut + kT2SubTile, 64, j0, r, b);
