@@ -163,9 +163,9 @@ contract_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
             const int col_d = (rem % p.tiles_n) * kCtBN;
             const uint32_t acc = tile_it & 1u;
             const uint32_t acc_ph = (tile_it >> 1) & 1u;
-            bool ok = mbar_wait(&acc_full[acc], acc_ph, abort_flag, p.status, kStageIdContract, 400 + acc);
-            ok = named_barrier_all(kCtEpiBarrier, 128, ok);
-            if (!ok) break;
+            if (!group_wait(&acc_full[acc], acc_ph, leader, kCtEpiBarrier, 128, abort_flag, p.status, kStageIdContract,
+                            400 + acc))
+                break;
             tcgen05_fence_after();
             const uint32_t t_acc = tmem_base + acc * kCtBN + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1

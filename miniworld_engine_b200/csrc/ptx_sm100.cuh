@@ -78,16 +78,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  : "memory");
 }
 
+// One poll.  The suspend-time hint lets the hardware park the thread (no issue slots used)
+// until the phase completes or the hint (nanoseconds) runs out, whichever comes first.
+constexpr uint32_t kTryWaitHintNs = 20000u;
+
 __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t done;
     asm volatile(
         "{\n\t"
         ".reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(done)
-        : "r"(smem_u32(bar)), "r"(parity)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(kTryWaitHintNs)
         : "memory");
     return done;
 }
@@ -143,6 +147,16 @@ __device__ __forceinline__ bool named_barrier_all(int id, int nthreads, bool ok)
         : "r"((uint32_t)ok), "r"(id), "r"(nthreads)
         : "memory");
     return r != 0;
+}
+
+// Wait of a whole warp group on one mbarrier phase: ONE thread polls (bounded), the others park
+// at the group's named barrier, which costs them no issue slots; the barrier also hands the
+// poller's verdict and its view of memory to every thread of the group.
+__device__ __forceinline__ bool group_wait(uint64_t* bar, uint32_t parity, bool poller, int bar_id, int nthreads,
+                                           volatile int* abort_flag, int32_t* status, int stage, int detail) {
+    bool ok = true;
+    if (poller) ok = mbar_wait(bar, parity, abort_flag, status, stage, detail);
+    return named_barrier_all(bar_id, nthreads, ok);
 }
 
 // ---------------------------------------------------------------------------------------

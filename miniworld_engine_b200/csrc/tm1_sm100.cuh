@@ -227,9 +227,9 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                         keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
                 }
             }
-            bool ok = mbar_wait(&x_full[s], ph, abort_flag, p.status, kStageIdTm1, 300 + s);
-            ok = named_barrier_all(kT1LnBarrier, kT1LnThreads, ok);
-            if (!ok) break;
+            if (!group_wait(&x_full[s], ph, lt == 0, kT1LnBarrier, kT1LnThreads, abort_flag, p.status,
+                            kStageIdTm1, 300 + s))
+                break;
             ln_half_row_inplace(sX + s * kT1XBytes, kT1SubTile, pos, h, sGamma, sBeta, p.eps, !keep);
             fence_proxy_async_smem();   // normalised tile -> visible to the UMMA (async proxy)
             mbar_arrive(&xn_ready[s]);
@@ -252,9 +252,9 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             const int bf = tile / p.tiles_per_fixed;
             const int f = bf % p.n_fixed;
             const int b = bf / p.n_fixed;
-            bool ok = mbar_wait(&acc_full[side], it & 1u, abort_flag, p.status, kStageIdTm1, 400 + side);
-            ok = named_barrier_all(bar_id, kT1EpiThreads, ok);
-            if (!ok) break;
+            if (!group_wait(&acc_full[side], it & 1u, leader, bar_id, kT1EpiThreads, abort_flag, p.status,
+                            kStageIdTm1, 400 + side))
+                break;
             tcgen05_fence_after();
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {

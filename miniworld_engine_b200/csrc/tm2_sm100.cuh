@@ -208,9 +208,9 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
             const uint32_t ph = (it >> 1) & 1u;
-            bool ok = mbar_wait(&x_full[s], ph, abort_flag, p.status, kStageIdTm2, 300 + s);
-            ok = named_barrier_all(kT2LnBarrier, kT2LnThreads, ok);
-            if (!ok) break;
+            if (!group_wait(&x_full[s], ph, lt == 0, kT2LnBarrier, kT2LnThreads, abort_flag, p.status,
+                            kStageIdTm2, 300 + s))
+                break;
             ln_half_row_inplace(sStage + s * kT2StageBytes, kT2SubTile, pos, h, sAff, sAff + kT2C, p.eps_in, false);
             fence_proxy_async_smem();
             mbar_arrive(&xn_ready[s]);
@@ -242,9 +242,9 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             const __nv_bfloat16* src =
                 p.tri + ((long long)b * kT2C + h * 64) * p.tri_plane_stride + (long long)r * p.tri_pitch + j;
             // the operand tile of this stage is free once the UMMAs of the group's previous tile retired
-            bool ok = mbar_wait(&s_empty[g], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 500 + g);
-            ok = named_barrier_all(bar_id, kT2TriThreads, ok);
-            if (!ok) break;
+            if (!group_wait(&s_empty[g], ph ^ 1u, tw == 0 && lane == 0, bar_id, kT2TriThreads, abort_flag, p.status,
+                            kStageIdTm2, 500 + g))
+                break;
             // pass 1: global -> (statistics, raw transposed copy in the operand tile)
             float sh0 = 0.f, sh1 = 0.f, a0 = 0.f, a1 = 0.f, q0 = 0.f, q1 = 0.f;
 #pragma unroll 1
@@ -326,10 +326,12 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             const int br = tile / p.tiles_per_row;
             const int r = br % p.rows;
             const int b = br / p.rows;
-            bool ok = mbar_wait(&acc_full[s], ph, abort_flag, p.status, kStageIdTm2, 400 + s);
-            if (ok && p.has_residual) ok = mbar_wait(res_full, it & 1u, abort_flag, p.status, kStageIdTm2, 410);
-            ok = named_barrier_all(kT2EpiBarrier, kT2EpiThreads, ok);
-            if (!ok) break;
+            bool ok = true;
+            if (leader) {
+                ok = mbar_wait(&acc_full[s], ph, abort_flag, p.status, kStageIdTm2, 400 + s);
+                if (ok && p.has_residual) ok = mbar_wait(res_full, it & 1u, abort_flag, p.status, kStageIdTm2, 410);
+            }
+            if (!named_barrier_all(kT2EpiBarrier, kT2EpiThreads, ok)) break;
             tcgen05_fence_after();
             if (!p.has_residual) {
                 if (leader) tma_store_wait_read<0>();      // previous tile's store has read the staging
