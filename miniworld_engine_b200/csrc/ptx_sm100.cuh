@@ -30,6 +30,25 @@ __device__ __forceinline__ void report_timeout(int32_t* status, int stage, int d
 }
 
 // ---------------------------------------------------------------------------------------
+// optional timeline tracing (compiled in only with -DTRIMUL_TRACE): block 0 stamps the global
+// nanosecond timer for local tile indices 8..23 into a device array that a debug entry point
+// copies out.  Layout: [role][tile - 8][event], 8 roles x 16 tiles x 4 events.
+// ---------------------------------------------------------------------------------------
+#ifdef TRIMUL_TRACE
+__device__ unsigned long long g_trace[8 * 16 * 4];
+#define TRIMUL_STAMP(role, it, ev)                                                             \
+    do {                                                                                       \
+        if (blockIdx.x == 0 && (it) >= 8u && (it) < 24u) {                                     \
+            unsigned long long t_;                                                             \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                             \
+            g_trace[((role) * 16 + ((it) - 8u)) * 4 + (ev)] = t_;                              \
+        }                                                                                      \
+    } while (0)
+#else
+#define TRIMUL_STAMP(role, it, ev) do { } while (0)
+#endif
+
+// ---------------------------------------------------------------------------------------
 // shared-memory addresses, fences
 // ---------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -255,6 +274,24 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t smem_addr) {
     return d;
 }
 
+// Shared-memory operand descriptor for an MN-major bf16 tile with the 128-byte swizzle: each
+// row is one K index and holds 64 consecutive M (or N) elements (128 bytes) — what a TMA load
+// with SWIZZLE_128B and a 64-element inner box writes when the contiguous tensor dimension is
+// the operand's M/N dimension.  Eight K rows form a 1024-byte group.
+//   leading byte offset = distance between consecutive 64-element blocks along M/N
+//   stride  byte offset = distance between consecutive 8-row groups along K
+// One UMMA (K = 16) consumes two 8-row groups, so stepping K by 16 adds 2 * sbo_bytes.
+__device__ __forceinline__ uint64_t umma_smem_desc_mn_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                            uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
 // Advancing a K-major SWIZZLE_128B descriptor by one UMMA K step (16 bf16 = 32 bytes) inside the
 // 128-byte row: add 32 >> 4 to the start-address field.
 constexpr uint64_t kDescKStep = 32u >> 4;
@@ -262,8 +299,9 @@ constexpr uint64_t kDescKStep = 32u >> 4;
 // Instruction descriptor for kind::f16 with bf16 A/B (both K-major), fp32 accumulate.
 //   [4,6) D format: 1 = f32    [7,10) A format: 1 = bf16    [10,13) B format: 1 = bf16
 //   [15] A major: 0 = K        [16] B major: 0 = K          [17,23) N >> 3        [24,29) M >> 4
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+__host__ __device__ constexpr uint32_t umma_idesc_bf16(int M, int N, int a_mn_major = 0, int b_mn_major = 0) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
 }
 
 // D[tmem] (+)= A[smem] * B[smem]^T, issued by ONE thread.

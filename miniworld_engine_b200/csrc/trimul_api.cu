@@ -301,7 +301,7 @@ int run_plain_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri,
 
 int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
                  const void* residual, cudaStream_t st, int32_t* status) {
-    CUtensorMap tmZ, tmWg, tmWo, tmOut, tmRes;
+    CUtensorMap tmZ, tmWg, tmWo, tmOut, tmRes, tmTri;
     const uint64_t dims[4] = {128, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
     const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
     const uint32_t box[4] = {64, 128, 1, 1};
@@ -319,8 +319,7 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     const int64_t total = (int64_t)d->B * d->rows * p.tiles_per_row;
     if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
     p.total_tiles = (int)total;
-    p.tri = static_cast<const __nv_bfloat16*>(tri->base);
-    p.tri_pitch = tri->pitch; p.tri_plane_stride = tri->plane_stride;
+    if (!encode_planes(&tmTri, *tri, d->B * 128, 64, 1, 128)) return TRIMUL_E_CUDA;
     p.gamma_in = w->ln_in_weight; p.beta_in = w->ln_in_bias;
     p.gamma_out = w->ln_out_weight; p.beta_out = w->ln_out_bias;
     p.eps_in = d->eps_in; p.eps_out = d->eps_out;
@@ -328,7 +327,7 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     p.status = status;
     if (!ensure_smem(tm2_sm100_kernel, kT2SmemBytes)) return TRIMUL_E_CUDA;
     const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-    tm2_sm100_kernel<<<grid, kT2Threads, kT2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmRes, p);
+    tm2_sm100_kernel<<<grid, kT2Threads, kT2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmRes, tmTri, p);
     return launch_status();
 }
 
@@ -340,6 +339,11 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // exported entry points
 // =========================================================================================
 extern "C" {
+
+#ifdef TRIMUL_TRACE
+// debug builds only: copy the timeline stamps of the last kernel that wrote them to the host
+int trimul_b200_debug_trace(void* host, size_t n) { return (int)cudaMemcpyFromSymbol(host, trimul::g_trace, n); }
+#endif
 
 int trimul_b200_abi_version(void) { return TRIMUL_B200_ABI_VERSION; }
 
@@ -430,7 +434,8 @@ int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes*
     if ((rc = check_planes(tri, desc->rows, desc->N)) != TRIMUL_OK) return rc;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (desc->dtype == TRIMUL_DTYPE_FP32) return run_plain_tm2<float>(desc, z, tri, w, out, residual, st);
-    const bool plain_layout = tri->row_chunk >= tri->rows && tri->col_chunk >= tri->cols;
+    const bool plain_layout = tri->row_chunk >= tri->rows && tri->col_chunk >= tri->cols &&
+                              (reinterpret_cast<uintptr_t>(tri->base) & 127u) == 0;
     if (tensor_core_path(desc) && plain_layout) return run_fast_tm2(desc, z, tri, w, out, residual, st, status);
     return run_plain_tm2<__nv_bfloat16>(desc, z, tri, w, out, residual, st);
 }

@@ -1,0 +1,159 @@
+"""Row-sharded TriangleMultiplication block over the GPUs of one node.
+
+Rank r owns rows ``I_r = [r*R, (r+1)*R)`` (``R = N / world``) of the pair tensor and of the
+output.  Stage 1 (LayerNorm + gated projections) and stage 3 (output stage) are row-local; the
+contraction couples rows, so there is exactly one exchange step per block, between stage 1 and
+stage 2, done with NCCL collectives whose result the contraction kernel reads in place
+(chunk-major operand planes, ``trimul_planes`` in ``include/trimul_b200.h``):
+
+* outgoing  ``out[i,j] = sum_k a[i,k] b[j,k]``, i in I_r: ``a[I_r]`` is local, every row of ``b`` is
+  needed -> **all-gather b** (row chunks: chunk s = rows I_s, produced by rank s);
+* incoming  ``out[i,j] = sum_k a[k,i] b[k,j]``, i in I_r: the local z rows are the k in I_r, so
+  rank r produces the k-slices ``a'[:, K_r]`` and ``b'[:, K_r]`` of the transposed operands
+  (``a'[i][k] = a[k,i]``).  It needs ``a'[I_r][all k]`` -> **all-to-all of a'** (rank s sends its
+  rows I_r), and ``b'[all j][all k]`` -> **all-gather b'**; both arrive as k-chunked planes.
+
+No k-sum is split across ranks, so the result equals the single-GPU result.  The reference has
+no distributed code at all; its single-GPU module is the behaviour to match.
+
+The exchange logic is independent of the device: ``exchange()`` works on flat tensors with any
+``torch.distributed`` backend, which is how the CPU tests drive it with gloo.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from . import stages as S
+
+__all__ = ["ShardPlan", "exchange", "trimul_forward_sharded"]
+
+
+@dataclass
+class ShardPlan:
+    """Sizes and operand-plane layouts of one rank's share of a block call."""
+
+    B: int
+    N: int
+    c: int
+    world: int
+    rank: int
+    outgoing: bool
+
+    def __post_init__(self):
+        if self.N % self.world != 0:
+            raise ValueError(f"N={self.N} must be divisible by the number of ranks ({self.world})")
+        if not 0 <= self.rank < self.world:
+            raise ValueError(f"rank {self.rank} outside [0, {self.world})")
+        self.R = self.N // self.world
+        self.row0 = self.rank * self.R
+        self.planes = self.B * self.c
+
+    # ---- buffer sizes in elements -------------------------------------------------------
+    @property
+    def pitch_full(self) -> int:      # row pitch of a plane whose rows hold all N columns
+        return S.round_up(self.N, 8)
+
+    @property
+    def pitch_slab(self) -> int:      # row pitch of a plane whose rows hold R columns
+        return S.round_up(self.R, 8)
+
+    def slab_elems(self) -> int:
+        """Elements of one rank's contribution to a gathered operand."""
+        if self.outgoing:
+            return self.planes * self.R * self.pitch_full          # [P][R rows][N cols]
+        return self.planes * self.N * self.pitch_slab              # [P][N rows][R cols]
+
+    def a2a_chunk_elems(self) -> int:
+        """Elements one rank sends to one peer in the incoming all-to-all: [P][R rows][R cols]."""
+        return self.planes * self.R * self.pitch_slab
+
+    # ---- plane descriptions -------------------------------------------------------------
+    def tm1_outputs(self, a_buf: torch.Tensor, b_buf: torch.Tensor):
+        """Where stage 1 writes.  Outgoing: ``a`` plain [P][R][N]; ``b`` straight into this rank's
+        chunk of the gathered buffer.  Incoming: ``a'`` [P][N][R] row-chunked by destination rank
+        (chunk r = rows I_r, contiguous, ready to be sent); ``b'`` into this rank's chunk."""
+        P, R, N = self.planes, self.R, self.N
+        if self.outgoing:
+            a = S.PlaneSpec(a_buf, P, R, N, self.pitch_full, R * self.pitch_full)
+            chunk = b_buf[self.rank * self.slab_elems():(self.rank + 1) * self.slab_elems()]
+            b = S.PlaneSpec(chunk, P, R, N, self.pitch_full, R * self.pitch_full)
+        else:
+            a = S.PlaneSpec(a_buf, P, N, R, self.pitch_slab, R * self.pitch_slab,
+                            chunk_stride=self.a2a_chunk_elems() if self.world > 1 else 0,
+                            row_chunk=R if self.world > 1 else None)
+            chunk = b_buf[self.rank * self.slab_elems():(self.rank + 1) * self.slab_elems()]
+            b = S.PlaneSpec(chunk, P, N, R, self.pitch_slab, N * self.pitch_slab)
+        return a, b
+
+    def contract_operands(self, a_buf: torch.Tensor, b_buf: torch.Tensor):
+        """How stage 2 reads the exchanged buffers.  ``a_buf`` is the local ``a`` (outgoing) or
+        the all-to-all result (incoming); ``b_buf`` is the gathered operand."""
+        P, R, N, W = self.planes, self.R, self.N, self.world
+        if self.outgoing:
+            a = S.PlaneSpec(a_buf, P, R, N, self.pitch_full, R * self.pitch_full)
+            b = S.PlaneSpec(b_buf, P, N, N, self.pitch_full, R * self.pitch_full,
+                            chunk_stride=self.slab_elems() if W > 1 else 0, row_chunk=R if W > 1 else None)
+        else:
+            a = S.PlaneSpec(a_buf, P, R, N, self.pitch_slab, R * self.pitch_slab,
+                            chunk_stride=self.a2a_chunk_elems() if W > 1 else 0, col_chunk=R if W > 1 else None)
+            b = S.PlaneSpec(b_buf, P, N, N, self.pitch_slab, N * self.pitch_slab,
+                            chunk_stride=self.slab_elems() if W > 1 else 0, col_chunk=R if W > 1 else None)
+        return a, b
+
+    def tri_spec(self, tri_buf: torch.Tensor) -> S.PlaneSpec:
+        return S.PlaneSpec(tri_buf, self.planes, self.R, self.N, self.pitch_full, self.R * self.pitch_full)
+
+    def alloc(self, dtype: torch.dtype, device):
+        """(a_send, a_recv, b_gathered, tri) buffers; ``a_recv`` is ``a_send`` when nothing moves."""
+        a_elems = self.planes * self.R * self.pitch_full if self.outgoing else self.world * self.a2a_chunk_elems()
+        a_send = torch.empty(a_elems, dtype=dtype, device=device)
+        a_recv = a_send if (self.outgoing or self.world == 1) else torch.empty_like(a_send)
+        b_full = torch.empty(self.world * self.slab_elems(), dtype=dtype, device=device)
+        tri = torch.empty(self.planes * self.R * self.pitch_full, dtype=dtype, device=device)
+        return a_send, a_recv, b_full, tri
+
+
+def exchange(plan: ShardPlan, a_send: torch.Tensor, a_recv: torch.Tensor, b_full: torch.Tensor, group=None):
+    """The block's one exchange step.  ``b_full`` already holds this rank's chunk at offset
+    ``rank * slab_elems``; after the call it holds every rank's chunk.  For the incoming
+    direction ``a_send`` ([world][P][R][pitch], chunk r destined for rank r) is exchanged into
+    ``a_recv`` (chunk s received from rank s).  Returns the async work handles (already waited
+    for backends without stream semantics)."""
+    if plan.world == 1:
+        return []
+    n = plan.slab_elems()
+    mine = b_full[plan.rank * n:(plan.rank + 1) * n]
+    works = [dist.all_gather_into_tensor(b_full, mine, group=group, async_op=True)]
+    if not plan.outgoing:
+        works.append(dist.all_to_all_single(a_recv, a_send, group=group, async_op=True))
+    for w in works:
+        w.wait()
+    return works
+
+
+@torch.no_grad()
+def trimul_forward_sharded(z_slab: torch.Tensor, mask: torch.Tensor | None, weights: dict, *, outgoing: bool,
+                           N: int | None = None, group=None, eps_in: float = 1e-5, eps_out: float = 1e-5,
+                           residual: torch.Tensor | None = None, buffers=None) -> torch.Tensor:
+    """One block call on this rank's ``[B, R, N, c]`` slab of the pair tensor; returns the matching
+    output slab.  ``mask`` is the FULL ``[B, N]`` token mask (or ``[B, N, N]`` pair mask), identical
+    on every rank.  ``weights`` is the keyword dict of ``stages.tm1`` / ``stages.tm2``."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    B, R, Nz, c = z_slab.shape
+    N = Nz if N is None else N
+    plan = ShardPlan(B, N, c, world, rank, outgoing)
+    if R != plan.R:
+        raise ValueError(f"slab has {R} rows, expected N/world = {plan.R}")
+    a_send, a_recv, b_full, tri_buf = buffers if buffers is not None else plan.alloc(z_slab.dtype, z_slab.device)
+    a_w, b_w = plan.tm1_outputs(a_send, b_full)
+    S.tm1(z_slab, mask, weights, a_w, b_w, outgoing=outgoing, row0=plan.row0, eps=eps_in)
+    exchange(plan, a_send, a_recv, b_full, group)
+    a_r, b_r = plan.contract_operands(a_recv, b_full)
+    tri = plan.tri_spec(tri_buf)
+    S.contract(a_r, b_r, tri)
+    return S.tm2(z_slab, tri, weights, residual=residual, row0=plan.row0, eps_in=eps_in, eps_out=eps_out)

@@ -17,7 +17,7 @@ import torch
 from . import _lib
 from .functional import _dtype_code, _mask_bytes, _require_cuda, _status_words, _weights_struct
 
-__all__ = ["PlaneSpec", "alloc_planes", "planes_to_dense", "tm1", "contract", "tm2", "round_up"]
+__all__ = ["PlaneSpec", "alloc_planes", "planes_to_dense", "dense_to_planes", "tm1", "contract", "tm2", "round_up"]
 
 
 def round_up(v: int, m: int) -> int:
@@ -72,13 +72,29 @@ def planes_to_dense(spec: PlaneSpec) -> torch.Tensor:
     """Gather the logical ``[planes, rows, cols]`` array out of a PlaneSpec (test helper)."""
     if spec.row_chunk is not None and spec.row_chunk < spec.rows:
         n = -(-spec.rows // spec.row_chunk)
-        v = spec.buf.view(n, spec.planes, spec.row_chunk, spec.pitch)[..., :spec.cols]
+        v = spec.buf[: n * spec.chunk_stride].view(n, spec.planes, spec.row_chunk, spec.pitch)[..., :spec.cols]
         return v.permute(1, 0, 2, 3).reshape(spec.planes, n * spec.row_chunk, spec.cols)[:, :spec.rows]
     if spec.col_chunk is not None and spec.col_chunk < spec.cols:
         n = -(-spec.cols // spec.col_chunk)
-        v = spec.buf.view(n, spec.planes, spec.rows, spec.pitch)[..., :spec.col_chunk]
+        v = spec.buf[: n * spec.chunk_stride].view(n, spec.planes, spec.rows, spec.pitch)[..., :spec.col_chunk]
         return v.permute(1, 2, 0, 3).reshape(spec.planes, spec.rows, n * spec.col_chunk)[..., :spec.cols]
     return spec.buf[: spec.planes * spec.plane_stride].view(spec.planes, spec.rows, spec.pitch)[..., :spec.cols]
+
+
+def dense_to_planes(spec: PlaneSpec, dense: torch.Tensor) -> None:
+    """Scatter a logical ``[planes, rows, cols]`` array into a PlaneSpec (test helper; chunked
+    layouts need rows / cols to be whole multiples of the chunk size)."""
+    P = spec.planes
+    if spec.row_chunk is not None and spec.row_chunk < spec.rows:
+        n = spec.rows // spec.row_chunk
+        v = spec.buf[: n * spec.chunk_stride].view(n, P, spec.row_chunk, spec.pitch)[..., :spec.cols]
+        v.permute(1, 0, 2, 3).copy_(dense.reshape(P, n, spec.row_chunk, spec.cols))
+    elif spec.col_chunk is not None and spec.col_chunk < spec.cols:
+        n = spec.cols // spec.col_chunk
+        v = spec.buf[: n * spec.chunk_stride].view(n, P, spec.rows, spec.pitch)[..., :spec.col_chunk]
+        v.permute(1, 2, 0, 3).copy_(dense.reshape(P, spec.rows, n, spec.col_chunk))
+    else:
+        spec.buf[: P * spec.plane_stride].view(P, spec.rows, spec.pitch)[..., :spec.cols].copy_(dense)
 
 
 def _desc(x, N, outgoing, mask_kind, eps_in, eps_out, plain, row0):

@@ -1,0 +1,96 @@
+"""Host logic of the row-sharded block on CPU: the exchange step runs over real
+``torch.distributed`` collectives (gloo, world size 2 and 4, one process per rank), stage 1 and
+stage 2 are played by the CPU oracle writing/reading the very operand-plane layouts the GPU
+kernels use.  Every rank must end up with exactly the rows of the contraction it owns."""
+
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from miniworld_engine_b200 import stages as S
+from miniworld_engine_b200.sharded import ShardPlan, exchange
+from oracle import trimul_oracle as O
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, N, c, B, outgoing, q):
+    try:
+        os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+        dist.init_process_group("gloo", rank=rank, world_size=world)
+        torch.set_num_threads(1)
+        w = O.make_weights(c, 0, affine="random")
+        z = O.make_input(B, N, c, 1)
+        m = O.make_token_mask(B, N, "tail3")
+        full = O.trimul_stages(z, m, w, outgoing)          # every rank recomputes the truth
+        plan = ShardPlan(B, N, c, world, rank, outgoing)
+        R, r0 = plan.R, plan.row0
+        # stage 1 on the local rows only.  left/right[b, r, s, ch] for z rows r in I_rank.
+        left, right = full["left"][:, r0:r0 + R], full["right"][:, r0:r0 + R]
+        if outgoing:   # plane element (r, k) = position (r0 + r, k)
+            a_d = left.permute(0, 3, 1, 2).reshape(plan.planes, R, N)
+            b_d = right.permute(0, 3, 1, 2).reshape(plan.planes, R, N)
+        else:          # transposed: plane element (i, k) = position (r0 + k, i)
+            a_d = left.permute(0, 3, 2, 1).reshape(plan.planes, N, R)
+            b_d = right.permute(0, 3, 2, 1).reshape(plan.planes, N, R)
+        a_send, a_recv, b_full, _ = plan.alloc(torch.float32, "cpu")
+        for t in (a_send, a_recv, b_full):
+            t.fill_(float("nan"))                          # nothing may be read that was not written
+        a_w, b_w = plan.tm1_outputs(a_send, b_full)
+        S.dense_to_planes(a_w, a_d.contiguous())
+        S.dense_to_planes(b_w, b_d.contiguous())
+        exchange(plan, a_send, a_recv, b_full)
+        a_r, b_r = plan.contract_operands(a_recv, b_full)
+        A, Bm = S.planes_to_dense(a_r), S.planes_to_dense(b_r)
+        assert not torch.isnan(A).any() and not torch.isnan(Bm).any()
+        tri = torch.einsum("pik,pjk->pij", A, Bm)          # [P][R][N]: rows I_rank of the contraction
+        want = full["tri"][:, r0:r0 + R].permute(0, 3, 1, 2).reshape(plan.planes, R, N)
+        err = O.rel_rms(tri, want)
+        dist.barrier()
+        dist.destroy_process_group()
+        q.put((rank, err, None))
+    except Exception as e:  # pragma: no cover
+        q.put((rank, None, repr(e)))
+
+
+@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
+def test_exchange_gives_each_rank_its_rows(world, outgoing):
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, 16, 8, 2, outgoing, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=180) for _ in procs]
+    for p in procs:
+        p.join(timeout=60)
+    for rank, err, exc in results:
+        assert exc is None, f"rank {rank}: {exc}"
+        assert err < 1e-6, f"rank {rank}: rel-RMS {err}"
+
+
+def test_plan_rejects_bad_partitions():
+    with pytest.raises(ValueError):
+        ShardPlan(1, 10, 8, 4, 0, True)
+    with pytest.raises(ValueError):
+        ShardPlan(1, 8, 8, 2, 2, True)
+
+
+def test_single_rank_plan_is_the_plain_layout():
+    plan = ShardPlan(1, 24, 8, 1, 0, False)
+    a_send, a_recv, b_full, tri = plan.alloc(torch.float32, "cpu")
+    assert a_recv is a_send
+    a_w, b_w = plan.tm1_outputs(a_send, b_full)
+    a_r, b_r = plan.contract_operands(a_recv, b_full)
+    for spec in (a_w, b_w, a_r, b_r):
+        assert spec.row_chunk is None and spec.col_chunk is None and spec.chunk_stride == 0
+    assert (a_r.rows, a_r.cols, b_r.rows, b_r.cols) == (24, 24, 24, 24)
