@@ -366,6 +366,44 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
     return fmaf(0.5f, t, 0.5f);
 }
 
+// ---------------------------------------------------------------------------------------
+// Packed fp32 pairs (sm_100 executes add/mul/fma on two fp32 lanes per instruction).  A pair
+// lives in a 64-bit register; the helpers below are what the LayerNorm and gate code is
+// written in, which halves its arithmetic instruction count.
+// ---------------------------------------------------------------------------------------
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 f2_pack(float lo, float hi) {
+    f32x2 r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+    return r;
+}
+__device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+// bf16x2 word -> (lo, hi) as fp32 pair, and back with round-to-nearest-even
+__device__ __forceinline__ f32x2 f2_from_bf16x2(uint32_t w) { return f2_pack(bf16_lo(w), bf16_hi(w)); }
+__device__ __forceinline__ uint32_t f2_to_bf16x2(f32x2 v) {
+    float lo, hi;
+    f2_unpack(v, lo, hi);
+    return pack_bf16x2(lo, hi);
+}
+__device__ __forceinline__ float f2_hsum(f32x2 v) {
+    float lo, hi;
+    f2_unpack(v, lo, hi);
+    return lo + hi;
+}
+
 __device__ __forceinline__ float tanh_fast(float x) {
     float t;
     asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(x));
@@ -376,6 +414,11 @@ __device__ __forceinline__ float tanh_fast(float x) {
 // The kernels halve the weight matrices once in shared memory (exact in bf16), so the
 // accumulators already hold hp and hg and the gate costs one MUFU and one FMA per value.
 __device__ __forceinline__ float gate_from_halves(float hp, float hg) { return fmaf(hp, tanh_fast(hg), hp); }
+// two gates at once, result rounded to a bf16x2 word
+__device__ __forceinline__ uint32_t gate2_bf16(float hp0, float hg0, float hp1, float hg1) {
+    const f32x2 hp = f2_pack(hp0, hp1);
+    return f2_to_bf16x2(f2_fma(hp, f2_pack(tanh_fast(hg0), tanh_fast(hg1)), hp));
+}
 
 // Multiply `nbytes` of bf16 data in shared memory by 0.5 in place (exact: only the exponent
 // changes), work split over `nthreads` cooperating threads with rank `tid`.
@@ -406,10 +449,11 @@ __device__ __forceinline__ void ln_half_row_inplace(uint8_t* tile, int sub_bytes
     const uint32_t swz = (uint32_t)(row & 7);
     uint8_t* rowp = tile + row * 128;
     // NOTE: no early exit for masked rows — the shuffles below need every lane of the warp.
-    // shift: channel 0 lives in chunk 0 of sub-tile 0, owned by the even lane of the pair
+    // shift: channel 0 lives in chunk 0 of sub-tile 0
     const uint32_t first = *reinterpret_cast<const uint32_t*>(rowp + (swz << 4));
     const float shift = bf16_lo(first);
-    float s1 = 0.f, s2 = 0.f;
+    const f32x2 nshift = f2_pack(-shift, -shift);
+    f32x2 s1 = 0ull, s2 = 0ull;   // (even, odd) element lanes; 0ull is the pair (+0.f, +0.f)
 #pragma unroll 1
     for (int s = 0; s < 2; ++s) {
 #pragma unroll
@@ -418,20 +462,20 @@ __device__ __forceinline__ void ln_half_row_inplace(uint8_t* tile, int sub_bytes
             const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float d0 = bf16_lo(w4[e]) - shift, d1 = bf16_hi(w4[e]) - shift;
-                s1 += d0;
-                s2 = fmaf(d0, d0, s2);
-                s1 += d1;
-                s2 = fmaf(d1, d1, s2);
+                const f32x2 d = f2_add(f2_from_bf16x2(w4[e]), nshift);
+                s1 = f2_add(s1, d);
+                s2 = f2_fma(d, d, s2);
             }
         }
     }
-    s1 += __shfl_xor_sync(0xffffffffu, s1, 1);
-    s2 += __shfl_xor_sync(0xffffffffu, s2, 1);
-    const float m1 = s1 * (1.0f / 128.0f);
-    const float var = fmaxf(fmaf(-m1, m1, s2 * (1.0f / 128.0f)), 0.f);
+    float t1 = f2_hsum(s1), t2 = f2_hsum(s2);
+    t1 += __shfl_xor_sync(0xffffffffu, t1, 1);
+    t2 += __shfl_xor_sync(0xffffffffu, t2, 1);
+    const float m1 = t1 * (1.0f / 128.0f);
+    const float var = fmaxf(fmaf(-m1, m1, t2 * (1.0f / 128.0f)), 0.f);
     const float rstd = rsqrtf(var + eps);
     const float nmr = -(shift + m1) * rstd;   // y = x*rstd + nmr
+    const f32x2 rstd2 = f2_pack(rstd, rstd), nmr2 = f2_pack(nmr, nmr);
 #pragma unroll 1
     for (int s = 0; s < 2; ++s) {
 #pragma unroll
@@ -445,14 +489,10 @@ __device__ __forceinline__ void ln_half_row_inplace(uint8_t* tile, int sub_bytes
             const float4 b0 = *reinterpret_cast<const float4*>(sBeta + ch);
             const float4 b1 = *reinterpret_cast<const float4*>(sBeta + ch + 4);
             uint4 o;
-            o.x = pack_bf16x2(fmaf(fmaf(bf16_lo(v.x), rstd, nmr), g0.x, b0.x),
-                              fmaf(fmaf(bf16_hi(v.x), rstd, nmr), g0.y, b0.y));
-            o.y = pack_bf16x2(fmaf(fmaf(bf16_lo(v.y), rstd, nmr), g0.z, b0.z),
-                              fmaf(fmaf(bf16_hi(v.y), rstd, nmr), g0.w, b0.w));
-            o.z = pack_bf16x2(fmaf(fmaf(bf16_lo(v.z), rstd, nmr), g1.x, b1.x),
-                              fmaf(fmaf(bf16_hi(v.z), rstd, nmr), g1.y, b1.y));
-            o.w = pack_bf16x2(fmaf(fmaf(bf16_lo(v.w), rstd, nmr), g1.z, b1.z),
-                              fmaf(fmaf(bf16_hi(v.w), rstd, nmr), g1.w, b1.w));
+            o.x = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v.x), rstd2, nmr2), f2_pack(g0.x, g0.y), f2_pack(b0.x, b0.y)));
+            o.y = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v.y), rstd2, nmr2), f2_pack(g0.z, g0.w), f2_pack(b0.z, b0.w)));
+            o.z = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v.z), rstd2, nmr2), f2_pack(g1.x, g1.y), f2_pack(b1.x, b1.y)));
+            o.w = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v.w), rstd2, nmr2), f2_pack(g1.z, g1.w), f2_pack(b1.z, b1.w)));
             if (zero_row) o = make_uint4(0u, 0u, 0u, 0u);
             *p = o;
         }

@@ -256,36 +256,47 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                             kStageIdTm1, 400 + side))
                 break;
             tcgen05_fence_after();
+            // 16 positions at a time; the TMEM loads of the next 16 are in flight while the current
+            // 16 are gated, rounded and written to the staging box (64 positions per TMA store)
+            auto emit16 = [&](int c16, const uint32_t (&rp)[16], const uint32_t (&rg)[16]) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i0 = k * 8 + 2 * e;
+                        o[e] = gate2_bf16(__uint_as_float(rp[i0]), __uint_as_float(rg[i0]),
+                                          __uint_as_float(rp[i0 + 1]), __uint_as_float(rg[i0 + 1]));
+                    }
+                    const int chunk = ((c16 & 3) * 2 + k) ^ (ch & 7);
+                    *reinterpret_cast<uint4*>(stg + ch * 128 + (chunk << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            };
+            uint32_t rpA[16], rgA[16], rpB[16], rgB[16];
+            tmem_ld_32x16(t_p, rpA);
+            tmem_ld_32x16(t_p + 128, rgA);
 #pragma unroll 1
             for (int half = 0; half < 2; ++half) {
                 if (leader) tma_store_wait_read<0>();      // the previous store has read the staging box
                 named_barrier_sync(bar_id, kT1EpiThreads);
 #pragma unroll 1
-                for (int c = 0; c < 2; ++c) {
-                    const int c32 = half * 2 + c;
-                    uint32_t rp[32], rg[32];
-                    tmem_ld_32x32(t_p + c32 * 32, rp);
-                    tmem_ld_32x32(t_p + 128 + c32 * 32, rg);
+                for (int cp = 0; cp < 2; ++cp) {
+                    const int c16 = half * 4 + cp * 2;
                     tmem_ld_wait();
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        uint32_t o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int i0 = k * 8 + 2 * e;
-                            o[e] = pack_bf16x2(
-                                gate_from_halves(__uint_as_float(rp[i0]), __uint_as_float(rg[i0])),
-                                gate_from_halves(__uint_as_float(rp[i0 + 1]), __uint_as_float(rg[i0 + 1])));
-                        }
-                        const int chunk = (c * 4 + k) ^ (ch & 7);
-                        *reinterpret_cast<uint4*>(stg + ch * 128 + (chunk << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    tmem_ld_32x16(t_p + (c16 + 1) * 16, rpB);
+                    tmem_ld_32x16(t_p + 128 + (c16 + 1) * 16, rgB);
+                    emit16(c16, rpA, rgA);
+                    tmem_ld_wait();
+                    if (c16 + 2 < 8) {
+                        tmem_ld_32x16(t_p + (c16 + 2) * 16, rpA);
+                        tmem_ld_32x16(t_p + 128 + (c16 + 2) * 16, rgA);
+                    } else {
+                        // every TMEM read of this side's accumulators has completed: hand them back early
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[side]);
                     }
-                }
-                if (half == 1) {
-                    // every TMEM read of this side's accumulators has completed
-                    tcgen05_fence_before();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&acc_empty[side]);
+                    emit16(c16 + 1, rpB, rgB);
                 }
                 fence_proxy_async_smem();
                 named_barrier_sync(bar_id, kT1EpiThreads);

@@ -261,16 +261,23 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             const uint32_t shx = __shfl_sync(0xffffffffu, v[0].x, lane & 24);
             const uint32_t shy = __shfl_sync(0xffffffffu, v[0].y, lane & 24);
             const float shift[4] = {bf16_lo(shx), bf16_hi(shx), bf16_lo(shy), bf16_hi(shy)};
-            float s1[4] = {0.f, 0.f, 0.f, 0.f}, s2[4] = {0.f, 0.f, 0.f, 0.f};
+            // positions (0,1) and (2,3) of the quad as packed fp32 pairs
+            const f32x2 nsh01 = f2_pack(-shift[0], -shift[1]), nsh23 = f2_pack(-shift[2], -shift[3]);
+            f32x2 a01 = 0ull, a23 = 0ull, q01 = 0ull, q23 = 0ull;
 #pragma unroll
             for (int m = 0; m < 16; ++m) {
-                const float d0 = bf16_lo(v[m].x) - shift[0], d1 = bf16_hi(v[m].x) - shift[1];
-                const float d2 = bf16_lo(v[m].y) - shift[2], d3 = bf16_hi(v[m].y) - shift[3];
-                s1[0] += d0; s2[0] = fmaf(d0, d0, s2[0]);
-                s1[1] += d1; s2[1] = fmaf(d1, d1, s2[1]);
-                s1[2] += d2; s2[2] = fmaf(d2, d2, s2[2]);
-                s1[3] += d3; s2[3] = fmaf(d3, d3, s2[3]);
+                const f32x2 d01 = f2_add(f2_from_bf16x2(v[m].x), nsh01);
+                const f32x2 d23 = f2_add(f2_from_bf16x2(v[m].y), nsh23);
+                a01 = f2_add(a01, d01);
+                q01 = f2_fma(d01, d01, q01);
+                a23 = f2_add(a23, d23);
+                q23 = f2_fma(d23, d23, q23);
             }
+            float s1[4], s2[4];
+            f2_unpack(a01, s1[0], s1[1]);
+            f2_unpack(a23, s1[2], s1[3]);
+            f2_unpack(q01, s2[0], s2[1]);
+            f2_unpack(q23, s2[2], s2[3]);
             // combine the 8 row slots of a quad (lanes that differ in bits 0..2)
 #pragma unroll
             for (int o = 1; o < 8; o <<= 1) {
@@ -287,15 +294,16 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                 rstd[e] = rsqrtf(fmaxf(fmaf(-m1, m1, s2[e] * inv_c), 0.f) + p.eps_out);
                 nmr[e] = -(shift[e] + m1) * rstd[e];
             }
+            const f32x2 r01 = f2_pack(rstd[0], rstd[1]), r23 = f2_pack(rstd[2], rstd[3]);
+            const f32x2 n01 = f2_pack(nmr[0], nmr[1]), n23 = f2_pack(nmr[2], nmr[3]);
             if (tw == 0 && lane == 0) TRIMUL_STAMP(3, it, 1);
 #pragma unroll
             for (int m = 0; m < 16; ++m) {
                 const float ga = sGamma[rs + 8 * m], be = sBeta[rs + 8 * m];
+                const f32x2 ga2 = f2_pack(ga, ga), be2 = f2_pack(be, be);
                 uint2 o;
-                o.x = pack_bf16x2(fmaf(fmaf(bf16_lo(v[m].x), rstd[0], nmr[0]), ga, be),
-                                  fmaf(fmaf(bf16_hi(v[m].x), rstd[1], nmr[1]), ga, be));
-                o.y = pack_bf16x2(fmaf(fmaf(bf16_lo(v[m].y), rstd[2], nmr[2]), ga, be),
-                                  fmaf(fmaf(bf16_hi(v[m].y), rstd[3], nmr[3]), ga, be));
+                o.x = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[m].x), r01, n01), ga2, be2));
+                o.y = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[m].y), r23, n23), ga2, be2));
                 *reinterpret_cast<uint2*>(base + m * 1024) = o;
             }
             fence_proxy_async_smem();
@@ -323,17 +331,18 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             if (!named_barrier_all(kT2EpiBarrier, kT2EpiThreads, ok)) break;
             tcgen05_fence_after();
             if (leader) TRIMUL_STAMP(5, it, 0);
+            // The staging tile is two 64-channel boxes, each stored (and committed) on its own.  Before
+            // a box is rewritten only ITS previous store must have finished reading it; the other
+            // box's store, issued later, may still be in flight (at most one group pending).
             if (!p.has_residual) {
-                if (leader) tma_store_wait_read<0>();      // previous tile's store has read the staging
+                if (leader) tma_store_wait_read<1>();
                 named_barrier_sync(kT2EpiBarrier, kT2EpiThreads);
             }
+            if (leader) TRIMUL_STAMP(5, it, 2);
             const uint32_t t_g = tmem_base + s * 256 + ((uint32_t)(q * 32) << 16);
-#pragma unroll 1
-            for (int c16 = 0; c16 < 8; ++c16) {
-                uint32_t rg[16], rp[16];
-                tmem_ld_32x16(t_g + c16 * 16, rg);
-                tmem_ld_32x16(t_g + 128 + c16 * 16, rp);
-                tmem_ld_wait();
+            // 16 output channels at a time; the TMEM loads of the next 16 are in flight while the
+            // current 16 are gated, rounded and written to the staging tile
+            auto emit16 = [&](int c16, const uint32_t (&rg)[16], const uint32_t (&rp)[16]) {
                 uint8_t* base = sOut + (c16 >> 2) * kT2SubTile + row * 128;
 #pragma unroll
                 for (int cc = 0; cc < 2; ++cc) {
@@ -348,26 +357,52 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int i0 = cc * 8 + 2 * e;
-                        float v0 = gate_from_halves(__uint_as_float(rp[i0]), __uint_as_float(rg[i0]));
-                        float v1 = gate_from_halves(__uint_as_float(rp[i0 + 1]), __uint_as_float(rg[i0 + 1]));
-                        if (p.has_residual) {
-                            // the reference rounds the block output to bf16 before `out + pair`
-                            v0 = __bfloat162float(__float2bfloat16_rn(v0)) + bf16_lo(res[e]);
-                            v1 = __bfloat162float(__float2bfloat16_rn(v1)) + bf16_hi(res[e]);
-                        }
-                        o[e] = pack_bf16x2(v0, v1);
+                        o[e] = gate2_bf16(__uint_as_float(rp[i0]), __uint_as_float(rg[i0]),
+                                          __uint_as_float(rp[i0 + 1]), __uint_as_float(rg[i0 + 1]));
+                        if (p.has_residual)   // the reference rounds the block output to bf16 before `out + pair`
+                            o[e] = f2_to_bf16x2(f2_add(f2_from_bf16x2(o[e]), f2_from_bf16x2(res[e])));
                     }
                     *dst = make_uint4(o[0], o[1], o[2], o[3]);
                 }
+            };
+            uint32_t rgA[16], rpA[16], rgB[16], rpB[16];
+            tmem_ld_32x16(t_g, rgA);
+            tmem_ld_32x16(t_g + 128, rpA);
+#pragma unroll 1
+            for (int c16 = 0; c16 < 8; c16 += 2) {
+                if (c16 == 4) {
+                    if (leader) TRIMUL_STAMP(5, it, 3);
+                    // box 0 (channels 0..63) is complete: store it, then make sure box 1 is free
+                    fence_proxy_async_smem();
+                    named_barrier_sync(kT2EpiBarrier, kT2EpiThreads);
+                    if (leader && !p.has_residual) {
+                        tma_store_4d(&tmOut, sOut, 0, j0, r, b);
+                        tma_store_commit();
+                        tma_store_wait_read<1>();
+                    }
+                    named_barrier_sync(kT2EpiBarrier, kT2EpiThreads);
+                }
+                tmem_ld_wait();
+                tmem_ld_32x16(t_g + (c16 + 1) * 16, rgB);
+                tmem_ld_32x16(t_g + 128 + (c16 + 1) * 16, rpB);
+                emit16(c16, rgA, rpA);
+                tmem_ld_wait();
+                if (c16 + 2 < 8) {
+                    tmem_ld_32x16(t_g + (c16 + 2) * 16, rgA);
+                    tmem_ld_32x16(t_g + 128 + (c16 + 2) * 16, rpA);
+                } else {
+                    // every TMEM read of this accumulator pair has completed: hand it back early
+                    tcgen05_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&acc_empty[s]);
+                }
+                emit16(c16 + 1, rgB, rpB);
             }
-            tcgen05_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&acc_empty[s]);
             if (leader) TRIMUL_STAMP(5, it, 1);
             fence_proxy_async_smem();
             named_barrier_sync(kT2EpiBarrier, kT2EpiThreads);
             if (leader) {
-                tma_store_4d(&tmOut, sOut, 0, j0, r, b);
+                if (p.has_residual) tma_store_4d(&tmOut, sOut, 0, j0, r, b);
                 tma_store_4d(&tmOut, sOut + kT2SubTile, 64, j0, r, b);
                 tma_store_commit();
                 if (p.has_residual) {

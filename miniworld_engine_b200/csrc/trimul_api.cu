@@ -51,7 +51,7 @@ EncodeTiledFn get_encode_fn() {
 
 // bf16 tensor of up to 4 dimensions, innermost first; strides in ELEMENTS for dims 1..3.
 bool encode_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* dims, const uint64_t* strides_elems,
-                 const uint32_t* box, bool swizzle128) {
+                 const uint32_t* box, int swizzle_bytes) {
     EncodeTiledFn fn = get_encode_fn();
     if (fn == nullptr) return false;
     cuuint64_t gdim[4];
@@ -66,14 +66,16 @@ bool encode_bf16(CUtensorMap* map, const void* base, int rank, const uint64_t* d
     for (int i = 0; i + 1 < rank; ++i) gstride[i] = strides_elems[i] * 2;
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), gdim, gstride,
                     bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    swizzle128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                    swizzle_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                    : swizzle_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                          : CU_TENSOR_MAP_SWIZZLE_NONE,
                     CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS;
 }
 
 // Channel-major planes as a 4-D tensor (col, row-in-chunk, plane, chunk) with the given box.
 bool encode_planes(CUtensorMap* map, const trimul_planes& pl, int planes, uint32_t box_cols, uint32_t box_rows,
-                   uint32_t box_planes) {
+                   uint32_t box_planes, int swizzle_bytes = 128) {
     const bool row_chunked = pl.row_chunk < pl.rows;
     const bool col_chunked = pl.col_chunk < pl.cols;
     const uint64_t chunks = row_chunked ? (uint64_t)((pl.rows + pl.row_chunk - 1) / pl.row_chunk)
@@ -84,7 +86,7 @@ bool encode_planes(CUtensorMap* map, const trimul_planes& pl, int planes, uint32
     const uint64_t chunk_stride = chunks > 1 ? (uint64_t)pl.chunk_stride : (uint64_t)pl.plane_stride * planes;
     const uint64_t strides[3] = {(uint64_t)pl.pitch, (uint64_t)pl.plane_stride, chunk_stride};
     const uint32_t box[4] = {box_cols, box_rows, box_planes, 1};
-    return encode_bf16(map, pl.base, 4, dims, strides, box, true);
+    return encode_bf16(map, pl.base, 4, dims, strides, box, swizzle_bytes);
 }
 
 int sm_count() {
@@ -196,16 +198,17 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
         const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
         const uint32_t box_out[4] = {64, 128, 1, 1};
         const uint32_t box_in[4] = {64, 1, 128, 1};
-        if (!encode_bf16(&tmZ, z, 4, dims, strides, inc ? box_in : box_out, true)) return TRIMUL_E_CUDA;
+        if (!encode_bf16(&tmZ, z, 4, dims, strides, inc ? box_in : box_out, 128)) return TRIMUL_E_CUDA;
     }
     const void* ws[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
     for (int m = 0; m < 4; ++m) {
         const uint64_t dims[2] = {128, 128};
         const uint64_t strides[1] = {128};
         const uint32_t box[2] = {64, 128};
-        if (!encode_bf16(&tmW[m], ws[m], 2, dims, strides, box, true)) return TRIMUL_E_CUDA;
+        if (!encode_bf16(&tmW[m], ws[m], 2, dims, strides, box, 128)) return TRIMUL_E_CUDA;
     }
     const int planes = d->B * 128;
+    // stores of a and b: 64 positions x 128 planes per box
     if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
     if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
 
@@ -305,14 +308,14 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     const uint64_t dims[4] = {128, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
     const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
     const uint32_t box[4] = {64, 128, 1, 1};
-    if (!encode_bf16(&tmZ, z, 4, dims, strides, box, true)) return TRIMUL_E_CUDA;
-    if (!encode_bf16(&tmOut, out, 4, dims, strides, box, true)) return TRIMUL_E_CUDA;
-    if (!encode_bf16(&tmRes, residual ? residual : z, 4, dims, strides, box, true)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmZ, z, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmOut, out, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmRes, residual ? residual : z, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
     const uint64_t wdims[2] = {128, 128};
     const uint64_t wstrides[1] = {128};
     const uint32_t wbox[2] = {64, 128};
-    if (!encode_bf16(&tmWg, w->w_gate, 2, wdims, wstrides, wbox, true)) return TRIMUL_E_CUDA;
-    if (!encode_bf16(&tmWo, w->w_out, 2, wdims, wstrides, wbox, true)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmWg, w->w_gate, 2, wdims, wstrides, wbox, 128)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmWo, w->w_out, 2, wdims, wstrides, wbox, 128)) return TRIMUL_E_CUDA;
     Tm2Params p;
     p.B = d->B; p.rows = d->rows; p.N = d->N;
     p.tiles_per_row = (d->N + kT2P - 1) / kT2P;
