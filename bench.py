@@ -17,7 +17,7 @@ ONE JSON line:
   launches of the timed region) against the measured peak in MEASURED_PEAKS.json;
 * ``cpu_baseline``: the CPU oracle (a port of the reference's reference.py) timed on this
   box's host cores on a bounded sample (rank 0, N=1 only);
-* ``clocks``: SM clock and throttle reasons sampled with nvidia-smi during the timed region.
+* ``clocks``: SM clock and throttle reasons sampled through NVML during the timed region.
 
 Workloads
   n768_outgoing (default)  bf16, B=1, N=768, c=128, all-ones token mask: the configuration
@@ -26,6 +26,8 @@ Workloads
                            collective in the data path: independent pair tensors).
   n384_outgoing            BASELINE config 2.
   n768_incoming_pad77      BASELINE config 3.
+  n2048_pair_sharded       BASELINE config 5: outgoing then incoming block at N=2048, output rows
+                           sharded over the ranks (strong scaling, NCCL exchange per block).
 
 ``--impl reference`` times the CPU oracle on the host cores instead (rank 0 only).
 """
@@ -49,6 +51,13 @@ WORKLOADS = {
     "n768_incoming_pad77": (1, 768, 128, False, "tail77"),
     "n1024_outgoing": (1, 1024, 128, True, "ones"),
     "n2048_outgoing": (1, 2048, 128, True, "rand5"),
+}
+# Outgoing block then incoming block on its output, output rows sharded over the ranks
+# (BASELINE config 5 at N=2048; the smaller ones are quick checks).  Strong scaling.
+PAIR_WORKLOADS = {
+    "n2048_pair_sharded": (1, 2048, 128, "rand5"),
+    "n1024_pair_sharded": (1, 1024, 128, "rand5"),
+    "n512_pair_sharded": (1, 512, 128, "rand5"),
 }
 METRIC = "trimul_block_tflops"
 UNIT = "TFLOP/s"
@@ -166,26 +175,40 @@ def run_reference(args):
         return
     import torch
     from oracle import trimul_oracle as O
-    B, N, c, outgoing, mask_kind = WORKLOADS[args.workload]
+    pair = args.workload in PAIR_WORKLOADS
+    if pair:
+        B, N, c, mask_kind = PAIR_WORKLOADS[args.workload]
+        outgoing = True
+    else:
+        B, N, c, outgoing, mask_kind = WORKLOADS[args.workload]
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     w = O.make_weights(c, 0).to(torch.bfloat16)
+    w2 = O.make_weights(c, 3).to(torch.bfloat16)
     z = O.make_input(B, N, c, 1).to(torch.bfloat16)
     m = O.make_token_mask(B, N, mask_kind)
+
+    def call():
+        y = O.trimul_forward(z, m, w, outgoing)
+        if pair:
+            y = O.trimul_forward(y, m, w2, False)
+        return y
+
     for _ in range(args.warmup):
-        O.trimul_forward(z, m, w, outgoing)
+        call()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        O.trimul_forward(z, m, w, outgoing)
+        call()
     dt = time.perf_counter() - t0
-    val = block_flops(B, N, c) * args.steps / dt / 1e12
+    val = (2.0 if pair else 1.0) * block_flops(B, N, c) * args.steps / dt / 1e12
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "calls_per_s": args.steps / dt, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded randn, all on the host)",
         "config": {"workload": args.workload, "B": B, "N": N, "c": c,
-                   "direction": "outgoing" if outgoing else "incoming", "mask": mask_kind},
+                   "direction": "outgoing then incoming" if pair else ("outgoing" if outgoing else "incoming"),
+                   "mask": mask_kind},
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{args.steps} full block calls per run (each step = one call of the workload)"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -332,14 +355,154 @@ def run_b200(args):
         dist.destroy_process_group()
 
 
+def run_sharded_pair(args):
+    """Outgoing block followed by an incoming block on its output, rows sharded over the ranks
+    with one NCCL exchange per block (all-gather b; incoming also all-to-all a)."""
+    import torch
+    import torch.distributed as dist
+    from oracle import trimul_oracle as O
+    from miniworld_engine_b200 import read_status, stages as S
+    from miniworld_engine_b200.sharded import ChannelShardPlan, ShardPlan, exchange
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the b200 arm has no CPU path (use --impl reference)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    B, N, c, mask_kind = PAIR_WORKLOADS[args.workload]
+    R = N // world
+    g = torch.Generator().manual_seed(1)
+    z_slab = None
+    for r in range(world):      # the same seeded tensor on every rank, generated slab by slab
+        blk = torch.randn(B, R, N, c, generator=g)
+        if r == rank:
+            z_slab = blk.to(torch.bfloat16).to(dev)
+    del blk
+    m = O.make_token_mask(B, N, mask_kind).to(dev)
+
+    def wdict(seed):
+        w = O.make_weights(c, seed).to(torch.bfloat16)
+        return dict(ln_in_w=w.ln_pair_weight.to(dev), ln_in_b=w.ln_pair_bias.to(dev), w_left=w.to_left.to(dev),
+                    w_left_gate=w.to_left_gate.to(dev), w_right=w.to_right.to(dev),
+                    w_right_gate=w.to_right_gate.to(dev), ln_out_w=w.ln_out_weight.to(dev),
+                    ln_out_b=w.ln_out_bias.to(dev), w_gate=w.to_gate.to(dev), w_out=w.to_out.to(dev))
+
+    w_out, w_in = wdict(0), wdict(3)
+    channels = args.shard_mode == "channels"
+    Plan = ChannelShardPlan if channels else ShardPlan
+    plans = {True: Plan(B, N, c, world, rank, True), False: Plan(B, N, c, world, rank, False)}
+    bufs = {k: p.alloc(torch.bfloat16, dev) for k, p in plans.items()}
+
+    def mark(ev):
+        ev.append(torch.cuda.Event(enable_timing=True))
+        ev[-1].record()
+
+    def block_channels(x, wd, outgoing, ev):
+        p, bf = plans[outgoing], bufs[outgoing]
+        a_w, b_w = p.tm1_outputs(bf)
+        S.tm1(x, m, wd, a_w, b_w, outgoing=outgoing, row0=p.row0)
+        mark(ev)
+        p.exchange_in(bf)
+        a_r, b_r, tri_w = p.contract_operands(bf)
+        S.contract(a_r, b_r, tri_w)
+        mark(ev)            # "exchange" slot = all-to-all in + contraction start; see stage names below
+        p.exchange_out(bf)
+        mark(ev)
+        y = S.tm2(x, p.tri_spec(bf), wd, row0=p.row0)
+        mark(ev)
+        return y
+
+    def block(x, wd, outgoing, ev):
+        if channels:
+            return block_channels(x, wd, outgoing, ev)
+        p = plans[outgoing]
+        a_send, a_recv, b_full, tri_buf = bufs[outgoing]
+        a_w, b_w = p.tm1_outputs(a_send, b_full)
+        S.tm1(x, m, wd, a_w, b_w, outgoing=outgoing, row0=p.row0)
+        ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+        exchange(p, a_send, a_recv, b_full)
+        ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+        a_r, b_r = p.contract_operands(a_recv, b_full)
+        tri = p.tri_spec(tri_buf)
+        S.contract(a_r, b_r, tri)
+        ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+        y = S.tm2(x, tri, wd, row0=p.row0)
+        ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+        return y
+
+    def step():
+        ev = [torch.cuda.Event(enable_timing=True)]
+        ev[0].record()
+        y1 = block(z_slab, w_out, True, ev)
+        y2 = block(y1, w_in, False, ev)
+        return ev, y2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(dev)
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
+    all_ev = [step()[0] for _ in range(args.steps)]
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    total_ms = all_ev[0][0].elapsed_time(all_ev[-1][-1])
+    names = ["tm1", "a2a_in+contract", "a2a_out", "tm2"] if channels else ["tm1", "exchange", "contract", "tm2"]
+    stage_ms = [sum(e[i].elapsed_time(e[i + 1]) + e[i + 4].elapsed_time(e[i + 5]) for e in all_ev) / args.steps
+                for i in range(4)]
+    if read_status(dev)[0] != 0:
+        raise SystemExit(f"bench.py: device status {read_status(dev)}: timing is invalid")
+    t = torch.tensor([total_ms] + stage_ms, device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, *stage_ms = [float(v) for v in t.cpu()]
+    if rank == 0:
+        peaks = measured_peaks()
+        flops = 2.0 * block_flops(B, N, c)
+        ms = total_ms / args.steps
+        gathered = (world - 1) * R * N * c * 2 * B          # bytes each rank receives per all-gather
+        a2a = (world - 1) * R * R * c * 2 * B               # and in the incoming all-to-all
+        if channels:                                        # three all-to-alls of (world-1)/world slabs
+            gathered, a2a = 3 * (world - 1) * R * N * (c // world) * 2 * B, 0
+        line = {
+            "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
+            "calls_per_s": 2e3 / ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (seeded randn pair tensor and weights)",
+            "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["bf16_tflops"],
+            "config": {"workload": args.workload, "B": B, "N": N, "c": c, "direction": "outgoing then incoming",
+                       "mask": mask_kind, "parallelism": (f"rows sharded over {world} GPU(s), contraction sharded over channel planes, "
+                                       "three all-to-alls per block") if channels else
+                       (f"output rows sharded over {world} GPU(s), all-gather of b per block, "
+                        "all-to-all of a for the incoming block"),
+                       "nvlink_bytes_received_per_rank_per_step": 2 * gathered + a2a},
+            "gpu_launches": 6 * args.steps,
+            "stages": {n: {"ms": v} for n, v in zip(names, stage_ms)},
+            "clocks": clocks,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="n768_outgoing", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="n768_outgoing", choices=sorted(WORKLOADS) + sorted(PAIR_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shard-mode", default="rows", choices=["rows", "channels"],
+                    help="exchange pattern of the *_pair_sharded workloads")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps
@@ -348,7 +511,10 @@ def main():
     else:
         args.steps = 50 if args.steps is None else args.steps
         args.warmup = 5 if args.warmup is None else args.warmup
-        run_b200(args)
+        if args.workload in PAIR_WORKLOADS:
+            run_sharded_pair(args)
+        else:
+            run_b200(args)
 
 
 if __name__ == "__main__":

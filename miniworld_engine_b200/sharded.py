@@ -13,7 +13,13 @@ stage 2, done with NCCL collectives whose result the contraction kernel reads in
   (``a'[i][k] = a[k,i]``).  It needs ``a'[I_r][all k]`` -> **all-to-all of a'** (rank s sends its
   rows I_r), and ``b'[all j][all k]`` -> **all-gather b'**; both arrive as k-chunked planes.
 
-No k-sum is split across ranks, so the result equals the single-GPU result.  The reference has
+A second exchange pattern, ``ChannelShardPlan``, moves less data: stage 1 and stage 3 stay
+row-sharded, but the contraction is sharded over CHANNEL PLANES.  Each rank sends the planes it
+does not own of its a and b rows to their owners (all-to-all), contracts its ``B*c/world`` planes
+over the full N x N x N, and returns the rows of ``tri`` to their owners (all-to-all).  Per block
+a rank receives ``3 (world-1)/world`` of one operand instead of ``(world-1)`` operand slabs.
+
+No k-sum is split across ranks in either pattern, so the result equals the single-GPU result.  The reference has
 no distributed code at all; its single-GPU module is the behaviour to match.
 
 The exchange logic is independent of the device: ``exchange()`` works on flat tensors with any
@@ -29,7 +35,7 @@ import torch.distributed as dist
 
 from . import stages as S
 
-__all__ = ["ShardPlan", "exchange", "trimul_forward_sharded"]
+__all__ = ["ShardPlan", "ChannelShardPlan", "exchange", "trimul_forward_sharded"]
 
 
 @dataclass
@@ -135,17 +141,121 @@ def exchange(plan: ShardPlan, a_send: torch.Tensor, a_recv: torch.Tensor, b_full
     return works
 
 
+@dataclass
+class ChannelShardPlan:
+    """Row-sharded stage 1 / stage 3 with a channel-sharded contraction (three all-to-alls).
+
+    Buffers (all chunk-major, chunk = peer rank, so every all-to-all moves contiguous equal
+    chunks and the kernels read/write the exchanged data in place):
+
+    * ``a_send``/``b_send``: stage 1 output in the plain plane-major layout; the planes of rank s
+      are the s-th contiguous chunk;
+    * ``a_recv``/``b_recv``: this rank's planes with the rows (outgoing) or the k-columns
+      (incoming) of every rank: row-chunked resp. column-chunked planes;
+    * ``tri_send``: contraction output for this rank's planes, row-chunked by destination rank;
+    * ``tri_recv``: chunk s holds planes of rank s for this rank's rows = the plain layout.
+    """
+
+    B: int
+    N: int
+    c: int
+    world: int
+    rank: int
+    outgoing: bool
+
+    def __post_init__(self):
+        if self.N % self.world != 0:
+            raise ValueError(f"N={self.N} must be divisible by the number of ranks ({self.world})")
+        if (self.B * self.c) % self.world != 0:
+            raise ValueError(f"B*c={self.B * self.c} must be divisible by the number of ranks ({self.world})")
+        if not 0 <= self.rank < self.world:
+            raise ValueError(f"rank {self.rank} outside [0, {self.world})")
+        self.R = self.N // self.world
+        self.row0 = self.rank * self.R
+        self.planes = self.B * self.c
+        self.my_planes = self.planes // self.world
+        self.pitch_full = S.round_up(self.N, 8)
+        self.pitch_slab = S.round_up(self.R, 8)
+
+    def _op_plane_elems(self) -> int:      # one stage-1 plane of this rank's slab
+        return self.R * self.pitch_full if self.outgoing else self.N * self.pitch_slab
+
+    def alloc(self, dtype: torch.dtype, device):
+        n_op = self.planes * self._op_plane_elems()
+        n_tri = self.planes * self.R * self.pitch_full
+        mk = lambda n: torch.empty(n, dtype=dtype, device=device)
+        return {"a_send": mk(n_op), "b_send": mk(n_op), "a_recv": mk(n_op), "b_recv": mk(n_op),
+                "tri_send": mk(n_tri), "tri_recv": mk(n_tri)}
+
+    def tm1_outputs(self, bufs):
+        P, R, N = self.planes, self.R, self.N
+        if self.outgoing:
+            mk = lambda t: S.PlaneSpec(t, P, R, N, self.pitch_full, R * self.pitch_full)
+        else:
+            mk = lambda t: S.PlaneSpec(t, P, N, R, self.pitch_slab, N * self.pitch_slab)
+        return mk(bufs["a_send"]), mk(bufs["b_send"])
+
+    def contract_operands(self, bufs):
+        Pp, R, N, W = self.my_planes, self.R, self.N, self.world
+        if self.outgoing:   # rows of every rank: [s][Pp][R][pitch_full]
+            mk = lambda t: S.PlaneSpec(t, Pp, N, N, self.pitch_full, R * self.pitch_full,
+                                       chunk_stride=Pp * R * self.pitch_full if W > 1 else 0,
+                                       row_chunk=R if W > 1 else None)
+        else:               # k-columns of every rank: [s][Pp][N][pitch_slab]
+            mk = lambda t: S.PlaneSpec(t, Pp, N, N, self.pitch_slab, N * self.pitch_slab,
+                                       chunk_stride=Pp * N * self.pitch_slab if W > 1 else 0,
+                                       col_chunk=R if W > 1 else None)
+        tri = S.PlaneSpec(bufs["tri_send"], Pp, N, N, self.pitch_full, R * self.pitch_full,
+                          chunk_stride=Pp * R * self.pitch_full if W > 1 else 0, row_chunk=R if W > 1 else None)
+        return mk(bufs["a_recv"]), mk(bufs["b_recv"]), tri
+
+    def tri_spec(self, bufs) -> S.PlaneSpec:
+        return S.PlaneSpec(bufs["tri_recv"], self.planes, self.R, self.N, self.pitch_full, self.R * self.pitch_full)
+
+    def exchange_in(self, bufs, group=None):
+        if self.world == 1:
+            bufs["a_recv"], bufs["b_recv"] = bufs["a_send"], bufs["b_send"]
+            return
+        works = [dist.all_to_all_single(bufs["a_recv"], bufs["a_send"], group=group, async_op=True),
+                 dist.all_to_all_single(bufs["b_recv"], bufs["b_send"], group=group, async_op=True)]
+        for w in works:
+            w.wait()
+
+    def exchange_out(self, bufs, group=None):
+        if self.world == 1:
+            bufs["tri_recv"] = bufs["tri_send"]
+            return
+        dist.all_to_all_single(bufs["tri_recv"], bufs["tri_send"], group=group)
+
+
 @torch.no_grad()
 def trimul_forward_sharded(z_slab: torch.Tensor, mask: torch.Tensor | None, weights: dict, *, outgoing: bool,
                            N: int | None = None, group=None, eps_in: float = 1e-5, eps_out: float = 1e-5,
-                           residual: torch.Tensor | None = None, buffers=None) -> torch.Tensor:
+                           residual: torch.Tensor | None = None, buffers=None, mode: str = "rows") -> torch.Tensor:
     """One block call on this rank's ``[B, R, N, c]`` slab of the pair tensor; returns the matching
     output slab.  ``mask`` is the FULL ``[B, N]`` token mask (or ``[B, N, N]`` pair mask), identical
-    on every rank.  ``weights`` is the keyword dict of ``stages.tm1`` / ``stages.tm2``."""
+    on every rank.  ``weights`` is the keyword dict of ``stages.tm1`` / ``stages.tm2``.
+    ``mode="rows"`` gathers the other operand (``ShardPlan``); ``mode="channels"`` shards the
+    contraction over channel planes (``ChannelShardPlan``)."""
     world = dist.get_world_size(group) if dist.is_initialized() else 1
     rank = dist.get_rank(group) if dist.is_initialized() else 0
     B, R, Nz, c = z_slab.shape
     N = Nz if N is None else N
+    if mode == "channels":
+        cp = ChannelShardPlan(B, N, c, world, rank, outgoing)
+        if R != cp.R:
+            raise ValueError(f"slab has {R} rows, expected N/world = {cp.R}")
+        bufs = buffers if buffers is not None else cp.alloc(z_slab.dtype, z_slab.device)
+        a_w, b_w = cp.tm1_outputs(bufs)
+        S.tm1(z_slab, mask, weights, a_w, b_w, outgoing=outgoing, row0=cp.row0, eps=eps_in)
+        cp.exchange_in(bufs, group)
+        a_r, b_r, tri_w = cp.contract_operands(bufs)
+        S.contract(a_r, b_r, tri_w)
+        cp.exchange_out(bufs, group)
+        return S.tm2(z_slab, cp.tri_spec(bufs), weights, residual=residual, row0=cp.row0,
+                     eps_in=eps_in, eps_out=eps_out)
+    if mode != "rows":
+        raise ValueError(f"mode must be rows|channels, got {mode!r}")
     plan = ShardPlan(B, N, c, world, rank, outgoing)
     if R != plan.R:
         raise ValueError(f"slab has {R} rows, expected N/world = {plan.R}")

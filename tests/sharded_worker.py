@@ -21,6 +21,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--N", type=int, default=512)
     ap.add_argument("--direction", default="outgoing")
+    ap.add_argument("--mode", default="rows")
     args = ap.parse_args()
     from miniworld_engine_b200 import read_status, trimul_forward
     from miniworld_engine_b200.sharded import trimul_forward_sharded
@@ -35,7 +36,7 @@ def main():
     m = O.make_token_mask(1, N, "rand5")
     wd = weights_dict(w, torch.bfloat16, dev)
     slab = z[:, rank * R:(rank + 1) * R].contiguous().to(dev)
-    out = trimul_forward_sharded(slab, m.to(dev), wd, outgoing=outgoing, N=N).cpu()
+    out = trimul_forward_sharded(slab, m.to(dev), wd, outgoing=outgoing, N=N, mode=args.mode).cpu()
     whole = trimul_forward(z.to(dev), m.to(dev), outgoing=outgoing, **forward_kwargs(w, torch.bfloat16, dev)).cpu()
     assert read_status(dev)[0] == 0
     ref = O.trimul_forward(z, m, w.to(torch.bfloat16), outgoing)[:, rank * R:(rank + 1) * R]

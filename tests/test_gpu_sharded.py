@@ -56,6 +56,56 @@ def _emulated_sharded(z, m, w, outgoing, world, dev):
     return torch.cat(outs, dim=1).cpu()
 
 
+def _emulated_channel_sharded(z, m, w, outgoing, world, dev):
+    """Same, for the channel-sharded contraction: three all-to-alls done as chunk copies."""
+    from miniworld_engine_b200 import stages as S
+    from miniworld_engine_b200.sharded import ChannelShardPlan
+    B, N, _, c = z.shape
+    wd = weights_dict(w, torch.bfloat16, dev)
+    zd, md = z.bfloat16().to(dev), m.to(dev)
+    plans = [ChannelShardPlan(B, N, c, world, r, outgoing) for r in range(world)]
+    bufs = [p.alloc(torch.bfloat16, dev) for p in plans]
+    for bf in bufs:
+        for t in bf.values():
+            t.view(torch.int16).fill_(0x7FC0)
+    R = plans[0].R
+    for r, p in enumerate(plans):
+        a_w, b_w = p.tm1_outputs(bufs[r])
+        S.tm1(zd[:, r * R:(r + 1) * R].contiguous(), md, wd, a_w, b_w, outgoing=outgoing, row0=p.row0)
+
+    def all_to_all(src, dst):
+        n = bufs[0][src].numel() // world
+        for r in range(world):
+            for s in range(world):
+                bufs[r][dst][s * n:(s + 1) * n].copy_(bufs[s][src][r * n:(r + 1) * n])
+
+    all_to_all("a_send", "a_recv")
+    all_to_all("b_send", "b_recv")
+    for r, p in enumerate(plans):
+        a_r, b_r, tri_w = p.contract_operands(bufs[r])
+        S.contract(a_r, b_r, tri_w)
+    all_to_all("tri_send", "tri_recv")
+    outs = [S.tm2(zd[:, r * R:(r + 1) * R].contiguous(), p.tri_spec(bufs[r]), wd, row0=p.row0)
+            for r, p in enumerate(plans)]
+    return torch.cat(outs, dim=1).cpu()
+
+
+@pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
+def test_one_gpu_emulation_of_channel_sharding(outgoing):
+    from miniworld_engine_b200 import read_status, trimul_forward
+    dev = torch.device("cuda", 0)
+    N, world = 512, 2
+    w = O.make_weights(128, 0, affine="random")
+    z = O.make_input(1, N, 128, 1)
+    m = O.make_token_mask(1, N, "rand5")
+    got = _emulated_channel_sharded(z, m, w, outgoing, world, dev)
+    assert read_status(dev)[0] == 0
+    whole = trimul_forward(z.bfloat16().to(dev), m.to(dev), outgoing=outgoing,
+                           **forward_kwargs(w, torch.bfloat16, dev)).cpu()
+    assert not torch.isnan(got.float()).any()
+    assert torch.equal(got, whole)          # same kernels, same accumulation order
+
+
 @pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
 @pytest.mark.parametrize("N,world", [(512, 2), (256, 4)])
 def test_one_gpu_emulation_of_row_sharding(N, world, outgoing):
@@ -83,13 +133,14 @@ def _free_port() -> int:
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+@pytest.mark.parametrize("mode", ["rows", "channels"])
 @pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
-def test_nccl_row_sharding_matches_single_gpu(outgoing):
+def test_nccl_row_sharding_matches_single_gpu(outgoing, mode):
     world = 2
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
            "--master-addr", "127.0.0.1", "--master-port", str(_free_port()),
            os.path.join(ROOT, "tests", "sharded_worker.py"), "--N", "512", "--direction",
-           "outgoing" if outgoing else "incoming"]
+           "outgoing" if outgoing else "incoming", "--mode", mode]
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=220, env=env, cwd=ROOT)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]

@@ -12,7 +12,7 @@ import torch.distributed as dist
 import torch.multiprocessing as mp
 
 from miniworld_engine_b200 import stages as S
-from miniworld_engine_b200.sharded import ShardPlan, exchange
+from miniworld_engine_b200.sharded import ChannelShardPlan, ShardPlan, exchange
 from oracle import trimul_oracle as O
 
 
@@ -22,7 +22,7 @@ def _free_port() -> int:
         return s.getsockname()[1]
 
 
-def _rank_main(rank, world, port, N, c, B, outgoing, q):
+def _rank_main(rank, world, port, N, c, B, outgoing, q, mode="rows"):
     try:
         os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
         dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -41,6 +41,27 @@ def _rank_main(rank, world, port, N, c, B, outgoing, q):
         else:          # transposed: plane element (i, k) = position (r0 + k, i)
             a_d = left.permute(0, 3, 2, 1).reshape(plan.planes, N, R)
             b_d = right.permute(0, 3, 2, 1).reshape(plan.planes, N, R)
+        want = full["tri"][:, r0:r0 + R].permute(0, 3, 1, 2).reshape(plan.planes, R, N)
+        if mode == "channels":
+            cp = ChannelShardPlan(B, N, c, world, rank, outgoing)
+            bufs = cp.alloc(torch.float32, "cpu")
+            for t in bufs.values():
+                t.fill_(float("nan"))
+            a_w, b_w = cp.tm1_outputs(bufs)
+            S.dense_to_planes(a_w, a_d.contiguous())
+            S.dense_to_planes(b_w, b_d.contiguous())
+            cp.exchange_in(bufs)
+            a_r, b_r, tri_w = cp.contract_operands(bufs)
+            A, Bm = S.planes_to_dense(a_r), S.planes_to_dense(b_r)
+            assert not torch.isnan(A).any() and not torch.isnan(Bm).any()
+            S.dense_to_planes(tri_w, torch.einsum("pik,pjk->pij", A, Bm))    # my planes, all rows
+            cp.exchange_out(bufs)
+            tri = S.planes_to_dense(cp.tri_spec(bufs))                         # all planes, my rows
+            err = O.rel_rms(tri, want)
+            dist.barrier()
+            dist.destroy_process_group()
+            q.put((rank, err, None))
+            return
         a_send, a_recv, b_full, _ = plan.alloc(torch.float32, "cpu")
         for t in (a_send, a_recv, b_full):
             t.fill_(float("nan"))                          # nothing may be read that was not written
@@ -52,7 +73,6 @@ def _rank_main(rank, world, port, N, c, B, outgoing, q):
         A, Bm = S.planes_to_dense(a_r), S.planes_to_dense(b_r)
         assert not torch.isnan(A).any() and not torch.isnan(Bm).any()
         tri = torch.einsum("pik,pjk->pij", A, Bm)          # [P][R][N]: rows I_rank of the contraction
-        want = full["tri"][:, r0:r0 + R].permute(0, 3, 1, 2).reshape(plan.planes, R, N)
         err = O.rel_rms(tri, want)
         dist.barrier()
         dist.destroy_process_group()
@@ -61,13 +81,15 @@ def _rank_main(rank, world, port, N, c, B, outgoing, q):
         q.put((rank, None, repr(e)))
 
 
+@pytest.mark.parametrize("mode", ["rows", "channels"])
 @pytest.mark.parametrize("world", [2, 4])
 @pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
-def test_exchange_gives_each_rank_its_rows(world, outgoing):
+def test_exchange_gives_each_rank_its_rows(world, outgoing, mode):
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
     port = _free_port()
-    procs = [ctx.Process(target=_rank_main, args=(r, world, port, 16, 8, 2, outgoing, q)) for r in range(world)]
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, 16, 8, 2, outgoing, q, mode))
+             for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=180) for _ in procs]
@@ -83,6 +105,11 @@ def test_plan_rejects_bad_partitions():
         ShardPlan(1, 10, 8, 4, 0, True)
     with pytest.raises(ValueError):
         ShardPlan(1, 8, 8, 2, 2, True)
+
+
+def test_channel_plan_rejects_bad_partitions():
+    with pytest.raises(ValueError):
+        ChannelShardPlan(1, 16, 6, 4, 0, True)      # planes not divisible
 
 
 def test_single_rank_plan_is_the_plain_layout():
