@@ -67,6 +67,8 @@ extern "C" {
 /* flags */
 #define TRIMUL_FLAG_PLAIN_KERNELS 1u  /* run the CUDA-core kernels even where tensor-core ones exist
                                          (cross-checking aid; same layouts, same rounding points)   */
+#define TRIMUL_FLAG_SINGLE_CTA_CONTRACT 2u /* contraction on lone CTAs (128x256 tiles) instead of CTA
+                                         pairs (256x256 tiles, cta_group::2); cross-checking aid    */
 
 /*
  * Problem description.  `rows`/`row0` select a horizontal slab of z for the row-sharded

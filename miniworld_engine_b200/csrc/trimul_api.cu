@@ -15,6 +15,7 @@
 #include <mutex>
 
 #include "contract_sm100.cuh"
+#include "contract2_sm100.cuh"
 #include "plain_kernels.cuh"
 #include "tm1_sm100.cuh"
 #include "tm2_sm100.cuh"
@@ -245,10 +246,10 @@ int run_plain_contract(int planes, const trimul_planes* a, const trimul_planes* 
     return launch_status();
 }
 
-bool fast_contract_ok(const trimul_planes* a, const trimul_planes* b, const trimul_planes* t) {
-    // a chunk boundary must not cut through a tile or a K slice
+bool fast_contract_ok(const trimul_planes* a, const trimul_planes* b, const trimul_planes* t, bool pair) {
+    // a chunk boundary must not cut through a tile (a CTA's half tile for the pair kernel) or a K slice
     if (a->row_chunk < a->rows && (a->row_chunk % kCtBM)) return false;
-    if (b->row_chunk < b->rows && (b->row_chunk % kCtBN)) return false;
+    if (b->row_chunk < b->rows && (b->row_chunk % (pair ? 128 : kCtBN))) return false;
     if (a->col_chunk < a->cols && (a->col_chunk % kCtBK)) return false;
     if (b->col_chunk < b->cols && (b->col_chunk % kCtBK)) return false;
     if (t->row_chunk < t->rows && (t->row_chunk % kCtBM)) return false;
@@ -260,10 +261,10 @@ bool fast_contract_ok(const trimul_planes* a, const trimul_planes* b, const trim
 }
 
 int run_fast_contract(int planes, const trimul_planes* a, const trimul_planes* b, const trimul_planes* t,
-                      cudaStream_t st, int32_t* status) {
+                      cudaStream_t st, int32_t* status, bool pair) {
     CUtensorMap tmA, tmB, tmD;
     if (!encode_planes(&tmA, *a, planes, kCtBK, kCtBM, 1)) return TRIMUL_E_CUDA;
-    if (!encode_planes(&tmB, *b, planes, kCtBK, kCtBN, 1)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmB, *b, planes, kCtBK, pair ? 128 : kCtBN, 1)) return TRIMUL_E_CUDA;
     if (!encode_planes(&tmD, *t, planes, 64, kCtBM, 1)) return TRIMUL_E_CUDA;
     ContractParams p;
     p.planes = planes;
@@ -275,6 +276,16 @@ int run_fast_contract(int planes, const trimul_planes* a, const trimul_planes* b
     p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_k_chunk = eff_chunk(b->col_chunk, b->cols);
     p.d_row_chunk = eff_chunk(t->row_chunk, t->rows); p.d_col_chunk = eff_chunk(t->col_chunk, t->cols);
     p.status = status;
+    if (pair) {
+        // CTA pairs: 256 x 256 tiles, one cluster of two CTAs per tile
+        const int64_t pair_tiles = (int64_t)planes * ((p.rows_a + 255) / 256) * ((p.rows_b + 255) / 256);
+        if (pair_tiles > 0x3fffffff) return TRIMUL_E_UNSUPPORTED;
+        if (!ensure_smem(contract2_sm100_kernel, kC2SmemBytes)) return TRIMUL_E_CUDA;
+        const int max_clusters = sm_count() / 2;
+        const int clusters = pair_tiles < max_clusters ? (int)pair_tiles : max_clusters;
+        contract2_sm100_kernel<<<2 * clusters, kCtThreads, kC2SmemBytes, st>>>(tmA, tmB, tmD, p);
+        return launch_status();
+    }
     const int64_t total = (int64_t)planes * p.tiles_m * p.tiles_n;
     if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
     if (!ensure_smem(contract_sm100_kernel, kCtSmemBytes)) return TRIMUL_E_CUDA;
@@ -422,8 +433,11 @@ int trimul_b200_contract(int32_t dtype, uint32_t flags, int32_t planes, const tr
     if (a->rows <= 0 || b->rows <= 0 || a->cols <= 0) return TRIMUL_E_INVALID;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (dtype == TRIMUL_DTYPE_FP32) return run_plain_contract<float>(planes, a, b, tri, st);
-    if ((flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0 && fast_contract_ok(a, b, tri))
-        return run_fast_contract(planes, a, b, tri, st, status);
+    if ((flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0) {
+        const bool pair = (flags & TRIMUL_FLAG_SINGLE_CTA_CONTRACT) == 0 && sm_count() >= 2;
+        if (fast_contract_ok(a, b, tri, pair)) return run_fast_contract(planes, a, b, tri, st, status, pair);
+        if (pair && fast_contract_ok(a, b, tri, false)) return run_fast_contract(planes, a, b, tri, st, status, false);
+    }
     return run_plain_contract<__nv_bfloat16>(planes, a, b, tri, st);
 }
 

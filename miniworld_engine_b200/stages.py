@@ -136,14 +136,16 @@ def tm1(z_slab: torch.Tensor, mask, weights: dict, a: PlaneSpec, b: PlaneSpec, *
         t.record_stream(torch.cuda.current_stream(z_slab.device))
 
 
-def contract(a: PlaneSpec, b: PlaneSpec, tri: PlaneSpec, *, plain_kernels: bool = False) -> None:
+def contract(a: PlaneSpec, b: PlaneSpec, tri: PlaneSpec, *, plain_kernels: bool = False,
+             single_cta: bool = False) -> None:
     """Stage 2: ``tri[p] = a[p] @ b[p]^T`` for every plane."""
     dev = a.buf.device
     code = _lib.DTYPE_BF16 if a.buf.dtype == torch.bfloat16 else _lib.DTYPE_FP32
     st = _status_words(dev)
     with torch.cuda.device(dev):
         rc = _lib.load().trimul_b200_contract(
-            code, _lib.FLAG_PLAIN_KERNELS if plain_kernels else 0, a.planes,
+            code, (_lib.FLAG_PLAIN_KERNELS if plain_kernels else 0) |
+            (_lib.FLAG_SINGLE_CTA_CONTRACT if single_cta else 0), a.planes,
             C.byref(a.struct()), C.byref(b.struct()), C.byref(tri.struct()),
             torch.cuda.current_stream(dev).cuda_stream, st.data_ptr())
     _lib.check(rc, "trimul_b200_contract")
