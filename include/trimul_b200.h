@@ -69,6 +69,9 @@ extern "C" {
                                          (cross-checking aid; same layouts, same rounding points)   */
 #define TRIMUL_FLAG_SINGLE_CTA_CONTRACT 2u /* contraction on lone CTAs (128x256 tiles) instead of CTA
                                          pairs (256x256 tiles, cta_group::2); cross-checking aid    */
+#define TRIMUL_FLAG_PAIR_STAGE1 4u    /* stage 1 on CTA pairs (each CTA holds one side's weights and
+                                         normalises half of every tile); same results, currently
+                                         slower than the default lone-CTA kernel                     */
 
 /*
  * Problem description.  `rows`/`row0` select a horizontal slab of z for the row-sharded

@@ -367,6 +367,72 @@ __device__ __forceinline__ float sigmoid_fast(float x) {
 }
 
 // ---------------------------------------------------------------------------------------
+// CTA pairs (clusters of two, tcgen05 cta_group::2).  No TMA multicast is used anywhere: a pair's
+// loads land in the issuing CTA and only their completion is signalled across the pair.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA load of a CTA pair: data lands in this CTA, completion is signalled on `bar_cluster_addr`
+// (a shared::cluster address, here always the leader's barrier).  No multicast.
+__device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,
+                                                 int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+        "%4, %5, %6}], [%2];"
+        ::"r"(smem_u32(dst)), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1),
+        "r"(c2), "r"(c3)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_result, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+// D[tmem of both CTAs] (+)= A . B^T with A, B halves in both CTAs' shared memory; ONE thread of
+// the leader CTA issues it.
+__device__ __forceinline__ void umma_bf16_ss_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                  uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// Arrive on the barrier at the same offset in BOTH CTAs once the pair's UMMAs issued so far retire.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(smem_u32(bar)), "h"(mask)
+        : "memory");
+}
+
+
+// ---------------------------------------------------------------------------------------
 // Packed fp32 pairs (sm_100 executes add/mul/fma on two fp32 lanes per instruction).  A pair
 // lives in a 64-bit register; the helpers below are what the LayerNorm and gate code is
 // written in, which halves its arithmetic instruction count.
@@ -481,6 +547,64 @@ __device__ __forceinline__ void ln_half_row_inplace(uint8_t* tile, int sub_bytes
 #pragma unroll
         for (int jj = 0; jj < 4; ++jj) {
             const int j = 4 * h + jj;
+            uint4* p = reinterpret_cast<uint4*>(rowp + s * sub_bytes + ((((uint32_t)j) ^ swz) << 4));
+            const uint4 v = *p;
+            const int ch = s * 64 + j * 8;
+            const float4 g0 = *reinterpret_cast<const float4*>(sGamma + ch);
+            const float4 g1 = *reinterpret_cast<const float4*>(sGamma + ch + 4);
+            const float4 b0 = *reinterpret_cast<const float4*>(sBeta + ch);
+            const float4 b1 = *reinterpret_cast<const float4*>(sBeta + ch + 4);
+            uint4 o;
+            o.x = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v.x), rstd2, nmr2), f2_pack(g0.x, g0.y), f2_pack(b0.x, b0.y)));
+            o.y = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v.y), rstd2, nmr2), f2_pack(g0.z, g0.w), f2_pack(b0.z, b0.w)));
+            o.z = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v.z), rstd2, nmr2), f2_pack(g1.x, g1.y), f2_pack(b1.x, b1.y)));
+            o.w = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v.w), rstd2, nmr2), f2_pack(g1.z, g1.w), f2_pack(b1.z, b1.w)));
+            if (zero_row) o = make_uint4(0u, 0u, 0u, 0u);
+            *p = o;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// LayerNorm of one 128-channel row by ONE thread, in place, same tile layout as above.  All lanes
+// of a warp work on the same chunk index at the same time, so the gamma/beta vector loads are
+// warp-uniform (one shared-memory wavefront each) and the tile accesses are conflict-free:
+// this variant moves about a third of the shared-memory wavefronts of the two-thread one, which
+// matters because these kernels are bound by shared-memory bandwidth, not by arithmetic.
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void ln_row_inplace(uint8_t* tile, int sub_bytes, int row, const float* sGamma,
+                                               const float* sBeta, float eps, bool zero_row) {
+    const uint32_t swz = (uint32_t)(row & 7);
+    uint8_t* rowp = tile + row * 128;
+    const uint32_t first = *reinterpret_cast<const uint32_t*>(rowp + (swz << 4));
+    const float shift = bf16_lo(first);
+    const f32x2 nshift = f2_pack(-shift, -shift);
+    // four independent accumulator pairs keep the dependent add/fma chains short
+    f32x2 s1[4] = {0ull, 0ull, 0ull, 0ull}, s2[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll 1
+    for (int s = 0; s < 2; ++s) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const uint4 v = *reinterpret_cast<const uint4*>(rowp + s * sub_bytes + ((((uint32_t)j) ^ swz) << 4));
+            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const f32x2 d = f2_add(f2_from_bf16x2(w4[e]), nshift);
+                s1[e] = f2_add(s1[e], d);
+                s2[e] = f2_fma(d, d, s2[e]);
+            }
+        }
+    }
+    const float m1 = f2_hsum(f2_add(f2_add(s1[0], s1[1]), f2_add(s1[2], s1[3]))) * (1.0f / 128.0f);
+    const float q1 = f2_hsum(f2_add(f2_add(s2[0], s2[1]), f2_add(s2[2], s2[3])));
+    const float var = fmaxf(fmaf(-m1, m1, q1 * (1.0f / 128.0f)), 0.f);
+    const float rstd = rsqrtf(var + eps);
+    const float nmr = -(shift + m1) * rstd;
+    const f32x2 rstd2 = f2_pack(rstd, rstd), nmr2 = f2_pack(nmr, nmr);
+#pragma unroll 1
+    for (int s = 0; s < 2; ++s) {
+#pragma unroll 4
+        for (int j = 0; j < 8; ++j) {
             uint4* p = reinterpret_cast<uint4*>(rowp + s * sub_bytes + ((((uint32_t)j) ^ swz) << 4));
             const uint4 v = *p;
             const int ch = s * 64 + j * 8;

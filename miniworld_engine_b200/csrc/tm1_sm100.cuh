@@ -12,7 +12,8 @@
 //   warp 0        TMA producer: the four weight matrices once, then z tiles into a 2-stage ring
 //   warp 1        UMMA issuer: per tile, left pair (proj, gate) then right pair, 128x128x16 each,
 //                 into four 128-column TMEM accumulators
-//   warps 2..9    LayerNorm: two threads per position normalise its 128 channels in place inside
+//   warps 2..9    LayerNorm: two groups of four warps on alternate tiles, one thread per position
+//                 normalises its 128 channels in place inside
 //                 the swizzled tile (the TMA SWIZZLE_128B image is the UMMA K-major layout) and
 //                 round to bf16; a masked position is written as a zero row, which makes both
 //                 projections of that position exactly zero, so the epilogue needs no mask
@@ -47,6 +48,7 @@ constexpr int kT1OffBars = kT1OffAffine + 2 * kT1C * 4;
 constexpr int kT1SmemBytes = kT1OffBars + 192;
 constexpr int kT1LnBarrier = 2;
 constexpr int kT1EpiBarrier = 3;       // 3: left side, 4: right side
+constexpr int kT1LnBarrier2 = 5;       // second LayerNorm group
 constexpr int kStageIdTm1 = 1;
 
 struct Tm1Params {
@@ -100,7 +102,7 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         mbar_init(w_ready, kT1LnThreads + 2 * kT1EpiThreads);
         for (int s = 0; s < 2; ++s) {
             mbar_init(&x_full[s], 1);
-            mbar_init(&xn_ready[s], kT1LnThreads);
+            mbar_init(&xn_ready[s], kT1LnThreads / 2);
             mbar_init(&x_empty[s], 1);
             mbar_init(&acc_full[s], 1);
             mbar_init(&acc_empty[s], 4);
@@ -202,12 +204,13 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         __syncwarp();
     } else if (warp < 10) {
         // ------------------------------------------------------------------ LayerNorm (+ mask)
-        const int lt = threadIdx.x - 64;      // 0..255
-        const int pos = lt >> 1;              // row of the tile
-        const int h = lt & 1;
-        uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
-            const int s = it & 1;
+        // two groups of four warps; group g takes the tiles with (local tile index & 1) == g, which
+        // are the ones in stage g; one thread per position
+        const int g = (warp - 2) >> 2;
+        const int pos = threadIdx.x - 64 - g * 128;    // 0..127, row of the tile
+        const int bar_id = g == 0 ? kT1LnBarrier : kT1LnBarrier2;
+        uint32_t it = g;
+        for (int tile = blockIdx.x + g * gridDim.x; tile < p.total_tiles; tile += 2 * gridDim.x, it += 2) {
             const uint32_t ph = (it >> 1) & 1u;
             // pair-mask value of this position (independent of the tile data: do it first)
             bool keep = true;
@@ -227,12 +230,10 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                         keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
                 }
             }
-            if (!group_wait(&x_full[s], ph, lt == 0, kT1LnBarrier, kT1LnThreads, abort_flag, p.status,
-                            kStageIdTm1, 300 + s))
-                break;
-            ln_half_row_inplace(sX + s * kT1XBytes, kT1SubTile, pos, h, sGamma, sBeta, p.eps, !keep);
+            if (!group_wait(&x_full[g], ph, pos == 0, bar_id, 128, abort_flag, p.status, kStageIdTm1, 300 + g)) break;
+            ln_row_inplace(sX + g * kT1XBytes, kT1SubTile, pos, sGamma, sBeta, p.eps, !keep);
             fence_proxy_async_smem();   // normalised tile -> visible to the UMMA (async proxy)
-            mbar_arrive(&xn_ready[s]);
+            mbar_arrive(&xn_ready[g]);
         }
     } else {
         // ------------------------------------------------------------------ epilogue, one side per group

@@ -10,7 +10,8 @@
 //                 MN-major — the channel-major tile is used as the A operand AS IT LIES, so the
 //                 channel-major -> row-major turn of the data costs nothing at all; 128x128x16
 //                 each, into a double-buffered pair of 128-column TMEM accumulators
-//   warps 2..9    LayerNorm_in: two threads per position, in place in the swizzled z tile
+//   warps 2..9    LayerNorm_in: two groups of four warps on alternate tiles, one thread per
+//                 position, in place in the swizzled z tile
 //   warps 10..17  LayerNorm_out, in place in the swizzled tri tile: a thread owns 4 positions (8
 //                 bytes) of 16 channel rows; the per-position sums are combined over the 8 lanes
 //                 that share the positions by warp shuffles
@@ -44,6 +45,7 @@ constexpr int kT2SmemBytes = kT2OffBars + 192;
 constexpr int kT2LnBarrier = 2;
 constexpr int kT2TriBarrier = 3;
 constexpr int kT2EpiBarrier = 4;
+constexpr int kT2LnBarrier2 = 5;        // second LayerNorm_in group
 constexpr int kStageIdTm2 = 3;
 
 struct Tm2Params {
@@ -97,7 +99,7 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         for (int s = 0; s < 2; ++s) {
             mbar_init(&x_full[s], 1);
             mbar_init(&t_full[s], 1);
-            mbar_init(&xn_ready[s], kT2LnThreads);
+            mbar_init(&xn_ready[s], kT2LnThreads / 2);
             mbar_init(&tn_ready[s], kT2TriThreads);
             mbar_init(&s_empty[s], 1);
             mbar_init(&acc_full[s], 1);
@@ -213,21 +215,19 @@ tm2_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         __syncwarp();
     } else if (warp < 10) {
         // ------------------------------------------------------------------ LayerNorm_in, in place
-        const int lt = threadIdx.x - 64;
-        const int pos = lt >> 1;
-        const int h = lt & 1;
-        uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
-            const int s = it & 1;
+        // two groups of four warps; group g takes the tiles in stage g; one thread per position
+        const int g = (warp - 2) >> 2;
+        const int pos = threadIdx.x - 64 - g * 128;
+        const int bar_id = g == 0 ? kT2LnBarrier : kT2LnBarrier2;
+        uint32_t it = g;
+        for (int tile = blockIdx.x + g * gridDim.x; tile < p.total_tiles; tile += 2 * gridDim.x, it += 2) {
             const uint32_t ph = (it >> 1) & 1u;
-            if (!group_wait(&x_full[s], ph, lt == 0, kT2LnBarrier, kT2LnThreads, abort_flag, p.status,
-                            kStageIdTm2, 300 + s))
-                break;
-            if (lt == 0) TRIMUL_STAMP(1, it, 0);
-            ln_half_row_inplace(sStage + s * kT2StageBytes, kT2SubTile, pos, h, sAff, sAff + kT2C, p.eps_in, false);
+            if (!group_wait(&x_full[g], ph, pos == 0, bar_id, 128, abort_flag, p.status, kStageIdTm2, 300 + g)) break;
+            if (pos == 0) TRIMUL_STAMP(1, it, 0);
+            ln_row_inplace(sStage + g * kT2StageBytes, kT2SubTile, pos, sAff, sAff + kT2C, p.eps_in, false);
             fence_proxy_async_smem();
-            if (lt == 0) TRIMUL_STAMP(1, it, 1);
-            mbar_arrive(&xn_ready[s]);
+            if (pos == 0) TRIMUL_STAMP(1, it, 1);
+            mbar_arrive(&xn_ready[g]);
         }
     } else if (warp < 18) {
         // ------------------------------------------------------------------ LayerNorm_out, in place

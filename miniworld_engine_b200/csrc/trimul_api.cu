@@ -18,6 +18,7 @@
 #include "contract2_sm100.cuh"
 #include "plain_kernels.cuh"
 #include "tm1_sm100.cuh"
+#include "tm1_pair_sm100.cuh"
 #include "tm2_sm100.cuh"
 
 using namespace trimul;
@@ -193,12 +194,14 @@ int run_plain_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, cons
 int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
                  const trimul_planes* a, const trimul_planes* b, cudaStream_t st, int32_t* status) {
     const bool inc = d->direction == TRIMUL_INCOMING;
+    const bool pair = (d->flags & TRIMUL_FLAG_PAIR_STAGE1) != 0 && sm_count() >= 2;
+    const uint32_t zpos = pair ? 64 : 128;       // positions one CTA loads per tile
     CUtensorMap tmZ, tmW[4], tmA, tmB;
     {
         const uint64_t dims[4] = {128, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
         const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
-        const uint32_t box_out[4] = {64, 128, 1, 1};
-        const uint32_t box_in[4] = {64, 1, 128, 1};
+        const uint32_t box_out[4] = {64, zpos, 1, 1};
+        const uint32_t box_in[4] = {64, 1, zpos, 1};
         if (!encode_bf16(&tmZ, z, 4, dims, strides, inc ? box_in : box_out, 128)) return TRIMUL_E_CUDA;
     }
     const void* ws[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
@@ -229,6 +232,15 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_col_chunk = eff_chunk(a->col_chunk, a->cols);
     p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
     p.status = status;
+    if (pair) {
+        // CTA pairs: one cluster of two CTAs per 128-position tile
+        if (!ensure_smem(tm1_pair_sm100_kernel, kP1SmemBytes)) return TRIMUL_E_CUDA;
+        const int max_clusters = sm_count() / 2;
+        const int clusters = p.total_tiles < max_clusters ? p.total_tiles : max_clusters;
+        tm1_pair_sm100_kernel<<<2 * clusters, kP1Threads, kP1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3],
+                                                                             tmA, tmB, p);
+        return launch_status();
+    }
     if (!ensure_smem(tm1_sm100_kernel, kT1SmemBytes)) return TRIMUL_E_CUDA;
     const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
     tm1_sm100_kernel<<<grid, kT1Threads, kT1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p);

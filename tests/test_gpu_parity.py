@@ -185,3 +185,32 @@ def test_module_state_dict_roundtrip_and_forward(dev):
         y = mod(z.to(dev), m.to(dev)).cpu()
     ref = O.trimul_forward(z, m, w.to(torch.bfloat16), False) + z
     assert O.rel_rms(y.float(), ref.float()) <= TOL_BF16
+
+
+def test_alternative_kernels_agree(dev):
+    """The lone-CTA contraction is another schedule of the same arithmetic as the CTA-pair one
+    (same accumulation order per output element): bit-identical.  The CTA-pair stage 1 sums the
+    LayerNorm statistics in a different order, so it may differ from the default in the last
+    bf16 bit of a few elements."""
+    from miniworld_engine_b200 import read_status, stages as S
+    from tests._util import weights_dict
+    w = O.make_weights(128, 0, affine="random")
+    wd = weights_dict(w, torch.bfloat16, dev)
+    N = 200
+    z = O.make_input(2, N, 128, 1).bfloat16().to(dev)
+    m = O.make_token_mask(2, N, "tail9").to(dev)
+    for outgoing in (True, False):
+        res = []
+        for pair in (False, True):
+            a = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
+            b = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
+            S.tm1(z, m, wd, a, b, outgoing=outgoing, pair_stage1=pair)
+            res.append((S.planes_to_dense(a).clone(), S.planes_to_dense(b).clone(), a, b))
+        assert O.rel_rms(res[1][0].float().cpu(), res[0][0].float().cpu()) <= 1e-3
+        assert O.rel_rms(res[1][1].float().cpu(), res[0][1].float().cpu()) <= 1e-3
+        t1 = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
+        t2 = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
+        S.contract(res[0][2], res[0][3], t1)
+        S.contract(res[0][2], res[0][3], t2, single_cta=True)
+        assert torch.equal(S.planes_to_dense(t1), S.planes_to_dense(t2))
+    assert read_status(dev)[0] == 0
