@@ -16,7 +16,7 @@
 // Roles per CTA (832 threads):
 //   warp 0        TMA producer: this CTA's two weight matrices, then its 64-position tiles
 //   warp 1        UMMA issuer (leader CTA only; the other CTA's warp 1 only allocates TMEM)
-//   warps 2..9    LayerNorm, two groups of four warps taking alternate tiles, two threads per position
+//   warps 2..9    LayerNorm, four groups of two warps taking every fourth tile, one thread per position
 //   warps 10..25  epilogue of this CTA's side, four groups of four warps: (accumulator set, half tile):
 //                 TMEM -> p * sigmoid(g) -> bf16 -> swizzled staging -> TMA store
 // Cross-CTA signalling (no TMA multicast anywhere):
@@ -44,8 +44,8 @@ constexpr int kP1OffStaging = kP1OffX + kP1Stages * kP1XBytes;
 constexpr int kP1OffAffine = kP1OffStaging + 4 * kP1BoxBytes;   // two boxes per epilogue group
 constexpr int kP1OffBars = kP1OffAffine + 2 * kT1C * 4;
 constexpr int kP1SmemBytes = kP1OffBars + 320;
-constexpr int kP1LnBarrier = 2;        // 2, 3: the two LayerNorm groups
-constexpr int kP1EpiBarrier = 4;       // 4..7: the four epilogue groups
+constexpr int kP1LnBarrier = 2;        // 2..5: the four LayerNorm groups
+constexpr int kP1EpiBarrier = 6;       // 6..9: the four epilogue groups
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kP1Threads, 1)
 tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWp,
@@ -196,14 +196,13 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         __syncwarp();
     } else if (warp < 10) {
         // ------------------------------------------------------------------ LayerNorm (+ mask)
-        // group g takes the tiles with (local tile index & 1) == g; two threads per position
-        const int g = (warp - 2) >> 2;
-        const int lt = threadIdx.x - 64 - g * 128;     // 0..127
-        const int pos = lt >> 1;                       // row of this CTA's half tile
-        const int h = lt & 1;
+        // four groups of two warps; group g takes the tiles with (local tile index & 3) == g; one
+        // thread per position of this CTA's half tile
+        const int g = (warp - 2) >> 1;
+        const int pos = threadIdx.x - 64 - g * 64;     // 0..63
         const int bar_id = kP1LnBarrier + g;
         uint32_t it = g;
-        for (int tile = cluster_id + g * num_clusters; tile < total_tiles; tile += 2 * num_clusters, it += 2) {
+        for (int tile = cluster_id + g * num_clusters; tile < total_tiles; tile += 4 * num_clusters, it += 4) {
             const int s = it % kP1Stages;
             const uint32_t ph = (it / kP1Stages) & 1u;
             bool keep = true;
@@ -223,13 +222,13 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                         keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
                 }
             }
-            if (!group_wait(&x_full[s], ph, lt == 0, bar_id, 128, abort_flag, p.status, kStageIdTm1, 1300 + s)) break;
-            if (lt == 0 && is_leader) TRIMUL_STAMP(1, it, 0);
-            ln_half_row_inplace(sX + s * kP1XBytes, kP1SubTile, pos, h, sGamma, sBeta, p.eps, !keep);
+            if (!group_wait(&x_full[s], ph, pos == 0, bar_id, 64, abort_flag, p.status, kStageIdTm1, 1300 + s)) break;
+            if (pos == 0 && is_leader) TRIMUL_STAMP(1, it, 0);
+            ln_row_inplace(sX + s * kP1XBytes, kP1SubTile, pos, sGamma, sBeta, p.eps, !keep);
             fence_proxy_async_smem();          // normalised half tile -> visible to the UMMA (async proxy)
-            named_barrier_sync(bar_id, 128);   // the whole half is written ...
-            if (lt == 0 && is_leader) TRIMUL_STAMP(1, it, 1);
-            if (lt == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&xn_ready[s]), 0));   // ... tell the leader
+            named_barrier_sync(bar_id, 64);    // the whole half is written ...
+            if (pos == 0 && is_leader) TRIMUL_STAMP(1, it, 1);
+            if (pos == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&xn_ready[s]), 0));   // ... tell the leader
         }
     } else {
         // ------------------------------------------------------------------ epilogue of this CTA's side

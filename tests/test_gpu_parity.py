@@ -214,3 +214,41 @@ def test_alternative_kernels_agree(dev):
         S.contract(res[0][2], res[0][3], t2, single_cta=True)
         assert torch.equal(S.planes_to_dense(t1), S.planes_to_dense(t2))
     assert read_status(dev)[0] == 0
+
+
+def test_cuda_graph_capture_and_replay(dev):
+    """The block call neither allocates nor synchronises once its buffers exist, so it can be
+    captured in a CUDA graph; replays must reproduce the eager result bit for bit (the reference
+    benchmarks its own path in this regime, benchmarks/runners/bench.py:295-344)."""
+    from miniworld_engine_b200 import read_status, stages as S
+    from tests._util import weights_dict
+    w = O.make_weights(128, 0)
+    wd = weights_dict(w, torch.bfloat16, dev)
+    N = 160
+    z = O.make_input(1, N, 128, 1).bfloat16().to(dev)
+    m = O.make_token_mask(1, N, "tail7").to(dev)
+    a = S.alloc_planes(128, N, N, torch.bfloat16, dev)
+    b = S.alloc_planes(128, N, N, torch.bfloat16, dev)
+    t = S.alloc_planes(128, N, N, torch.bfloat16, dev)
+
+    def block():
+        S.tm1(z, m, wd, a, b, outgoing=False)
+        S.contract(a, b, t)
+        return S.tm2(z, t, wd, residual=z)
+
+    eager = block().clone()
+    side = torch.cuda.Stream(device=dev)
+    side.wait_stream(torch.cuda.current_stream(dev))
+    with torch.cuda.stream(side):
+        block()                                   # warm-up on the capture stream (module load, attributes)
+    torch.cuda.current_stream(dev).wait_stream(side)
+    torch.cuda.synchronize(dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = block()
+    for _ in range(3):
+        out.zero_()
+        graph.replay()
+        torch.cuda.synchronize(dev)
+        assert torch.equal(out, eager)
+    assert read_status(dev)[0] == 0
