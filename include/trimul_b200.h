@@ -72,6 +72,9 @@ extern "C" {
 #define TRIMUL_FLAG_PAIR_STAGE1 4u    /* stage 1 on CTA pairs (each CTA holds one side's weights and
                                          normalises half of every tile); same results, currently
                                          slower than the default lone-CTA kernel                     */
+#define TRIMUL_FLAG_FOLDED_NORM 8u    /* stage 1 with the input LayerNorm folded into the projection
+                                         weights (held in tensor memory) and applied per position
+                                         in the epilogue; rounds W*gamma instead of LN(x) to bf16    */
 
 /*
  * Problem description.  `rows`/`row0` select a horizontal slab of z for the row-sharded

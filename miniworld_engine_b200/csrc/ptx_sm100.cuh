@@ -131,8 +131,12 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any thread of the CTA has timed out,
 // every other wait in the CTA returns false promptly, and all roles fall through to the
 // kernel's tear-down.  Returns true when the phase completed.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* status, int stage, int detail) {
+// The polling loop is kept OUT OF LINE: these kernels wait in dozens of places, and inlining the
+// loop everywhere pushed their code past what the SM's instruction cache holds (hit rates of
+// 60-90 % and the instruction-fetch path near its peak); the call costs nothing that matters on a
+// path that is about to sleep anyway.
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                            int32_t* status, int stage, int detail) {
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -149,6 +153,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     *abort_flag = 1;
     report_timeout(status, stage, detail);
     return false;
+}
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          int32_t* status, int stage, int detail) {
+    if (mbar_try_wait(bar, parity)) return true;
+    return mbar_wait_slow(bar, parity, abort_flag, status, stage, detail);
 }
 
 // Collective AND over the `nthreads` threads that share named barrier `id`: every one of them
@@ -341,6 +350,15 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[16])
         "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
         : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
           "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Same, 8 consecutive columns.
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
         : "r"(taddr)
         : "memory");
 }
@@ -622,5 +640,38 @@ __device__ __forceinline__ void ln_row_inplace(uint8_t* tile, int sub_bytes, int
         }
     }
 }
+
+// Mean / rstd of one 128-channel row of a swizzled z tile (one pass, sums shifted by the row's
+// first element so the variance does not cancel).  Returns rstd and t = -mean * rstd.
+__device__ __forceinline__ void row_stats(const uint8_t* tile, int sub_bytes, int row, float eps, float& rstd,
+                                          float& t) {
+    const uint32_t swz = (uint32_t)(row & 7);
+    const uint8_t* rowp = tile + row * 128;
+    const uint32_t first = *reinterpret_cast<const uint32_t*>(rowp + (swz << 4));
+    const float shift = bf16_lo(first);
+    const f32x2 nshift = f2_pack(-shift, -shift);
+    f32x2 s1[4] = {0ull, 0ull, 0ull, 0ull}, s2[4] = {0ull, 0ull, 0ull, 0ull};
+    // (short loop bodies on purpose: see the note on instruction-cache pressure at mbar_wait_slow)
+#pragma unroll 1
+    for (int s = 0; s < 2; ++s) {
+#pragma unroll 4
+        for (int j = 0; j < 8; ++j) {
+            const uint4 v = *reinterpret_cast<const uint4*>(rowp + s * sub_bytes + ((((uint32_t)j) ^ swz) << 4));
+            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const f32x2 d = f2_add(f2_from_bf16x2(w4[e]), nshift);
+                s1[e] = f2_add(s1[e], d);
+                s2[e] = f2_fma(d, d, s2[e]);
+            }
+        }
+    }
+    const float m1 = f2_hsum(f2_add(f2_add(s1[0], s1[1]), f2_add(s1[2], s1[3]))) * (1.0f / 128.0f);
+    const float q1 = f2_hsum(f2_add(f2_add(s2[0], s2[1]), f2_add(s2[2], s2[3])));
+    const float var = fmaxf(fmaf(-m1, m1, q1 * (1.0f / 128.0f)), 0.f);
+    rstd = rsqrtf(var + eps);
+    t = -(shift + m1) * rstd;
+}
+
 
 }  // namespace trimul

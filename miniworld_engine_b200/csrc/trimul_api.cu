@@ -19,7 +19,9 @@
 #include "plain_kernels.cuh"
 #include "tm1_sm100.cuh"
 #include "tm1_pair_sm100.cuh"
+#include "tm1_fold_sm100.cuh"
 #include "tm2_sm100.cuh"
+#include "tm2_fold_sm100.cuh"
 
 using namespace trimul;
 
@@ -232,6 +234,16 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_col_chunk = eff_chunk(a->col_chunk, a->cols);
     p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
     p.status = status;
+    if ((d->flags & TRIMUL_FLAG_FOLDED_NORM) != 0) {
+        // LayerNorm folded into the weights, which live in tensor memory
+        Tm1FoldParams fp;
+        fp.base = p;
+        for (int m = 0; m < 4; ++m) fp.w[m] = static_cast<const __nv_bfloat16*>(ws[m]);
+        if (!ensure_smem(tm1_fold_sm100_kernel, kF1SmemBytes)) return TRIMUL_E_CUDA;
+        const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+        tm1_fold_sm100_kernel<<<grid, kF1Threads, kF1SmemBytes, st>>>(tmZ, tmA, tmB, fp);
+        return launch_status();
+    }
     if (pair) {
         // CTA pairs: one cluster of two CTAs per 128-position tile
         if (!ensure_smem(tm1_pair_sm100_kernel, kP1SmemBytes)) return TRIMUL_E_CUDA;
@@ -351,8 +363,22 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     p.eps_in = d->eps_in; p.eps_out = d->eps_out;
     p.has_residual = residual != nullptr;
     p.status = status;
-    if (!ensure_smem(tm2_sm100_kernel, kT2SmemBytes)) return TRIMUL_E_CUDA;
     const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+    if ((d->flags & TRIMUL_FLAG_FOLDED_NORM) != 0 && (residual == nullptr || residual == z)) {
+        // both LayerNorms folded into the weights, result written in place over the z tile
+        Tm2FoldParams fp;
+        fp.base = p;
+        fp.residual_is_z = residual != nullptr;
+        if (residual != nullptr) {
+            if (!ensure_smem(tm2_fold_sm100_kernel<true>, kG2SmemBytes)) return TRIMUL_E_CUDA;
+            tm2_fold_sm100_kernel<true><<<grid, kG2Threads, kG2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmTri, fp);
+        } else {
+            if (!ensure_smem(tm2_fold_sm100_kernel<false>, kG2SmemBytes)) return TRIMUL_E_CUDA;
+            tm2_fold_sm100_kernel<false><<<grid, kG2Threads, kG2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmTri, fp);
+        }
+        return launch_status();
+    }
+    if (!ensure_smem(tm2_sm100_kernel, kT2SmemBytes)) return TRIMUL_E_CUDA;
     tm2_sm100_kernel<<<grid, kT2Threads, kT2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmRes, tmTri, p);
     return launch_status();
 }
