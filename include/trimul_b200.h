@@ -72,9 +72,14 @@ extern "C" {
 #define TRIMUL_FLAG_PAIR_STAGE1 4u    /* stage 1 on CTA pairs (each CTA holds one side's weights and
                                          normalises half of every tile); same results, currently
                                          slower than the default lone-CTA kernel                     */
-#define TRIMUL_FLAG_FOLDED_NORM 8u    /* stage 1 with the input LayerNorm folded into the projection
+#define TRIMUL_FLAG_FOLDED_STAGE1 8u   /* stage 1 with the input LayerNorm folded into the projection
                                          weights (held in tensor memory) and applied per position
-                                         in the epilogue; rounds W*gamma instead of LN(x) to bf16    */
+                                         in the epilogue; rounds W*gamma instead of LN(x) to bf16;
+                                         currently slower than the default kernel                   */
+#define TRIMUL_FLAG_INPLACE_NORM_STAGE3 16u /* stage 3 with both LayerNorms applied in place in shared
+                                         memory before the projections (rounds LN(x) to bf16 like the
+                                         reference) instead of the default kernel, which folds them
+                                         into the weights; cross-checking aid, slower               */
 
 /*
  * Problem description.  `rows`/`row0` select a horizontal slab of z for the row-sharded

@@ -24,7 +24,8 @@ MASK_NONE, MASK_TOKEN, MASK_PAIR = 0, 1, 2
 FLAG_PLAIN_KERNELS = 1
 FLAG_SINGLE_CTA_CONTRACT = 2
 FLAG_PAIR_STAGE1 = 4
-FLAG_FOLDED_NORM = 8
+FLAG_FOLDED_STAGE1 = 8
+FLAG_INPLACE_NORM_STAGE3 = 16
 
 EXPORTED_SYMBOLS = (
     "trimul_b200_abi_version",

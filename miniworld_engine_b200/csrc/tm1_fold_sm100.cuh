@@ -229,7 +229,7 @@ tm1_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                         const uint32_t d_g = d_p + 64;
                         const uint32_t a_p = tmem_base + (side * 2) * 64;
                         const uint32_t a_g = a_p + 64;
-#pragma unroll
+#pragma unroll 2
                         for (int kk = 0; kk < kT1C / 16; ++kk) {
                             // B operand: positions half*64 .. +63 (64 rows of 128 bytes = 8 KB per half)
                             const uint64_t db = umma_smem_desc_sw128(xs + (kk >> 2) * kT1SubTile + half * 8192) +
@@ -341,54 +341,50 @@ tm1_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 tcgen05_fence_after();
                 if (leader) TRIMUL_STAMP(4 + side, it, half * 2);
                 uint8_t* stg = sOut + (side * 2 + (use & 1u)) * kF1BoxBytes;
-                // 16 positions at a time; the TMEM loads of the next 16 are in flight while the
-                // current 16 get their statistics, are gated, rounded and written to the staging box
-                auto emit16 = [&](int c16, const uint32_t (&rp)[16], const uint32_t (&rg)[16]) {
-                    const int pair0 = half * 32 + c16 * 8;      // first position pair of the 16
+                // 8 positions (one 16-byte chunk) at a time; the TMEM loads of the next 8 are in flight
+                // while the current 8 get their statistics, are gated, rounded and written to the staging
+                // box.  The loop stays rolled to keep the code small.
+                auto emit8 = [&](int c8, const uint32_t (&rp)[8], const uint32_t (&rg)[8]) {
+                    const int pair0 = half * 32 + c8 * 4;       // first position pair of the 8
+                    uint32_t o[4];
 #pragma unroll
-                    for (int k = 0; k < 2; ++k) {
-                        uint32_t o[4];
-#pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const int i0 = k * 8 + 2 * e;
-                            const ulonglong2 st = *reinterpret_cast<const ulonglong2*>(stats + (pair0 + k * 4 + e) * 16);
-                            const f32x2 r2 = st.x, t2 = st.y;
-                            const f32x2 hp = f2_fma(f2_pack(__uint_as_float(rp[i0]), __uint_as_float(rp[i0 + 1])), r2,
-                                                    f2_fma(t2, sp2, bp2));
-                            const f32x2 hg = f2_fma(f2_pack(__uint_as_float(rg[i0]), __uint_as_float(rg[i0 + 1])), r2,
-                                                    f2_fma(t2, sg2, bg2));
-                            float g0, g1;
-                            f2_unpack(hg, g0, g1);
-                            uint32_t w = f2_to_bf16x2(f2_fma(hp, f2_pack(tanh_fast(g0), tanh_fast(g1)), hp));
-                            if (masked) w &= maskw[pair0 + k * 4 + e];
-                            o[e] = w;
-                        }
-                        const int chunk = (c16 * 2 + k) ^ (ch & 7);
-                        *reinterpret_cast<uint4*>(stg + ch * 128 + (chunk << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                    for (int e = 0; e < 4; ++e) {
+                        const ulonglong2 st = *reinterpret_cast<const ulonglong2*>(stats + (pair0 + e) * 16);
+                        const f32x2 r2 = st.x, t2 = st.y;
+                        const f32x2 hp = f2_fma(f2_pack(__uint_as_float(rp[2 * e]), __uint_as_float(rp[2 * e + 1])), r2,
+                                                f2_fma(t2, sp2, bp2));
+                        const f32x2 hg = f2_fma(f2_pack(__uint_as_float(rg[2 * e]), __uint_as_float(rg[2 * e + 1])), r2,
+                                                f2_fma(t2, sg2, bg2));
+                        float g0, g1;
+                        f2_unpack(hg, g0, g1);
+                        uint32_t w = f2_to_bf16x2(f2_fma(hp, f2_pack(tanh_fast(g0), tanh_fast(g1)), hp));
+                        if (masked) w &= maskw[pair0 + e];
+                        o[e] = w;
                     }
+                    *reinterpret_cast<uint4*>(stg + ch * 128 + ((c8 ^ (ch & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
                 };
-                uint32_t rpA[16], rgA[16], rpB[16], rgB[16];
-                tmem_ld_32x16(t_p, rpA);
-                tmem_ld_32x16(t_p + 64, rgA);
-                tmem_ld_wait();
-                tmem_ld_32x16(t_p + 16, rpB);
-                tmem_ld_32x16(t_p + 64 + 16, rgB);
-                emit16(0, rpA, rgA);
-                tmem_ld_wait();
-                tmem_ld_32x16(t_p + 32, rpA);
-                tmem_ld_32x16(t_p + 64 + 32, rgA);
-                emit16(1, rpB, rgB);
-                tmem_ld_wait();
-                tmem_ld_32x16(t_p + 48, rpB);
-                tmem_ld_32x16(t_p + 64 + 48, rgB);
-                emit16(2, rpA, rgA);
-                tmem_ld_wait();
-                // every TMEM read of this side's accumulators has completed: hand them back early
-                tcgen05_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&acc_empty[side]);
-                if (leader) TRIMUL_STAMP(4 + side, it, half * 2 + 1);
-                emit16(3, rpB, rgB);
+                uint32_t rpA[8], rgA[8], rpB[8], rgB[8];
+                tmem_ld_32x8(t_p, rpA);
+                tmem_ld_32x8(t_p + 64, rgA);
+#pragma unroll 1
+                for (int c8 = 0; c8 < 8; c8 += 2) {
+                    tmem_ld_wait();
+                    tmem_ld_32x8(t_p + (c8 + 1) * 8, rpB);
+                    tmem_ld_32x8(t_p + 64 + (c8 + 1) * 8, rgB);
+                    emit8(c8, rpA, rgA);
+                    tmem_ld_wait();
+                    if (c8 + 2 < 8) {
+                        tmem_ld_32x8(t_p + (c8 + 2) * 8, rpA);
+                        tmem_ld_32x8(t_p + 64 + (c8 + 2) * 8, rgA);
+                    } else {
+                        // every TMEM read of this side's accumulators has completed: hand them back early
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[side]);
+                        if (leader) TRIMUL_STAMP(4 + side, it, half * 2 + 1);
+                    }
+                    emit8(c8 + 1, rpB, rgB);
+                }
                 fence_proxy_async_smem();
                 named_barrier_sync(bar_id, kF1EpiThreads);
                 if (leader) {

@@ -15,9 +15,14 @@
 // (W*gamma instead of LN(x)); against an fp32 evaluation it is closer than the reference's own
 // bf16 path.
 //
+// A z buffer lives long (load, statistics, epilogue, store), a tri buffer only until its UMMAs
+// and statistics are done, so the z ring is three deep and the tri ring two.  The statistics of a
+// tile travel to the epilogue through the first 2 KB of the tile's own tri buffer, which is dead
+// by then; that leaves shared memory for the third z buffer.
+//
 // Persistent kernel, one CTA per SM, 640 threads, 128-position tiles (z row r, columns j0..j0+127):
 //   warp 0        TMA producer: Wg, Wo once; per tile the z tile and the tri tile [128 channels]
-//                 [128 positions] (channel-major, as the contraction wrote it), 2-stage rings
+//                 [128 positions] (channel-major, as the contraction wrote it)
 //   warp 1        UMMA issuer: gate = z . Wg'^T (z K-major), proj = tri . Wo'^T (tri MN-major, used as
 //                 it lies), 128x128x16 each, into a double-buffered pair of TMEM accumulators
 //   warp 2        store warp: TMA-stores each 64-channel half of a finished tile and hands the z
@@ -40,11 +45,11 @@ namespace trimul {
 constexpr int kG2Threads = 640;
 constexpr int kG2EpiThreads = 256;      // warps 4..11, two groups of 128
 constexpr int kG2StatThreads = 128;     // each of the two statistics groups
-constexpr int kG2StatSlots = 4;
-constexpr int kG2OffZ = kT2WBytes;                          // 2 x 32 KB z ring
-constexpr int kG2OffT = kG2OffZ + 2 * kT2XBytes;            // 2 x 32 KB tri ring
-constexpr int kG2OffStats = kG2OffT + 2 * kT2TBytes;        // [4 slots][128 positions] (r_in, t_in, r_out, t_out)
-constexpr int kG2OffConst = kG2OffStats + kG2StatSlots * 2048;   // [2 matrices][64 channel pairs] (s0, s1, b0, b1)
+constexpr int kG2ZStages = 3;
+constexpr int kG2OffZ = kT2WBytes;                          // 3 x 32 KB z ring
+constexpr int kG2OffT = kG2OffZ + kG2ZStages * kT2XBytes;   // 2 x 32 KB tri ring; once a tile's tri data is dead its
+                                                            // first 2 KB hold [128 positions] (r_in, t_in, r_out, t_out)
+constexpr int kG2OffConst = kG2OffT + 2 * kT2TBytes;        // [2 matrices][64 channel pairs] (s0, s1, b0, b1)
 constexpr int kG2OffBars = kG2OffConst + 2048;
 constexpr int kG2SmemBytes = kG2OffBars + 256;
 constexpr int kG2StatInBarrier = 2;
@@ -107,21 +112,21 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
     uint8_t* sW = smem;
     uint8_t* sZ = smem + kG2OffZ;
     uint8_t* sT = smem + kG2OffT;
-    float4* sStats = reinterpret_cast<float4*>(smem + kG2OffStats);
     float4* sConst = reinterpret_cast<float4*>(smem + kG2OffConst);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kG2OffBars);
     uint64_t* w_full = bars;            // weights landed
     uint64_t* w_ready = bars + 1;       // weights folded (256 arrivals)
-    uint64_t* z_full = bars + 2;        // [2] z tile landed
-    uint64_t* t_full = bars + 4;        // [2] tri tile landed
-    uint64_t* z_empty = bars + 6;       // [2] the store of the tile written over the z tile has read it (1 arrival)
-    uint64_t* t_empty = bars + 8;       // [2] UMMAs retired + 128 statistics threads done
-    uint64_t* acc_full = bars + 10;     // [2]
-    uint64_t* acc_empty = bars + 12;    // [2] (8 arrivals)
-    uint64_t* box_ready = bars + 14;    // [2 stages][2 halves] result half written (4 arrivals)
-    uint64_t* stat_in = bars + 18;      // [4] slot's z statistics written (128 arrivals)
-    uint64_t* stat_out = bars + 22;     // [4] slot's tri statistics written (128 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 26);
+    uint64_t* z_full = bars + 2;        // [3] z tile landed
+    uint64_t* z_empty = bars + 5;       // [3] the store of the tile written over the z tile has read it (1 arrival)
+    uint64_t* box_ready = bars + 8;     // [3 stages][2 halves] result half written (4 arrivals)
+    uint64_t* t_full = bars + 14;       // [2] tri tile landed
+    uint64_t* tri_dead = bars + 16;     // [2] the tile's UMMAs retired + its 128 statistics threads done reading
+    uint64_t* t_empty = bars + 18;      // [2] the epilogue has taken the statistics out of the buffer (8 arrivals)
+    uint64_t* acc_full = bars + 20;     // [2]
+    uint64_t* acc_empty = bars + 22;    // [2] (8 arrivals)
+    uint64_t* stat_in = bars + 24;      // [2] z statistics written into the tri buffer (128 arrivals)
+    uint64_t* stat_out = bars + 26;     // [2] tri statistics written (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 28);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5;
@@ -130,17 +135,18 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
     if (threadIdx.x == 0) {
         mbar_init(w_full, 1);
         mbar_init(w_ready, kG2EpiThreads);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kG2ZStages; ++s) {
             mbar_init(&z_full[s], 1);
-            mbar_init(&t_full[s], 1);
             mbar_init(&z_empty[s], 1);
-            mbar_init(&t_empty[s], 1 + kG2StatThreads);
-            mbar_init(&acc_full[s], 1);
-            mbar_init(&acc_empty[s], 8);
             mbar_init(&box_ready[2 * s], 4);
             mbar_init(&box_ready[2 * s + 1], 4);
         }
-        for (int s = 0; s < kG2StatSlots; ++s) {
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&t_full[s], 1);
+            mbar_init(&tri_dead[s], 1 + kG2StatThreads);
+            mbar_init(&t_empty[s], 8);
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 8);
             mbar_init(&stat_in[s], kG2StatThreads);
             mbar_init(&stat_out[s], kG2StatThreads);
         }
@@ -171,23 +177,24 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1u;
+                const int zs = it % kG2ZStages;
+                const uint32_t zph = (it / kG2ZStages) & 1u;
                 const int j0 = (tile % p.tiles_per_row) * kT2P;
                 const int br = tile / p.tiles_per_row;
                 const int r = br % p.rows;
                 const int b = br / p.rows;
-                // the tri buffer is handed back first (its readers finish before the epilogue starts)
                 if (!mbar_wait(&t_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 100 + s)) break;
                 // tri planes viewed as (column, row, plane, chunk): 64 columns x 128 planes per box
                 mbar_arrive_expect_tx(&t_full[s], kT2TBytes);
                 uint8_t* dt = sT + s * kT2TBytes;
                 tma_load_4d(dt, &tmTri, &t_full[s], j0, r, b * kT2C, 0);
                 tma_load_4d(dt + kT2SubTile, &tmTri, &t_full[s], j0 + 64, r, b * kT2C, 0);
-                if (!mbar_wait(&z_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 110 + s)) break;
+                if (!mbar_wait(&z_empty[zs], zph ^ 1u, abort_flag, p.status, kStageIdTm2, 110 + zs)) break;
                 TRIMUL_STAMP(0, it, 0);
-                mbar_arrive_expect_tx(&z_full[s], kT2XBytes);
-                uint8_t* dz = sZ + s * kT2XBytes;
-                tma_load_4d(dz, &tmZ, &z_full[s], 0, j0, r, b);
-                tma_load_4d(dz + kT2SubTile, &tmZ, &z_full[s], 64, j0, r, b);
+                mbar_arrive_expect_tx(&z_full[zs], kT2XBytes);
+                uint8_t* dz = sZ + zs * kT2XBytes;
+                tma_load_4d(dz, &tmZ, &z_full[zs], 0, j0, r, b);
+                tma_load_4d(dz + kT2SubTile, &tmZ, &z_full[zs], 64, j0, r, b);
             }
         }
         __syncwarp();
@@ -220,11 +227,12 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                                  umma_smem_desc_sw128(wo + (kk >> 2) * kT2SubTile) + (kk & 3) * kDescKStep, idesc_mn,
                                  kk != 0);
                 }
-                umma_commit(&t_empty[s]);
-                if (!mbar_wait(&z_full[s], ph, abort_flag, p.status, kStageIdTm2, 220 + s)) break;
+                umma_commit(&tri_dead[s]);
+                const int zs = it % kG2ZStages;
+                if (!mbar_wait(&z_full[zs], (it / kG2ZStages) & 1u, abort_flag, p.status, kStageIdTm2, 220 + zs)) break;
                 tcgen05_fence_after();
                 TRIMUL_STAMP(1, it, 1);
-                const uint32_t xs = smem_u32(sZ + s * kT2XBytes);
+                const uint32_t xs = smem_u32(sZ + zs * kT2XBytes);
 #pragma unroll 2
                 for (int kk = 0; kk < kT2C / 16; ++kk) {
                     const uint32_t sub = (kk >> 2) * kT2SubTile;
@@ -242,8 +250,8 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
-                const int s = it & 1;
-                const uint32_t ph = (it >> 1) & 1u;
+                const int s = it % kG2ZStages;
+                const uint32_t ph = (it / kG2ZStages) & 1u;
                 const int j0 = (tile % p.tiles_per_row) * kT2P;
                 const int br = tile / p.tiles_per_row;
                 const int r = br % p.rows;
@@ -296,22 +304,23 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         for (int tile = blockIdx.x; run && tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
             const uint32_t ph = (it >> 1) & 1u;
-            const int slot = it & (kG2StatSlots - 1);
-            const uint32_t sph = (it / kG2StatSlots) & 1u;
+            const int zs = it % kG2ZStages;
             bool ok = true;
             if (leader) {
                 ok = mbar_wait(&acc_full[s], ph, abort_flag, p.status, kStageIdTm2, 400 + s) &&
-                     mbar_wait(&stat_in[slot], sph, abort_flag, p.status, kStageIdTm2, 410 + slot) &&
-                     mbar_wait(&stat_out[slot], sph, abort_flag, p.status, kStageIdTm2, 420 + slot);
+                     mbar_wait(&stat_in[s], ph, abort_flag, p.status, kStageIdTm2, 410 + s) &&
+                     mbar_wait(&stat_out[s], ph, abort_flag, p.status, kStageIdTm2, 420 + s);
             }
             if (!named_barrier_all(bar_id, 128, ok)) break;
             tcgen05_fence_after();
             if (e == 0) TRIMUL_STAMP(4, it, 0);
-            const float4 st = sStats[slot * 128 + row];
+            const float4 st = reinterpret_cast<const float4*>(sT + s * kT2TBytes)[row];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&t_empty[s]);    // this warp has its statistics: the tri buffer may be refilled
             const f32x2 rin = f2_pack(st.x, st.x), tin = f2_pack(st.y, st.y);
             const f32x2 rout = f2_pack(st.z, st.z), tout = f2_pack(st.w, st.w);
             const uint32_t t_g = tmem_base + s * 256 + grp * 64 + lane_bits;     // gate; proj 128 columns on
-            uint8_t* tile_row = sZ + s * kT2XBytes + grp * kT2SubTile + row * 128;
+            uint8_t* tile_row = sZ + zs * kT2XBytes + grp * kT2SubTile + row * 128;
             // 8 output channels (one 16-byte chunk) at a time; the TMEM loads of the next 8 are in
             // flight while the current 8 get their statistics, are gated, rounded and written over the
             // z tile.  The loop stays rolled to keep the code small.
@@ -361,7 +370,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             }
             fence_proxy_async_smem();      // result half -> visible to the TMA store (async proxy)
             __syncwarp();
-            if (lane == 0) mbar_arrive(&box_ready[2 * s + grp]);
+            if (lane == 0) mbar_arrive(&box_ready[2 * zs + grp]);
             if (e == 0) TRIMUL_STAMP(4, it, 1);
         }
     } else if (warp < 16) {
@@ -371,17 +380,19 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
             const uint32_t ph = (it >> 1) & 1u;
-            const int slot = it & (kG2StatSlots - 1);
-            if (!group_wait(&z_full[s], ph, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag, p.status,
-                            kStageIdTm2, 300 + s))
+            const int zs = it % kG2ZStages;
+            if (!group_wait(&z_full[zs], (it / kG2ZStages) & 1u, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag,
+                            p.status, kStageIdTm2, 300 + zs))
                 break;
             if (pos == 0) TRIMUL_STAMP(3, it, 0);
             float rstd, t;
-            row_stats(sZ + s * kT2XBytes, kT2SubTile, pos, p.eps_in, rstd, t);
-            // slot it & 3 was last read by the epilogue of tile it - 4; this tile's z load had to wait
-            // for the store of tile it - 2, issued after that epilogue had finished
-            *reinterpret_cast<float2*>(&sStats[slot * 128 + pos]) = make_float2(rstd, t);
-            mbar_arrive(&stat_in[slot]);
+            row_stats(sZ + zs * kT2XBytes, kT2SubTile, pos, p.eps_in, rstd, t);
+            // the statistics go into the tile's tri buffer once nothing reads the tri data any more
+            if (!group_wait(&tri_dead[s], ph, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag, p.status,
+                            kStageIdTm2, 310 + s))
+                break;
+            *reinterpret_cast<float2*>(reinterpret_cast<float4*>(sT + s * kT2TBytes) + pos) = make_float2(rstd, t);
+            mbar_arrive(&stat_in[s]);
             if (pos == 0) TRIMUL_STAMP(3, it, 1);
         }
     } else {
@@ -401,7 +412,6 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
             const uint32_t ph = (it >> 1) & 1u;
-            const int slot = it & (kG2StatSlots - 1);
             if (!group_wait(&t_full[s], ph, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag, p.status,
                             kStageIdTm2, 500 + s))
                 break;
@@ -452,12 +462,13 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             const float m1 = s1[0] * inv_c;
             const float rstd = rsqrtf(fmaxf(fmaf(-m1, m1, s2[0] * inv_c), 0.f) + p.eps_out);
             const float t = -(shift + m1) * rstd;
-            mbar_arrive(&t_empty[s]);                   // this thread is done with the tri tile
-            // position 8 cq + rs == tid.  Slot it & 3 was last read by the epilogue of tile it - 4, which
-            // had drained its accumulators before the UMMAs of tile it - 2 (whose retirement this
-            // tile's load waited for) could start
-            *(reinterpret_cast<float2*>(&sStats[slot * 128 + tid]) + 1) = make_float2(rstd, t);
-            mbar_arrive(&stat_out[slot]);
+            mbar_arrive(&tri_dead[s]);                  // this thread is done with the tri data
+            if (!group_wait(&tri_dead[s], ph, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag, p.status,
+                            kStageIdTm2, 510 + s))
+                break;
+            // position 8 cq + rs == tid
+            *(reinterpret_cast<float2*>(reinterpret_cast<float4*>(sT + s * kT2TBytes) + tid) + 1) = make_float2(rstd, t);
+            mbar_arrive(&stat_out[s]);
             if (tid == 0) TRIMUL_STAMP(5, it, 1);
         }
     }

@@ -234,7 +234,7 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_col_chunk = eff_chunk(a->col_chunk, a->cols);
     p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
     p.status = status;
-    if ((d->flags & TRIMUL_FLAG_FOLDED_NORM) != 0) {
+    if ((d->flags & TRIMUL_FLAG_FOLDED_STAGE1) != 0) {
         // LayerNorm folded into the weights, which live in tensor memory
         Tm1FoldParams fp;
         fp.base = p;
@@ -364,8 +364,9 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     p.has_residual = residual != nullptr;
     p.status = status;
     const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-    if ((d->flags & TRIMUL_FLAG_FOLDED_NORM) != 0 && (residual == nullptr || residual == z)) {
-        // both LayerNorms folded into the weights, result written in place over the z tile
+    if ((d->flags & TRIMUL_FLAG_INPLACE_NORM_STAGE3) == 0 && (residual == nullptr || residual == z)) {
+        // default: both LayerNorms folded into the weights, result written in place over the z tile
+        // (a residual other than z itself needs a tile buffer this kernel does not have)
         Tm2FoldParams fp;
         fp.base = p;
         fp.residual_is_z = residual != nullptr;

@@ -132,10 +132,13 @@ def trimul_forward(
     eps_out: float = 1e-5,
     residual: torch.Tensor | None = None,
     plain_kernels: bool = False,
+    inplace_norm: bool = False,
 ) -> torch.Tensor:
     """One block call on the current CUDA stream.  ``mask`` is a ``[B,N]`` token mask, a
     ``[B,N,N]`` pair mask or None; ``residual`` (same shape/dtype as ``x``) is added to the
-    result when given."""
+    result when given.  Passing ``x`` itself as the residual (the block's ``pair + update`` form)
+    costs nothing extra: the last stage adds the tile it already holds.  ``plain_kernels`` and
+    ``inplace_norm`` select cross-checking variants of the kernels (see the flags in the C header)."""
     if x.dim() != 4 or x.shape[1] != x.shape[2]:
         raise ValueError(f"x must be [B, N, N, c], got {tuple(x.shape)}")
     _require_cuda(x, "x")
@@ -163,7 +166,8 @@ def trimul_forward(
     lib = _lib.load()
     desc = _lib.make_desc(B, N, c, dtype=code, direction=_lib.OUTGOING if outgoing else _lib.INCOMING,
                           mask_kind=mask_kind, eps_in=eps_in, eps_out=eps_out,
-                          flags=_lib.FLAG_PLAIN_KERNELS if plain_kernels else 0)
+                          flags=(_lib.FLAG_PLAIN_KERNELS if plain_kernels else 0) |
+                          (_lib.FLAG_INPLACE_NORM_STAGE3 if inplace_norm else 0))
     w, keep = _weights_struct(c, x.dtype, ln_in_weight, ln_in_bias, w_left, w_left_gate, w_right, w_right_gate,
                               ln_out_weight, ln_out_bias, w_gate, w_out, x.device)
     nbytes = C.c_size_t()

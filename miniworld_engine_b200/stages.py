@@ -97,14 +97,16 @@ def dense_to_planes(spec: PlaneSpec, dense: torch.Tensor) -> None:
         spec.buf[: P * spec.plane_stride].view(P, spec.rows, spec.pitch)[..., :spec.cols].copy_(dense)
 
 
-def _desc(x, N, outgoing, mask_kind, eps_in, eps_out, plain, row0, pair_stage1=False, folded_norm=False):
+def _desc(x, N, outgoing, mask_kind, eps_in, eps_out, plain, row0, pair_stage1=False, folded_stage1=False,
+          inplace_norm=False):
     B, rows, _, c = x.shape
     return _lib.make_desc(B, N, c, dtype=_dtype_code(x),
                           direction=_lib.OUTGOING if outgoing else _lib.INCOMING, mask_kind=mask_kind,
                           eps_in=eps_in, eps_out=eps_out,
                           flags=(_lib.FLAG_PLAIN_KERNELS if plain else 0) |
                           (_lib.FLAG_PAIR_STAGE1 if pair_stage1 else 0) |
-                          (_lib.FLAG_FOLDED_NORM if folded_norm else 0),
+                          (_lib.FLAG_FOLDED_STAGE1 if folded_stage1 else 0) |
+                          (_lib.FLAG_INPLACE_NORM_STAGE3 if inplace_norm else 0),
                           rows=rows, row0=row0)
 
 
@@ -122,12 +124,12 @@ def _mask_arg(mask, B, N):
 
 def tm1(z_slab: torch.Tensor, mask, weights: dict, a: PlaneSpec, b: PlaneSpec, *, outgoing: bool,
         row0: int = 0, eps: float = 1e-5, plain_kernels: bool = False, pair_stage1: bool = False,
-        folded_norm: bool = False) -> None:
+        folded_stage1: bool = False) -> None:
     """Stage 1 on a ``[B, rows, N, c]`` slab of z (rows ``row0 .. row0+rows`` of the grid)."""
     _require_cuda(z_slab, "z")
     B, rows, N, c = z_slab.shape
     kind, mask_u8 = _mask_arg(mask, B, N)
-    d = _desc(z_slab, N, outgoing, kind, eps, eps, plain_kernels, row0, pair_stage1, folded_norm)
+    d = _desc(z_slab, N, outgoing, kind, eps, eps, plain_kernels, row0, pair_stage1, folded_stage1)
     w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, **weights)
     st = _status_words(z_slab.device)
     with torch.cuda.device(z_slab.device):
@@ -157,11 +159,11 @@ def contract(a: PlaneSpec, b: PlaneSpec, tri: PlaneSpec, *, plain_kernels: bool 
 
 def tm2(z_slab: torch.Tensor, tri: PlaneSpec, weights: dict, *, residual=None, row0: int = 0,
         eps_in: float = 1e-5, eps_out: float = 1e-5, plain_kernels: bool = False,
-        folded_norm: bool = False) -> torch.Tensor:
+        inplace_norm: bool = False) -> torch.Tensor:
     """Stage 3 on a ``[B, rows, N, c]`` slab; returns the matching output slab."""
     _require_cuda(z_slab, "z")
     B, rows, N, c = z_slab.shape
-    d = _desc(z_slab, N, True, _lib.MASK_NONE, eps_in, eps_out, plain_kernels, row0, False, folded_norm)
+    d = _desc(z_slab, N, True, _lib.MASK_NONE, eps_in, eps_out, plain_kernels, row0, False, False, inplace_norm)
     w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, **weights)
     out = torch.empty_like(z_slab)
     st = _status_words(z_slab.device)

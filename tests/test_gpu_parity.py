@@ -126,11 +126,23 @@ def test_mask_none_equals_all_ones_and_batches_are_independent(dev):
 
 
 def test_residual_matches_reference_module_semantics(dev):
+    """out + pair is a bf16 add of the bf16-rounded block output (module.py:453).  The residual
+    that IS the input takes the default last stage (it adds the z tile it already holds); any
+    other residual tensor takes the in-place-normalising variant, which has a tile buffer for it."""
+    from miniworld_engine_b200 import read_status, trimul_forward
     w, z = O.make_weights(128, 0), O.make_input(1, 130, 128, 1)
-    zb = z.bfloat16()
-    y = run_block(z, None, w, True, torch.bfloat16, dev)
-    yr = run_block(z, None, w, True, torch.bfloat16, dev, residual=zb.to(dev))
-    assert torch.equal(yr, y + zb)       # bf16 add of the bf16-rounded block output, module.py:453
+    kw = forward_kwargs(w, torch.bfloat16, dev)
+    zd = z.bfloat16().to(dev)
+    other = O.make_input(1, 130, 128, 7).bfloat16().to(dev)
+    y = trimul_forward(zd, None, outgoing=True, **kw)
+    yr = trimul_forward(zd, None, outgoing=True, residual=zd, **kw)
+    assert torch.equal(yr, y + zd)
+    y_inplace = trimul_forward(zd, None, outgoing=True, inplace_norm=True, **kw)
+    yo = trimul_forward(zd, None, outgoing=True, residual=other, **kw)
+    assert torch.equal(yo, y_inplace + other)
+    yz = trimul_forward(zd, None, outgoing=True, residual=zd.clone(), **kw)
+    assert torch.equal(yz, y_inplace + zd)
+    assert read_status(dev)[0] == 0
 
 
 def test_tensor_core_kernels_match_plain_kernels(dev):
@@ -213,7 +225,37 @@ def test_alternative_kernels_agree(dev):
         S.contract(res[0][2], res[0][3], t1)
         S.contract(res[0][2], res[0][3], t2, single_cta=True)
         assert torch.equal(S.planes_to_dense(t1), S.planes_to_dense(t2))
+        # stage 1 with the LayerNorm folded into weights held in tensor memory: rounds W*gamma
+        # instead of LN(x) to bf16, so it agrees with the default to bf16 noise, not bit for bit
+        a = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
+        b = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
+        S.tm1(z, m, wd, a, b, outgoing=outgoing, folded_stage1=True)
+        assert O.rel_rms(S.planes_to_dense(a).float().cpu(), res[0][0].float().cpu()) <= 5e-3
+        assert O.rel_rms(S.planes_to_dense(b).float().cpu(), res[0][1].float().cpu()) <= 5e-3
+        # stage 3: default (both LayerNorms folded into the weights) against the in-place variant,
+        # with and without the residual
+        for residual in (None, z):
+            y_fold = S.tm2(z, t1, wd, residual=residual)
+            y_inpl = S.tm2(z, t1, wd, residual=residual, inplace_norm=True)
+            assert O.rel_rms(y_fold.float().cpu(), y_inpl.float().cpu()) <= 6e-3
     assert read_status(dev)[0] == 0
+
+
+def test_folded_norm_is_no_further_from_fp32_than_the_reference_bf16_path(dev):
+    """The default stage 3 rounds W*gamma to bf16 where the reference rounds LN(x).  Neither is
+    'the' answer; measured against an fp32 evaluation of the same bf16 inputs the folded form must
+    not be worse than the reference's own bf16 path (plus a little slack)."""
+    from miniworld_engine_b200 import trimul_forward
+    from tests._util import forward_kwargs
+    for affine, shift in (("unit", 0.0), ("random", 0.0), ("random", 4.0)):
+        w = O.make_weights(128, 3, affine=affine)
+        z = (O.make_input(1, 192, 128, 5) + shift).bfloat16()
+        wb = w.to(torch.bfloat16)
+        truth = O.trimul_forward(z.float(), None, wb.to(torch.float32), True)
+        ref_bf16 = O.trimul_forward(z, None, wb, True).float()
+        y = trimul_forward(z.to(dev), None, outgoing=True, **forward_kwargs(w, torch.bfloat16, dev)).float().cpu()
+        e_ref, e_ours = O.rel_rms(ref_bf16, truth), O.rel_rms(y, truth)
+        assert e_ours <= 1.1 * e_ref, f"{affine}, shift {shift}: ours {e_ours:.3e} vs reference bf16 {e_ref:.3e}"
 
 
 def test_cuda_graph_capture_and_replay(dev):
