@@ -395,7 +395,7 @@ def run_sharded_pair(args):
     import torch.distributed as dist
     from oracle import trimul_oracle as O
     from miniworld_engine_b200 import read_status, stages as S
-    from miniworld_engine_b200.sharded import ChannelShardPlan, ShardPlan, exchange
+    from miniworld_engine_b200.sharded import ChannelShardPlan, PeerShardContext, ShardPlan, exchange
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -425,10 +425,18 @@ def run_sharded_pair(args):
                     ln_out_b=w.ln_out_bias.to(dev), w_gate=w.to_gate.to(dev), w_out=w.to_out.to(dev))
 
     w_out, w_in = wdict(0), wdict(3)
-    channels = args.shard_mode == "channels"
+    peer = args.shard_mode == "peer"
+    channels = args.shard_mode == "channels" or peer
     Plan = ChannelShardPlan if channels else ShardPlan
     plans = {True: Plan(B, N, c, world, rank, True), False: Plan(B, N, c, world, rank, False)}
-    bufs = {k: p.alloc(torch.bfloat16, dev) for k, p in plans.items()}
+    if peer:
+        if world == 1:
+            dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1, device_id=dev)
+        ctx = PeerShardContext(B, N, c, torch.bfloat16, dev)
+        bufs = {k: {"a_recv": ctx._local["a"], "b_recv": ctx._local["b"], "tri_send": ctx._local["tri"],
+                    "tri_recv": ctx._local["tri"]} for k in plans}
+    else:
+        bufs = {k: p.alloc(torch.bfloat16, dev) for k, p in plans.items()}
 
     def mark(ev):
         ev.append(torch.cuda.Event(enable_timing=True))
@@ -449,7 +457,25 @@ def run_sharded_pair(args):
         mark(ev)
         return y
 
+    def block_peer(x, wd, outgoing, ev):
+        # the exchanges are the stores of the scattering kernels; only barriers stand between stages
+        p, bf = plans[outgoing], bufs[outgoing]
+        a_dest, b_dest, tri_dest = ctx._dest[outgoing]
+        S.tm1_scatter(x, m, wd, a_dest, b_dest, outgoing=outgoing, row0=p.row0)
+        mark(ev)
+        ctx.barrier()
+        a_r, b_r, _ = p.contract_operands(bf)
+        S.contract_scatter(a_r, b_r, tri_dest)
+        mark(ev)
+        ctx.barrier()
+        mark(ev)
+        y = S.tm2(x, p.tri_spec(bf), wd, row0=p.row0)
+        mark(ev)
+        return y
+
     def block(x, wd, outgoing, ev):
+        if peer:
+            return block_peer(x, wd, outgoing, ev)
         if channels:
             return block_channels(x, wd, outgoing, ev)
         p = plans[outgoing]
@@ -488,7 +514,8 @@ def run_sharded_pair(args):
     barrier()
     clocks = sampler.stop() if sampler else None
     total_ms = all_ev[0][0].elapsed_time(all_ev[-1][-1])
-    names = ["tm1", "a2a_in+contract", "a2a_out", "tm2"] if channels else ["tm1", "exchange", "contract", "tm2"]
+    names = (["tm1+scatter", "barrier+contract+scatter", "barrier", "tm2"] if peer else
+             ["tm1", "a2a_in+contract", "a2a_out", "tm2"] if channels else ["tm1", "exchange", "contract", "tm2"])
     stage_ms = [sum(e[i].elapsed_time(e[i + 1]) + e[i + 4].elapsed_time(e[i + 5]) for e in all_ev) / args.steps
                 for i in range(4)]
     if read_status(dev)[0] != 0:
@@ -513,6 +540,8 @@ def run_sharded_pair(args):
             "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["bf16_tflops"],
             "config": {"workload": args.workload, "B": B, "N": N, "c": c, "direction": "outgoing then incoming",
                        "mask": mask_kind, "parallelism": (f"rows sharded over {world} GPU(s), contraction sharded over channel planes, "
+                                       "exchanges done by the kernels' own TMA stores into peer memory, two barriers per block")
+                       if peer else (f"rows sharded over {world} GPU(s), contraction sharded over channel planes, "
                                        "three all-to-alls per block") if channels else
                        (f"output rows sharded over {world} GPU(s), all-gather of b per block, "
                         "all-to-all of a for the incoming block"),
@@ -522,7 +551,7 @@ def run_sharded_pair(args):
             "clocks": clocks,
         }
         print(json.dumps(line), flush=True)
-    if world > 1:
+    if world > 1 or peer:
         dist.destroy_process_group()
 
 
@@ -534,7 +563,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="n768_outgoing", choices=sorted(WORKLOADS) + sorted(PAIR_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shard-mode", default="rows", choices=["rows", "channels"],
+    ap.add_argument("--shard-mode", default="rows", choices=["rows", "channels", "peer"],
                     help="exchange pattern of the *_pair_sharded workloads")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -194,6 +194,31 @@ int trimul_b200_contract(int32_t dtype, uint32_t flags, int32_t planes,
                          void* stream, int32_t* status);
 
 /*
+ * Scattering variants of stages 1 and 2, for a contraction that is sharded over channel planes
+ * across several GPUs of one node.  They have NO counterpart in the reference, which runs on a
+ * single GPU: they are the exchange steps of the multi-GPU plan, performed by the producing
+ * kernels' own stores instead of by separate collectives.
+ *
+ * trimul_b200_tm1_scatter: as trimul_b200_tm1, but planes [k*P, (k+1)*P), P = B*c / n_dest, are
+ * written to a_dest[k] / b_dest[k] (plane index inside a destination counts from 0).
+ * trimul_b200_contract_scatter: as trimul_b200_contract, but output rows [k*R, (k+1)*R),
+ * R = rows_a / n_dest, are written to tri_dest[k] (row index inside a destination counts from 0).
+ * Destination buffers may lie in another GPU's memory that is mapped into this process (peer
+ * access); all destinations of one call share one geometry and only differ in `base`.
+ * The calls order nothing between GPUs: the caller puts a cross-GPU barrier between a scattering
+ * stage and the stage that consumes what other GPUs scattered.  1 <= n_dest <= 8.  Only the
+ * tensor-core kernels scatter: bf16, c = 128, P a multiple of 8 that divides or is a multiple of
+ * 128, R a multiple of 128; anything else returns TRIMUL_E_UNSUPPORTED and the caller falls back
+ * to the plain stages plus a collective.
+ */
+int trimul_b200_tm1_scatter(const trimul_desc* desc, const void* z, const uint8_t* mask,
+                            const trimul_weights* w, int32_t n_dest, const trimul_planes* a_dest,
+                            const trimul_planes* b_dest, void* stream, int32_t* status);
+int trimul_b200_contract_scatter(int32_t dtype, uint32_t flags, int32_t planes,
+                                 const trimul_planes* a, const trimul_planes* b, int32_t n_dest,
+                                 const trimul_planes* tri_dest, void* stream, int32_t* status);
+
+/*
  * Stage 3: LayerNorm_out over the channels of tri, the output projection, the output gate
  * computed from a fresh LayerNorm_in of the z slab (unmasked, reference.py:83), optional
  * residual; writes out [B, rows, N, c].  tri planes are [B*c][rows][N] for both directions.

@@ -16,6 +16,10 @@
 //   empty[s]     in each CTA; the leader's tcgen05.commit arrives on both (commit multicast)
 //   acc_full[a]  in each CTA; commit multicast
 //   acc_empty[a] in the leader, 8 arrivals: the four epilogue warps of each CTA (remote arrive)
+//
+// kScatter = true: the output rows are split into row chunks of d_row_chunk rows and chunk d is
+// stored through destination map d (the multi-GPU exchange of the channel-sharded contraction,
+// done by the producing kernel's own TMA stores: chunk d is GPU d's slab of rows).
 #pragma once
 
 #include "contract_sm100.cuh"
@@ -28,9 +32,11 @@ constexpr int kC2StageBytes = 2 * kC2HalfBytes;          // this CTA's A half + 
 constexpr int kC2SmemBytes = kC2Stages * kC2StageBytes + kCtStagingBytes + kCtBarBytes;
 constexpr int kC2EpiBarrier = 1;
 
+template <bool kScatter>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kCtThreads, 1)
 contract2_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                       const __grid_constant__ CUtensorMap tmD, const ContractParams p) {
+                       const __grid_constant__ CUtensorMap tmD, const ContractParams p,
+                       const __grid_constant__ ScatterMaps sc) {
     extern __shared__ __align__(1024) uint8_t smem[];
     // (a misaligned dynamic shared-memory base would be the same in both CTAs: uniform exit)
     if ((smem_u32(smem) & 1023u) != 0u) {
@@ -194,8 +200,11 @@ contract2_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
                 fence_proxy_async_smem();
                 named_barrier_sync(kC2EpiBarrier, 128);
                 if (leader_thread) {
-                    tma_store_4d(&tmD, buf, col0 % p.d_col_chunk, row_d % p.d_row_chunk, plane,
-                                 col0 / p.d_col_chunk + row_d / p.d_row_chunk);
+                    if (kScatter)   // this CTA's 128 rows lie inside one destination's row chunk
+                        tma_store_4d(&sc.map[row_d / p.d_row_chunk], buf, col0, row_d % p.d_row_chunk, plane, 0);
+                    else
+                        tma_store_4d(&tmD, buf, col0 % p.d_col_chunk, row_d % p.d_row_chunk, plane,
+                                     col0 / p.d_col_chunk + row_d / p.d_row_chunk);
                     tma_store_commit();
                 }
             }

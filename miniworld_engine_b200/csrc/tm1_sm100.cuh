@@ -22,6 +22,10 @@
 // All worker warps first halve the weight matrices in shared memory (exact in bf16), so the
 // accumulators hold p/2 and g/2 and p*sigmoid(g) = (p/2)*tanh(g/2) + p/2 is one MUFU + one FMA.
 //
+// kScatter = true: the 128 channel planes of a tile are stored in segments of planes_per_dest
+// planes, segment k through destination map (first plane of the segment) / planes_per_dest — the
+// multi-GPU exchange of the channel-sharded contraction, done by this kernel's own TMA stores.
+//
 // A tile is 128 consecutive positions along the index that becomes the contraction's k: for the
 // outgoing direction z row f, columns t0..t0+127; for the incoming direction z column f, rows
 // t0..t0+127 (a strided TMA box), so both directions store plane element (f, t0+p).
@@ -65,14 +69,17 @@ struct Tm1Params {
     const float* beta;
     float eps;
     int a_row_chunk, a_col_chunk, b_row_chunk, b_col_chunk;
+    int planes_per_dest;  // scatter variant: planes of one destination (a multiple of 8; divides or is a multiple of 128)
     int32_t* status;
 };
 
+template <bool kScatter>
 __global__ void __launch_bounds__(kT1Threads, 1)
 tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWl,
                  const __grid_constant__ CUtensorMap tmWlg, const __grid_constant__ CUtensorMap tmWr,
                  const __grid_constant__ CUtensorMap tmWrg, const __grid_constant__ CUtensorMap tmA,
-                 const __grid_constant__ CUtensorMap tmB, const Tm1Params p) {
+                 const __grid_constant__ CUtensorMap tmB, const Tm1Params p,
+                 const __grid_constant__ ScatterMaps scA, const __grid_constant__ ScatterMaps scB) {
     extern __shared__ __align__(1024) uint8_t smem[];
     if ((smem_u32(smem) & 1023u) != 0u) {
         if (threadIdx.x == 0) report_timeout(p.status, kStageIdTm1, 900);
@@ -244,6 +251,7 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         const int bar_id = kT1EpiBarrier + side;
         uint8_t* stg = sOut + side * kT1SubTile;
         const CUtensorMap* om = side == 0 ? &tmA : &tmB;
+        const ScatterMaps* sm = side == 0 ? &scA : &scB;
         const int rc = side == 0 ? p.a_row_chunk : p.b_row_chunk;
         const int cc = side == 0 ? p.a_col_chunk : p.b_col_chunk;
         const uint32_t t_p = tmem_base + side * 256 + ((uint32_t)(q * 32) << 16);
@@ -304,7 +312,17 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                 if (leader) {
                     const int col0 = t0 + half * 64;
                     if (col0 < p.n_run) {
-                        tma_store_4d(om, stg, col0 % cc, f % rc, b * kT1C, col0 / cc + f / rc);
+                        if (kScatter) {
+                            const int seg = p.planes_per_dest < kT1C ? p.planes_per_dest : kT1C;
+                            for (int k0 = 0; k0 < kT1C; k0 += seg) {
+                                const int plane = b * kT1C + k0;
+                                const int d = plane / p.planes_per_dest;
+                                tma_store_4d(&sm->map[d], stg + k0 * 128, col0 % cc, f % rc,
+                                             plane - d * p.planes_per_dest, col0 / cc + f / rc);
+                            }
+                        } else {
+                            tma_store_4d(om, stg, col0 % cc, f % rc, b * kT1C, col0 / cc + f / rc);
+                        }
                         tma_store_commit();
                     }
                 }

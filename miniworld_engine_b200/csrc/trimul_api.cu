@@ -193,8 +193,10 @@ int run_plain_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, cons
     return launch_status();
 }
 
+// `n_dest` == 0: a and b are single plane sets.  `n_dest` > 0: a[k] and b[k], k < n_dest, are the
+// buffers that receive planes [k * P, (k + 1) * P), P = B * 128 / n_dest (identical geometry).
 int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
-                 const trimul_planes* a, const trimul_planes* b, cudaStream_t st, int32_t* status) {
+                 const trimul_planes* a, const trimul_planes* b, cudaStream_t st, int32_t* status, int n_dest = 0) {
     const bool inc = d->direction == TRIMUL_INCOMING;
     const bool pair = (d->flags & TRIMUL_FLAG_PAIR_STAGE1) != 0 && sm_count() >= 2;
     const uint32_t zpos = pair ? 64 : 128;       // positions one CTA loads per tile
@@ -214,9 +216,22 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
         if (!encode_bf16(&tmW[m], ws[m], 2, dims, strides, box, 128)) return TRIMUL_E_CUDA;
     }
     const int planes = d->B * 128;
-    // stores of a and b: 64 positions x 128 planes per box
-    if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
-    if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+    ScatterMaps scA, scB;
+    const int planes_per_dest = n_dest > 0 ? planes / n_dest : planes;
+    if (n_dest > 0) {
+        // stores of a and b: 64 positions x one destination's share of the 128 planes per box
+        const uint32_t seg = planes_per_dest < 128 ? planes_per_dest : 128;
+        for (int k = 0; k < n_dest; ++k) {
+            if (!encode_planes(&scA.map[k], a[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
+            if (!encode_planes(&scB.map[k], b[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
+        }
+        tmA = scA.map[0];
+        tmB = scB.map[0];
+    } else {
+        // stores of a and b: 64 positions x 128 planes per box
+        if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+        if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+    }
 
     Tm1Params p;
     p.B = d->B; p.c = 128;
@@ -233,7 +248,15 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     p.gamma = w->ln_in_weight; p.beta = w->ln_in_bias; p.eps = d->eps_in;
     p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_col_chunk = eff_chunk(a->col_chunk, a->cols);
     p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
+    p.planes_per_dest = planes_per_dest;
     p.status = status;
+    if (n_dest > 0) {
+        if (!ensure_smem(tm1_sm100_kernel<true>, kT1SmemBytes)) return TRIMUL_E_CUDA;
+        const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+        tm1_sm100_kernel<true><<<grid, kT1Threads, kT1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p,
+                                                                     scA, scB);
+        return launch_status();
+    }
     if ((d->flags & TRIMUL_FLAG_FOLDED_STAGE1) != 0) {
         // LayerNorm folded into the weights, which live in tensor memory
         Tm1FoldParams fp;
@@ -253,9 +276,10 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
                                                                              tmA, tmB, p);
         return launch_status();
     }
-    if (!ensure_smem(tm1_sm100_kernel, kT1SmemBytes)) return TRIMUL_E_CUDA;
+    if (!ensure_smem(tm1_sm100_kernel<false>, kT1SmemBytes)) return TRIMUL_E_CUDA;
     const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-    tm1_sm100_kernel<<<grid, kT1Threads, kT1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p);
+    tm1_sm100_kernel<false><<<grid, kT1Threads, kT1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p,
+                                                                  scA, scB);
     return launch_status();
 }
 
@@ -284,12 +308,18 @@ bool fast_contract_ok(const trimul_planes* a, const trimul_planes* b, const trim
     return true;
 }
 
+// `n_dest` == 0: t is one plane set.  `n_dest` > 0 (pair kernel only): t[k], k < n_dest, receives
+// output rows [k * R, (k + 1) * R), R = rows_a / n_dest (identical geometry, R a multiple of 128).
 int run_fast_contract(int planes, const trimul_planes* a, const trimul_planes* b, const trimul_planes* t,
-                      cudaStream_t st, int32_t* status, bool pair) {
+                      cudaStream_t st, int32_t* status, bool pair, int n_dest = 0) {
     CUtensorMap tmA, tmB, tmD;
+    ScatterMaps sc;
     if (!encode_planes(&tmA, *a, planes, kCtBK, kCtBM, 1)) return TRIMUL_E_CUDA;
     if (!encode_planes(&tmB, *b, planes, kCtBK, pair ? 128 : kCtBN, 1)) return TRIMUL_E_CUDA;
-    if (!encode_planes(&tmD, *t, planes, 64, kCtBM, 1)) return TRIMUL_E_CUDA;
+    for (int k = 0; k < n_dest; ++k)
+        if (!encode_planes(&sc.map[k], t[k], planes, 64, kCtBM, 1)) return TRIMUL_E_CUDA;
+    if (n_dest > 0) tmD = sc.map[0];
+    else if (!encode_planes(&tmD, *t, planes, 64, kCtBM, 1)) return TRIMUL_E_CUDA;
     ContractParams p;
     p.planes = planes;
     p.rows_a = (int)a->rows; p.rows_b = (int)b->rows; p.K = (int)a->cols;
@@ -299,17 +329,24 @@ int run_fast_contract(int planes, const trimul_planes* a, const trimul_planes* b
     p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_k_chunk = eff_chunk(a->col_chunk, a->cols);
     p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_k_chunk = eff_chunk(b->col_chunk, b->cols);
     p.d_row_chunk = eff_chunk(t->row_chunk, t->rows); p.d_col_chunk = eff_chunk(t->col_chunk, t->cols);
+    if (n_dest > 0) { p.d_row_chunk = (int)t->rows; p.d_col_chunk = (int)t->cols; }
     p.status = status;
     if (pair) {
         // CTA pairs: 256 x 256 tiles, one cluster of two CTAs per tile
         const int64_t pair_tiles = (int64_t)planes * ((p.rows_a + 255) / 256) * ((p.rows_b + 255) / 256);
         if (pair_tiles > 0x3fffffff) return TRIMUL_E_UNSUPPORTED;
-        if (!ensure_smem(contract2_sm100_kernel, kC2SmemBytes)) return TRIMUL_E_CUDA;
         const int max_clusters = sm_count() / 2;
         const int clusters = pair_tiles < max_clusters ? (int)pair_tiles : max_clusters;
-        contract2_sm100_kernel<<<2 * clusters, kCtThreads, kC2SmemBytes, st>>>(tmA, tmB, tmD, p);
+        if (n_dest > 0) {
+            if (!ensure_smem(contract2_sm100_kernel<true>, kC2SmemBytes)) return TRIMUL_E_CUDA;
+            contract2_sm100_kernel<true><<<2 * clusters, kCtThreads, kC2SmemBytes, st>>>(tmA, tmB, tmD, p, sc);
+        } else {
+            if (!ensure_smem(contract2_sm100_kernel<false>, kC2SmemBytes)) return TRIMUL_E_CUDA;
+            contract2_sm100_kernel<false><<<2 * clusters, kCtThreads, kC2SmemBytes, st>>>(tmA, tmB, tmD, p, sc);
+        }
         return launch_status();
     }
+    if (n_dest > 0) return TRIMUL_E_UNSUPPORTED;
     const int64_t total = (int64_t)planes * p.tiles_m * p.tiles_n;
     if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
     if (!ensure_smem(contract_sm100_kernel, kCtSmemBytes)) return TRIMUL_E_CUDA;
@@ -478,6 +515,75 @@ int trimul_b200_contract(int32_t dtype, uint32_t flags, int32_t planes, const tr
         if (pair && fast_contract_ok(a, b, tri, false)) return run_fast_contract(planes, a, b, tri, st, status, false);
     }
     return run_plain_contract<__nv_bfloat16>(planes, a, b, tri, st);
+}
+
+namespace {
+// all destination buffers of a scattering call must share one geometry (only the base differs)
+bool same_geometry(const trimul_planes* v, int n) {
+    for (int k = 1; k < n; ++k)
+        if (v[k].rows != v[0].rows || v[k].cols != v[0].cols || v[k].pitch != v[0].pitch ||
+            v[k].plane_stride != v[0].plane_stride || v[k].chunk_stride != v[0].chunk_stride ||
+            v[k].row_chunk != v[0].row_chunk || v[k].col_chunk != v[0].col_chunk)
+            return false;
+    return true;
+}
+}  // namespace
+
+int trimul_b200_tm1_scatter(const trimul_desc* desc, const void* z, const uint8_t* mask, const trimul_weights* w,
+                            int32_t n_dest, const trimul_planes* a_dest, const trimul_planes* b_dest, void* stream,
+                            int32_t* status) {
+    int rc = check_desc(desc);
+    if (rc != TRIMUL_OK) return rc;
+    if ((rc = check_weights(w)) != TRIMUL_OK) return rc;
+    if (z == nullptr || !aligned16(z) || a_dest == nullptr || b_dest == nullptr) return TRIMUL_E_INVALID;
+    if (desc->mask_kind != TRIMUL_MASK_NONE && mask == nullptr) return TRIMUL_E_INVALID;
+    if (n_dest < 1 || n_dest > kMaxDest) return TRIMUL_E_INVALID;
+    const int64_t planes = (int64_t)desc->B * desc->c;
+    if (planes % n_dest != 0) return TRIMUL_E_INVALID;
+    const int64_t per = planes / n_dest;
+    const bool inc = desc->direction == TRIMUL_INCOMING;
+    const int64_t prow = inc ? desc->N : desc->rows, pcol = inc ? desc->rows : desc->N;
+    for (int k = 0; k < n_dest; ++k) {
+        if ((rc = check_planes(&a_dest[k], prow, pcol)) != TRIMUL_OK) return rc;
+        if ((rc = check_planes(&b_dest[k], prow, pcol)) != TRIMUL_OK) return rc;
+        if (((reinterpret_cast<uintptr_t>(a_dest[k].base) | reinterpret_cast<uintptr_t>(b_dest[k].base)) & 127u) != 0)
+            return TRIMUL_E_INVALID;
+    }
+    if (!same_geometry(a_dest, n_dest) || !same_geometry(b_dest, n_dest)) return TRIMUL_E_INVALID;
+    // tensor-core kernel only: a destination's share must be whole 8-plane groups of a 128-plane tile
+    if (!tensor_core_path(desc)) return TRIMUL_E_UNSUPPORTED;
+    if (per % 8 != 0 || !(128 % per == 0 || per % 128 == 0)) return TRIMUL_E_UNSUPPORTED;
+    if ((a_dest->col_chunk < a_dest->cols && a_dest->col_chunk % 64) ||
+        (b_dest->col_chunk < b_dest->cols && b_dest->col_chunk % 64))
+        return TRIMUL_E_UNSUPPORTED;
+    return run_fast_tm1(desc, z, mask, w, a_dest, b_dest, static_cast<cudaStream_t>(stream), status, n_dest);
+}
+
+int trimul_b200_contract_scatter(int32_t dtype, uint32_t flags, int32_t planes, const trimul_planes* a,
+                                 const trimul_planes* b, int32_t n_dest, const trimul_planes* tri_dest, void* stream,
+                                 int32_t* status) {
+    (void)flags;
+    if (a == nullptr || b == nullptr || tri_dest == nullptr) return TRIMUL_E_INVALID;
+    if (planes <= 0 || planes > 65535) return TRIMUL_E_INVALID;
+    if (dtype != TRIMUL_DTYPE_BF16 && dtype != TRIMUL_DTYPE_FP32) return TRIMUL_E_INVALID;
+    if (n_dest < 1 || n_dest > kMaxDest) return TRIMUL_E_INVALID;
+    int rc;
+    if ((rc = check_planes(a, a->rows, a->cols)) != TRIMUL_OK) return rc;
+    if ((rc = check_planes(b, b->rows, a->cols)) != TRIMUL_OK) return rc;
+    if (a->rows <= 0 || b->rows <= 0 || a->cols <= 0 || a->rows % n_dest != 0) return TRIMUL_E_INVALID;
+    const int64_t R = a->rows / n_dest;
+    for (int k = 0; k < n_dest; ++k) {
+        if ((rc = check_planes(&tri_dest[k], R, b->rows)) != TRIMUL_OK) return rc;
+        if ((reinterpret_cast<uintptr_t>(tri_dest[k].base) & 127u) != 0) return TRIMUL_E_INVALID;
+        if (tri_dest[k].row_chunk < R || tri_dest[k].col_chunk < b->rows) return TRIMUL_E_UNSUPPORTED;
+    }
+    if (!same_geometry(tri_dest, n_dest)) return TRIMUL_E_INVALID;
+    // CTA-pair tensor-core kernel only; each CTA's 128 output rows must lie in one destination
+    if (dtype != TRIMUL_DTYPE_BF16 || sm_count() < 2 || R % 128 != 0) return TRIMUL_E_UNSUPPORTED;
+    trimul_planes shape = tri_dest[0];        // operand checks of the tile geometry use the full extent
+    shape.rows = a->rows; shape.row_chunk = a->rows;
+    if (!fast_contract_ok(a, b, &shape, true)) return TRIMUL_E_UNSUPPORTED;
+    return run_fast_contract(planes, a, b, tri_dest, static_cast<cudaStream_t>(stream), status, true, n_dest);
 }
 
 int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes* tri, const trimul_weights* w,

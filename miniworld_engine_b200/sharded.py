@@ -19,7 +19,13 @@ does not own of its a and b rows to their owners (all-to-all), contracts its ``B
 over the full N x N x N, and returns the rows of ``tri`` to their owners (all-to-all).  Per block
 a rank receives ``3 (world-1)/world`` of one operand instead of ``(world-1)`` operand slabs.
 
-No k-sum is split across ranks in either pattern, so the result equals the single-GPU result.  The reference has
+``PeerShardContext`` runs the channel-sharded pattern WITHOUT collectives in the data path: the
+three exchanges are the TMA stores of the producing kernels themselves, aimed at the consumer
+rank's memory (peer access over NVLink through symmetric-memory buffers), so the transfer of a
+tile overlaps the computation of the next one and nothing is copied twice.  Only two stream-ordered
+cross-GPU barriers per block remain.
+
+No k-sum is split across ranks in any pattern, so the result equals the single-GPU result.  The reference has
 no distributed code at all; its single-GPU module is the behaviour to match.
 
 The exchange logic is independent of the device: ``exchange()`` works on flat tensors with any
@@ -35,7 +41,8 @@ import torch.distributed as dist
 
 from . import stages as S
 
-__all__ = ["ShardPlan", "ChannelShardPlan", "exchange", "trimul_forward_sharded"]
+__all__ = ["ShardPlan", "ChannelShardPlan", "PeerShardContext", "peer_dest_specs", "exchange",
+           "trimul_forward_sharded"]
 
 
 @dataclass
@@ -226,6 +233,80 @@ class ChannelShardPlan:
             bufs["tri_recv"] = bufs["tri_send"]
             return
         dist.all_to_all_single(bufs["tri_recv"], bufs["tri_send"], group=group)
+
+
+def peer_dest_specs(cp: ChannelShardPlan, get_a, get_b, get_tri):
+    """Where rank ``cp.rank`` stores what it produces, per destination rank d: its chunk inside
+    d's ``a_recv`` / ``b_recv`` (stage 1 planes of d, this rank's rows) and inside d's ``tri_recv``
+    (this rank's planes, d's rows).  ``get_x(d)`` returns rank d's flat receive buffer (a tensor
+    whose memory this process can write: local, or a peer's through symmetric memory)."""
+    Pp, R, N, r, W = cp.my_planes, cp.R, cp.N, cp.rank, cp.world
+    if cp.outgoing:      # d's a_recv is [source][Pp][R][pitch_full]
+        n = Pp * R * cp.pitch_full
+        mk = lambda t: S.PlaneSpec(t[r * n:(r + 1) * n], Pp, R, N, cp.pitch_full, R * cp.pitch_full)
+    else:                # d's a_recv is [source][Pp][N][pitch_slab]
+        n = Pp * N * cp.pitch_slab
+        mk = lambda t: S.PlaneSpec(t[r * n:(r + 1) * n], Pp, N, R, cp.pitch_slab, N * cp.pitch_slab)
+    nt = Pp * R * cp.pitch_full      # d's tri_recv is [source][Pp][R][pitch_full]
+    mt = lambda t: S.PlaneSpec(t[r * nt:(r + 1) * nt], Pp, R, N, cp.pitch_full, R * cp.pitch_full)
+    return ([mk(get_a(d)) for d in range(W)], [mk(get_b(d)) for d in range(W)],
+            [mt(get_tri(d)) for d in range(W)])
+
+
+class PeerShardContext:
+    """Buffers and peer mappings of the collective-free channel-sharded block (one per process,
+    reusable for any number of calls with the same B, N, c and dtype).
+
+    Construction is collective over ``group`` (symmetric-memory rendezvous).  ``forward`` enqueues,
+    on the current stream: scattering stage 1, barrier, scattering contraction, barrier, stage 3.
+    The barriers order this rank's reads after every peer's stores of the same step and keep a
+    peer from overwriting a buffer that is still being read: a rank passes the first barrier of
+    block t+1 only after it finished stage 3 of block t, and the second barrier of block t only
+    after its contraction of block t.
+    """
+
+    def __init__(self, B: int, N: int, c: int, dtype: torch.dtype, device, group=None):
+        import os
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
+        import torch.distributed._symmetric_memory as symm_mem
+        self.group = dist.group.WORLD if group is None else group
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.B, self.N, self.c, self.dtype, self.device = B, N, c, dtype, torch.device(device)
+        plans = [ChannelShardPlan(B, N, c, self.world, self.rank, o) for o in (True, False)]
+        n_op = max(p.planes * p._op_plane_elems() for p in plans)
+        n_tri = plans[0].planes * plans[0].R * plans[0].pitch_full
+        self._plans = {True: plans[0], False: plans[1]}
+        self._local, self._handles, self._peer = {}, {}, {}
+        for name, n in (("a", n_op), ("b", n_op), ("tri", n_tri)):
+            t = symm_mem.empty(n, dtype=dtype, device=self.device)
+            h = symm_mem.rendezvous(t, self.group)
+            self._local[name], self._handles[name] = t, h
+            self._peer[name] = [t if d == self.rank else h.get_buffer(d, (n,), dtype) for d in range(self.world)]
+        self._dest = {o: peer_dest_specs(self._plans[o], lambda d: self._peer["a"][d], lambda d: self._peer["b"][d],
+                                         lambda d: self._peer["tri"][d]) for o in (True, False)}
+
+    def barrier(self) -> None:
+        """Stream-ordered barrier over the ranks of the group (device-side signal exchange)."""
+        self._handles["a"].barrier(channel=0)
+
+    @torch.no_grad()
+    def forward(self, z_slab: torch.Tensor, mask, weights: dict, *, outgoing: bool, eps_in: float = 1e-5,
+                eps_out: float = 1e-5, residual=None) -> torch.Tensor:
+        cp = self._plans[outgoing]
+        if tuple(z_slab.shape) != (self.B, cp.R, self.N, self.c) or z_slab.dtype != self.dtype:
+            raise ValueError(f"slab must be {(self.B, cp.R, self.N, self.c)} {self.dtype}, got "
+                             f"{tuple(z_slab.shape)} {z_slab.dtype}")
+        a_dest, b_dest, tri_dest = self._dest[outgoing]
+        S.tm1_scatter(z_slab, mask, weights, a_dest, b_dest, outgoing=outgoing, row0=cp.row0, eps=eps_in)
+        self.barrier()
+        bufs = {"a_recv": self._local["a"], "b_recv": self._local["b"], "tri_send": self._local["tri"],
+                "tri_recv": self._local["tri"]}
+        a_r, b_r, _ = cp.contract_operands(bufs)
+        S.contract_scatter(a_r, b_r, tri_dest)
+        self.barrier()
+        return S.tm2(z_slab, cp.tri_spec(bufs), weights, residual=residual, row0=cp.row0,
+                     eps_in=eps_in, eps_out=eps_out)
 
 
 @torch.no_grad()

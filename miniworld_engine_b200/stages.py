@@ -157,6 +157,51 @@ def contract(a: PlaneSpec, b: PlaneSpec, tri: PlaneSpec, *, plain_kernels: bool 
     _lib.check(rc, "trimul_b200_contract")
 
 
+def _plane_array(specs):
+    arr = (_lib.Planes * len(specs))()
+    for k, sp in enumerate(specs):
+        arr[k] = sp.struct()
+    return arr
+
+
+def tm1_scatter(z_slab: torch.Tensor, mask, weights: dict, a_dest, b_dest, *, outgoing: bool,
+                row0: int = 0, eps: float = 1e-5) -> None:
+    """Stage 1 whose output planes are split evenly over ``len(a_dest)`` destination buffers
+    (``a_dest[k]`` / ``b_dest[k]`` receive planes ``[k*P, (k+1)*P)``); the buffers may be another
+    GPU's memory mapped into this process.  Raises ``NotImplementedError`` where only the
+    non-scattering stage exists (fp32, c != 128, odd plane counts)."""
+    _require_cuda(z_slab, "z")
+    B, rows, N, c = z_slab.shape
+    kind, mask_u8 = _mask_arg(mask, B, N)
+    d = _desc(z_slab, N, outgoing, kind, eps, eps, False, row0)
+    w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, **weights)
+    st = _status_words(z_slab.device)
+    if len(a_dest) != len(b_dest):
+        raise ValueError("a_dest and b_dest must have the same length")
+    aa, bb = _plane_array(a_dest), _plane_array(b_dest)
+    with torch.cuda.device(z_slab.device):
+        rc = _lib.load().trimul_b200_tm1_scatter(
+            C.byref(d), z_slab.data_ptr(), mask_u8.data_ptr() if mask_u8 is not None else None, C.byref(w),
+            len(a_dest), aa, bb, torch.cuda.current_stream(z_slab.device).cuda_stream, st.data_ptr())
+    _lib.check(rc, "trimul_b200_tm1_scatter")
+    for t in keep:
+        t.record_stream(torch.cuda.current_stream(z_slab.device))
+
+
+def contract_scatter(a: PlaneSpec, b: PlaneSpec, tri_dest) -> None:
+    """Stage 2 whose output rows are split evenly over ``len(tri_dest)`` destination buffers
+    (``tri_dest[k]`` receives rows ``[k*R, (k+1)*R)``)."""
+    dev = a.buf.device
+    st = _status_words(dev)
+    tt = _plane_array(tri_dest)
+    with torch.cuda.device(dev):
+        rc = _lib.load().trimul_b200_contract_scatter(
+            _lib.DTYPE_BF16 if a.buf.dtype == torch.bfloat16 else _lib.DTYPE_FP32, 0, a.planes,
+            C.byref(a.struct()), C.byref(b.struct()), len(tri_dest), tt,
+            torch.cuda.current_stream(dev).cuda_stream, st.data_ptr())
+    _lib.check(rc, "trimul_b200_contract_scatter")
+
+
 def tm2(z_slab: torch.Tensor, tri: PlaneSpec, weights: dict, *, residual=None, row0: int = 0,
         eps_in: float = 1e-5, eps_out: float = 1e-5, plain_kernels: bool = False,
         inplace_norm: bool = False) -> torch.Tensor:

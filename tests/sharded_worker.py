@@ -36,7 +36,13 @@ def main():
     m = O.make_token_mask(1, N, "rand5")
     wd = weights_dict(w, torch.bfloat16, dev)
     slab = z[:, rank * R:(rank + 1) * R].contiguous().to(dev)
-    out = trimul_forward_sharded(slab, m.to(dev), wd, outgoing=outgoing, N=N, mode=args.mode).cpu()
+    if args.mode == "peer":
+        from miniworld_engine_b200.sharded import PeerShardContext
+        ctx = PeerShardContext(1, N, 128, torch.bfloat16, dev)
+        out = ctx.forward(slab, m.to(dev), wd, outgoing=outgoing)
+        out = ctx.forward(slab, m.to(dev), wd, outgoing=outgoing).cpu()     # buffers are reused between calls
+    else:
+        out = trimul_forward_sharded(slab, m.to(dev), wd, outgoing=outgoing, N=N, mode=args.mode).cpu()
     whole = trimul_forward(z.to(dev), m.to(dev), outgoing=outgoing, **forward_kwargs(w, torch.bfloat16, dev)).cpu()
     assert read_status(dev)[0] == 0
     ref = O.trimul_forward(z, m, w.to(torch.bfloat16), outgoing)[:, rank * R:(rank + 1) * R]

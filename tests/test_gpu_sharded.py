@@ -90,6 +90,73 @@ def _emulated_channel_sharded(z, m, w, outgoing, world, dev):
     return torch.cat(outs, dim=1).cpu()
 
 
+def _emulated_peer_sharded(z, m, w, outgoing, world, dev):
+    """The collective-free variant: every virtual rank's scattering stage 1 and scattering
+    contraction store straight into the receive buffers of all virtual ranks (here: buffers on the
+    same GPU; on several GPUs the same pointers are peer mappings)."""
+    from miniworld_engine_b200 import stages as S
+    from miniworld_engine_b200.sharded import ChannelShardPlan, peer_dest_specs
+    B, N, _, c = z.shape
+    wd = weights_dict(w, torch.bfloat16, dev)
+    zd, md = z.bfloat16().to(dev), m.to(dev)
+    plans = [ChannelShardPlan(B, N, c, world, r, outgoing) for r in range(world)]
+    bufs = [p.alloc(torch.bfloat16, dev) for p in plans]
+    for bf in bufs:
+        for t in bf.values():
+            t.view(torch.int16).fill_(0x7FC0)
+    R = plans[0].R
+    dests = [peer_dest_specs(p, lambda d: bufs[d]["a_recv"], lambda d: bufs[d]["b_recv"],
+                             lambda d: bufs[d]["tri_recv"]) for p in plans]
+    for r, p in enumerate(plans):
+        S.tm1_scatter(zd[:, r * R:(r + 1) * R].contiguous(), md, wd, dests[r][0], dests[r][1],
+                      outgoing=outgoing, row0=p.row0)
+    for r, p in enumerate(plans):
+        a_r, b_r, _ = p.contract_operands(bufs[r])
+        S.contract_scatter(a_r, b_r, dests[r][2])
+    outs = [S.tm2(zd[:, r * R:(r + 1) * R].contiguous(), p.tri_spec(bufs[r]), wd, row0=p.row0)
+            for r, p in enumerate(plans)]
+    return torch.cat(outs, dim=1).cpu()
+
+
+@pytest.mark.parametrize("B,N,world", [(1, 512, 2), (1, 512, 4), (2, 256, 2)])
+@pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
+def test_one_gpu_emulation_of_peer_scatter(outgoing, B, N, world):
+    from miniworld_engine_b200 import read_status, trimul_forward
+    dev = torch.device("cuda", 0)
+    w = O.make_weights(128, 0, affine="random")
+    z = O.make_input(B, N, 128, 1)
+    m = O.make_token_mask(B, N, "rand5")
+    got = _emulated_peer_sharded(z, m, w, outgoing, world, dev)
+    assert read_status(dev)[0] == 0
+    whole = trimul_forward(z.bfloat16().to(dev), m.to(dev), outgoing=outgoing,
+                           **forward_kwargs(w, torch.bfloat16, dev)).cpu()
+    assert not torch.isnan(got.float()).any()
+    assert torch.equal(got, whole)          # same kernels, same accumulation order
+
+
+def test_scatter_entry_points_reject_what_they_cannot_do():
+    from miniworld_engine_b200 import stages as S
+    from miniworld_engine_b200.sharded import ChannelShardPlan, peer_dest_specs
+    dev = torch.device("cuda", 0)
+    w = O.make_weights(128, 0)
+    # fp32 has no scattering kernel
+    wd32 = weights_dict(w, torch.float32, dev)
+    p = ChannelShardPlan(1, 256, 128, 2, 0, True)
+    bufs = p.alloc(torch.float32, dev)
+    d = peer_dest_specs(p, lambda k: bufs["a_recv"], lambda k: bufs["b_recv"], lambda k: bufs["tri_recv"])
+    z = torch.zeros(1, 128, 256, 128, device=dev)
+    with pytest.raises(NotImplementedError):
+        S.tm1_scatter(z, None, wd32, d[0], d[1], outgoing=True)
+    # R = 64 rows per destination: a contraction tile would straddle two destinations
+    wd = weights_dict(w, torch.bfloat16, dev)
+    p = ChannelShardPlan(1, 256, 128, 4, 0, True)
+    bufs = p.alloc(torch.bfloat16, dev)
+    d = peer_dest_specs(p, lambda k: bufs["a_recv"], lambda k: bufs["b_recv"], lambda k: bufs["tri_recv"])
+    a_r, b_r, _ = p.contract_operands(bufs)
+    with pytest.raises(NotImplementedError):
+        S.contract_scatter(a_r, b_r, d[2])
+
+
 @pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
 def test_one_gpu_emulation_of_channel_sharding(outgoing):
     from miniworld_engine_b200 import read_status, trimul_forward
@@ -133,7 +200,7 @@ def _free_port() -> int:
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
-@pytest.mark.parametrize("mode", ["rows", "channels"])
+@pytest.mark.parametrize("mode", ["rows", "channels", "peer"])
 @pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
 def test_nccl_row_sharding_matches_single_gpu(outgoing, mode):
     world = 2
