@@ -131,12 +131,13 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // Bounded wait.  `abort_flag` is a CTA-shared word: once any thread of the CTA has timed out,
 // every other wait in the CTA returns false promptly, and all roles fall through to the
 // kernel's tear-down.  Returns true when the phase completed.
-// The polling loop is kept OUT OF LINE: these kernels wait in dozens of places, and inlining the
-// loop everywhere pushed their code past what the SM's instruction cache holds (hit rates of
-// 60-90 % and the instruction-fetch path near its peak); the call costs nothing that matters on a
-// path that is about to sleep anyway.
-__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                            int32_t* status, int stage, int detail) {
+// kOutOfLine = true keeps the polling loop out of line.  Kernels that wait in dozens of places
+// and have large epilogues can outgrow the SM's instruction cache when the loop is inlined
+// everywhere (instruction-cache hit rates of 60-90 % and the instruction-fetch path near its
+// peak were measured); for them the call is cheaper than the misses.  Kernels whose code fits
+// keep the inlined loop, which measured 5-10 % faster there.
+__device__ __forceinline__ bool mbar_wait_loop(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                               int32_t* status, int stage, int detail) {
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
@@ -154,10 +155,18 @@ __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, vola
     report_timeout(status, stage, detail);
     return false;
 }
+__device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                            int32_t* status, int stage, int detail) {
+    return mbar_wait_loop(bar, parity, abort_flag, status, stage, detail);
+}
+template <bool kOutOfLine = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
                                           int32_t* status, int stage, int detail) {
-    if (mbar_try_wait(bar, parity)) return true;
-    return mbar_wait_slow(bar, parity, abort_flag, status, stage, detail);
+    if (kOutOfLine) {
+        if (mbar_try_wait(bar, parity)) return true;
+        return mbar_wait_slow(bar, parity, abort_flag, status, stage, detail);
+    }
+    return mbar_wait_loop(bar, parity, abort_flag, status, stage, detail);
 }
 
 // Collective AND over the `nthreads` threads that share named barrier `id`: every one of them
@@ -180,10 +189,11 @@ __device__ __forceinline__ bool named_barrier_all(int id, int nthreads, bool ok)
 // Wait of a whole warp group on one mbarrier phase: ONE thread polls (bounded), the others park
 // at the group's named barrier, which costs them no issue slots; the barrier also hands the
 // poller's verdict and its view of memory to every thread of the group.
+template <bool kOutOfLine = false>
 __device__ __forceinline__ bool group_wait(uint64_t* bar, uint32_t parity, bool poller, int bar_id, int nthreads,
                                            volatile int* abort_flag, int32_t* status, int stage, int detail) {
     bool ok = true;
-    if (poller) ok = mbar_wait(bar, parity, abort_flag, status, stage, detail);
+    if (poller) ok = mbar_wait<kOutOfLine>(bar, parity, abort_flag, status, stage, detail);
     return named_barrier_all(bar_id, nthreads, ok);
 }
 

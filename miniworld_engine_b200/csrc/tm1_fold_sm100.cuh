@@ -185,7 +185,7 @@ tm1_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
                 const int s = it % kF1XStages;
                 const uint32_t ph = (it / kF1XStages) & 1u;
-                if (!mbar_wait(&x_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm1, 100 + s)) break;
+                if (!mbar_wait<true>(&x_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm1, 100 + s)) break;
                 const int t0 = (tile % p.tiles_per_fixed) * kT1P;
                 const int bf = tile / p.tiles_per_fixed;
                 const int f = bf % p.n_fixed;
@@ -206,20 +206,20 @@ tm1_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         // ------------------------------------------------------------------ UMMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(128, 64);
-            bool ok = mbar_wait(w_ready, 0, abort_flag, p.status, kStageIdTm1, 200);
+            bool ok = mbar_wait<true>(w_ready, 0, abort_flag, p.status, kStageIdTm1, 200);
             tcgen05_fence_after();
             uint32_t it = 0;
             for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
                 const int s = it % kF1XStages;
                 const uint32_t ph = (it / kF1XStages) & 1u;
-                if (!mbar_wait(&x_full[s], ph, abort_flag, p.status, kStageIdTm1, 210 + s)) break;
+                if (!mbar_wait<true>(&x_full[s], ph, abort_flag, p.status, kStageIdTm1, 210 + s)) break;
                 tcgen05_fence_after();
                 TRIMUL_STAMP(1, it, 0);
                 const uint32_t xs = smem_u32(sX + s * kF1XBytes);
                 for (int half = 0; ok && half < 2; ++half) {
                     for (int side = 0; side < 2; ++side) {
                         // use counter of this side's accumulators: 2 * it + half, so the parity is `half`
-                        if (!mbar_wait(&acc_empty[side], (uint32_t)half ^ 1u, abort_flag, p.status, kStageIdTm1,
+                        if (!mbar_wait<true>(&acc_empty[side], (uint32_t)half ^ 1u, abort_flag, p.status, kStageIdTm1,
                                        220 + side)) {
                             ok = false;
                             break;
@@ -273,7 +273,7 @@ tm1_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                         keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
                 }
             }
-            if (!group_wait(&x_full[s], ph, pos == 0, bar_id, 128, abort_flag, p.status, kStageIdTm1, 300 + s)) break;
+            if (!group_wait<true>(&x_full[s], ph, pos == 0, bar_id, 128, abort_flag, p.status, kStageIdTm1, 300 + s)) break;
             if (pos == 0) TRIMUL_STAMP(2 + g, it, 0);
             float rstd, t;
             row_stats(sX + s * kF1XBytes, kT1SubTile, pos, p.eps, rstd, t);
@@ -327,9 +327,9 @@ tm1_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             for (int half = 0; half < 2; ++half, ++use) {
                 bool mine = true;
                 if (leader) {
-                    mine = mbar_wait(&acc_full[side], use & 1u, abort_flag, p.status, kStageIdTm1, 400 + side);
+                    mine = mbar_wait<true>(&acc_full[side], use & 1u, abort_flag, p.status, kStageIdTm1, 400 + side);
                     if (mine && half == 0)
-                        mine = mbar_wait(&stat_ready[slot], (it / kF1StatSlots) & 1u, abort_flag, p.status,
+                        mine = mbar_wait<true>(&stat_ready[slot], (it / kF1StatSlots) & 1u, abort_flag, p.status,
                                          kStageIdTm1, 410 + slot);
                     // the store issued two boxes ago has read its staging box
                     tma_store_wait_read<1>();

@@ -183,13 +183,13 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 const int br = tile / p.tiles_per_row;
                 const int r = br % p.rows;
                 const int b = br / p.rows;
-                if (!mbar_wait(&t_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 100 + s)) break;
+                if (!mbar_wait<true>(&t_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 100 + s)) break;
                 // tri planes viewed as (column, row, plane, chunk): 64 columns x 128 planes per box
                 mbar_arrive_expect_tx(&t_full[s], kT2TBytes);
                 uint8_t* dt = sT + s * kT2TBytes;
                 tma_load_4d(dt, &tmTri, &t_full[s], j0, r, b * kT2C, 0);
                 tma_load_4d(dt + kT2SubTile, &tmTri, &t_full[s], j0 + 64, r, b * kT2C, 0);
-                if (!mbar_wait(&z_empty[zs], zph ^ 1u, abort_flag, p.status, kStageIdTm2, 110 + zs)) break;
+                if (!mbar_wait<true>(&z_empty[zs], zph ^ 1u, abort_flag, p.status, kStageIdTm2, 110 + zs)) break;
                 TRIMUL_STAMP(0, it, 0);
                 mbar_arrive_expect_tx(&z_full[zs], kT2XBytes);
                 uint8_t* dz = sZ + zs * kT2XBytes;
@@ -203,19 +203,19 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         if (lane == 0) {
             constexpr uint32_t idesc = umma_idesc_bf16(kT2P, kT2C);
             constexpr uint32_t idesc_mn = umma_idesc_bf16(kT2P, kT2C, 1, 0);   // A (tri) is MN-major
-            bool ok = mbar_wait(w_ready, 0, abort_flag, p.status, kStageIdTm2, 200);
+            bool ok = mbar_wait<true>(w_ready, 0, abort_flag, p.status, kStageIdTm2, 200);
             tcgen05_fence_after();
             uint32_t it = 0;
             for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1u;
                 // accumulator pair `s` was last used by tile it-2
-                if (!mbar_wait(&acc_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 210 + s)) break;
+                if (!mbar_wait<true>(&acc_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 210 + s)) break;
                 const uint32_t wg = smem_u32(sW);
                 const uint32_t wo = wg + 2 * kT2SubTile;
                 const uint32_t d_g = tmem_base + s * 256;
                 const uint32_t d_p = d_g + 128;
-                if (!mbar_wait(&t_full[s], ph, abort_flag, p.status, kStageIdTm2, 230 + s)) break;
+                if (!mbar_wait<true>(&t_full[s], ph, abort_flag, p.status, kStageIdTm2, 230 + s)) break;
                 tcgen05_fence_after();
                 TRIMUL_STAMP(1, it, 0);
                 const uint32_t ts = smem_u32(sT + s * kT2TBytes);
@@ -229,7 +229,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 }
                 umma_commit(&tri_dead[s]);
                 const int zs = it % kG2ZStages;
-                if (!mbar_wait(&z_full[zs], (it / kG2ZStages) & 1u, abort_flag, p.status, kStageIdTm2, 220 + zs)) break;
+                if (!mbar_wait<true>(&z_full[zs], (it / kG2ZStages) & 1u, abort_flag, p.status, kStageIdTm2, 220 + zs)) break;
                 tcgen05_fence_after();
                 TRIMUL_STAMP(1, it, 1);
                 const uint32_t xs = smem_u32(sZ + zs * kT2XBytes);
@@ -257,10 +257,10 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 const int r = br % p.rows;
                 const int b = br / p.rows;
                 const uint8_t* src = sZ + s * kT2XBytes;
-                if (!mbar_wait(&box_ready[2 * s], ph, abort_flag, p.status, kStageIdTm2, 600 + s)) break;
+                if (!mbar_wait<true>(&box_ready[2 * s], ph, abort_flag, p.status, kStageIdTm2, 600 + s)) break;
                 tma_store_4d(&tmOut, src, 0, j0, r, b);
                 tma_store_commit();
-                if (!mbar_wait(&box_ready[2 * s + 1], ph, abort_flag, p.status, kStageIdTm2, 610 + s)) break;
+                if (!mbar_wait<true>(&box_ready[2 * s + 1], ph, abort_flag, p.status, kStageIdTm2, 610 + s)) break;
                 tma_store_4d(&tmOut, src + kT2SubTile, 64, j0, r, b);
                 tma_store_commit();
                 tma_store_wait_read<0>();
@@ -282,7 +282,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         const int bar_id = kG2EpiBarrier + grp;
         // fold gamma and 1/2 into the weights: thread e takes matrix e >> 7 (0: Wg with LN_in,
         // 1: Wo with LN_out), output channel e & 127
-        bool run = mbar_wait(w_full, 0, abort_flag, p.status, kStageIdTm2, 150);
+        bool run = mbar_wait<true>(w_full, 0, abort_flag, p.status, kStageIdTm2, 150);
         if (run) {
             const int m = e >> 7, n = e & 127;
             float s_, b_;
@@ -295,7 +295,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         }
         mbar_arrive(w_ready);
         // every channel's constants are needed by every epilogue thread
-        run = run && mbar_wait(w_ready, 0, abort_flag, p.status, kStageIdTm2, 160);
+        run = run && mbar_wait<true>(w_ready, 0, abort_flag, p.status, kStageIdTm2, 160);
 
         const uint32_t lane_bits = (uint32_t)(q * 32) << 16;
         const ulonglong2* cG = reinterpret_cast<const ulonglong2*>(sConst) + grp * 32;
@@ -307,9 +307,9 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             const int zs = it % kG2ZStages;
             bool ok = true;
             if (leader) {
-                ok = mbar_wait(&acc_full[s], ph, abort_flag, p.status, kStageIdTm2, 400 + s) &&
-                     mbar_wait(&stat_in[s], ph, abort_flag, p.status, kStageIdTm2, 410 + s) &&
-                     mbar_wait(&stat_out[s], ph, abort_flag, p.status, kStageIdTm2, 420 + s);
+                ok = mbar_wait<true>(&acc_full[s], ph, abort_flag, p.status, kStageIdTm2, 400 + s) &&
+                     mbar_wait<true>(&stat_in[s], ph, abort_flag, p.status, kStageIdTm2, 410 + s) &&
+                     mbar_wait<true>(&stat_out[s], ph, abort_flag, p.status, kStageIdTm2, 420 + s);
             }
             if (!named_barrier_all(bar_id, 128, ok)) break;
             tcgen05_fence_after();
@@ -381,14 +381,14 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             const int s = it & 1;
             const uint32_t ph = (it >> 1) & 1u;
             const int zs = it % kG2ZStages;
-            if (!group_wait(&z_full[zs], (it / kG2ZStages) & 1u, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag,
+            if (!group_wait<true>(&z_full[zs], (it / kG2ZStages) & 1u, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag,
                             p.status, kStageIdTm2, 300 + zs))
                 break;
             if (pos == 0) TRIMUL_STAMP(3, it, 0);
             float rstd, t;
             row_stats(sZ + zs * kT2XBytes, kT2SubTile, pos, p.eps_in, rstd, t);
             // the statistics go into the tile's tri buffer once nothing reads the tri data any more
-            if (!group_wait(&tri_dead[s], ph, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag, p.status,
+            if (!group_wait<true>(&tri_dead[s], ph, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag, p.status,
                             kStageIdTm2, 310 + s))
                 break;
             *reinterpret_cast<float2*>(reinterpret_cast<float4*>(sT + s * kT2TBytes) + pos) = make_float2(rstd, t);
@@ -412,7 +412,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
             const uint32_t ph = (it >> 1) & 1u;
-            if (!group_wait(&t_full[s], ph, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag, p.status,
+            if (!group_wait<true>(&t_full[s], ph, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag, p.status,
                             kStageIdTm2, 500 + s))
                 break;
             if (tid == 0) TRIMUL_STAMP(5, it, 0);
@@ -463,7 +463,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             const float rstd = rsqrtf(fmaxf(fmaf(-m1, m1, s2[0] * inv_c), 0.f) + p.eps_out);
             const float t = -(shift + m1) * rstd;
             mbar_arrive(&tri_dead[s]);                  // this thread is done with the tri data
-            if (!group_wait(&tri_dead[s], ph, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag, p.status,
+            if (!group_wait<true>(&tri_dead[s], ph, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag, p.status,
                             kStageIdTm2, 510 + s))
                 break;
             // position 8 cq + rs == tid

@@ -121,3 +121,44 @@ def test_single_rank_plan_is_the_plain_layout():
     for spec in (a_w, b_w, a_r, b_r):
         assert spec.row_chunk is None and spec.col_chunk is None and spec.chunk_stride == 0
     assert (a_r.rows, a_r.cols, b_r.rows, b_r.cols) == (24, 24, 24, 24)
+
+
+@pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
+@pytest.mark.parametrize("world", [2, 4])
+def test_peer_destinations_are_the_chunks_the_contraction_reads(world, outgoing):
+    """The collective-free plan: what rank r's scattering stage 1 writes through its destination
+    specs must be exactly what every rank's contraction operands (and stage 3) then read.  The
+    scatter itself is emulated with tensor copies: planes [d*P, (d+1)*P) of rank r's stage-1 result
+    go to destination d, output rows [d*R, (d+1)*R) of the contraction go to destination d."""
+    from miniworld_engine_b200 import stages as S
+    from miniworld_engine_b200.sharded import ChannelShardPlan, peer_dest_specs
+    B, N, c = 1, 16 * world, 8 * world
+    plans = [ChannelShardPlan(B, N, c, world, r, outgoing) for r in range(world)]
+    bufs = [p.alloc(torch.float32, "cpu") for p in plans]
+    for bf in bufs:
+        for t in bf.values():
+            t.fill_(float("nan"))
+    R, Pp = plans[0].R, plans[0].my_planes
+    g = torch.Generator().manual_seed(5)
+    # the full operands a[p][i][k] (outgoing) or a'[p][i][k] = a[p][k][i] (incoming), as one array
+    a_full = torch.randn(B * c, N, N, generator=g)
+    b_full = torch.randn(B * c, N, N, generator=g)
+    for r, p in enumerate(plans):
+        a_d, b_d, _ = peer_dest_specs(p, lambda d: bufs[d]["a_recv"], lambda d: bufs[d]["b_recv"],
+                                      lambda d: bufs[d]["tri_recv"])
+        for full, dests in ((a_full, a_d), (b_full, b_d)):
+            # stage 1 of rank r produces rows [r*R, (r+1)*R) (outgoing) or k-columns (incoming) of every plane
+            mine = full[:, r * R:(r + 1) * R, :] if outgoing else full[:, :, r * R:(r + 1) * R]
+            for d in range(world):
+                S.dense_to_planes(dests[d], mine[d * Pp:(d + 1) * Pp])
+    tri_full = torch.einsum("pik,pjk->pij", a_full, b_full)
+    for r, p in enumerate(plans):
+        a_r, b_r, _ = p.contract_operands(bufs[r])
+        assert torch.equal(S.planes_to_dense(a_r), a_full[r * Pp:(r + 1) * Pp])
+        assert torch.equal(S.planes_to_dense(b_r), b_full[r * Pp:(r + 1) * Pp])
+        _, _, t_d = peer_dest_specs(p, lambda d: bufs[d]["a_recv"], lambda d: bufs[d]["b_recv"],
+                                    lambda d: bufs[d]["tri_recv"])
+        for d in range(world):      # rank r's planes, destination d's rows
+            S.dense_to_planes(t_d[d], tri_full[r * Pp:(r + 1) * Pp, d * R:(d + 1) * R])
+    for r, p in enumerate(plans):
+        assert torch.equal(S.planes_to_dense(p.tri_spec(bufs[r])), tri_full[:, r * R:(r + 1) * R])
