@@ -659,111 +659,6 @@ __device__ __forceinline__ void ln_row_inplace(uint8_t* tile, int sub_bytes, int
     }
 }
 
-// ---------------------------------------------------------------------------------------
-// LayerNorm of one 128-channel row, IN PLACE, by the two threads in lanes l and l + 16 of a warp:
-// thread h = lane >> 4 owns 16-byte chunks 4h..4h+3 of each sub-tile, i.e. channels [32h, 32h+32)
-// and [64+32h, 64+32h+32).  Its 64 values stay in registers between the statistics and the
-// normalisation, so the row is read once and written once; the partial sums cross by one
-// shuffle.  Half the latency of a thread per row, which is what matters when the tile ring is
-// only two deep.  A quarter-warp touches eight consecutive rows at the same chunk index
-// (conflict-free under the swizzle) and one gamma/beta address.
-// `zero_row` stores zeros instead (masked position); such a thread still takes part in the shuffle.
-// ---------------------------------------------------------------------------------------
-__device__ __forceinline__ void ln_row_split16_inplace(uint8_t* tile, int sub_bytes, int row, int h,
-                                                       const float* sGamma, const float* sBeta, float eps,
-                                                       bool zero_row) {
-    const uint32_t swz = (uint32_t)(row & 7);
-    uint8_t* rowp = tile + row * 128;
-    const float shift = bf16_lo(*reinterpret_cast<const uint32_t*>(rowp + (swz << 4)));   // channel 0
-    const f32x2 nshift = f2_pack(-shift, -shift);
-    uint4 v[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i)
-        v[i] = *reinterpret_cast<const uint4*>(rowp + (i >> 2) * sub_bytes + ((((uint32_t)(4 * h + (i & 3))) ^ swz) << 4));
-    f32x2 s1[4] = {0ull, 0ull, 0ull, 0ull}, s2[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const f32x2 d = f2_add(f2_from_bf16x2(w4[e]), nshift);
-            s1[e] = f2_add(s1[e], d);
-            s2[e] = f2_fma(d, d, s2[e]);
-        }
-    }
-    float t1 = f2_hsum(f2_add(f2_add(s1[0], s1[1]), f2_add(s1[2], s1[3])));
-    float t2 = f2_hsum(f2_add(f2_add(s2[0], s2[1]), f2_add(s2[2], s2[3])));
-    t1 += __shfl_xor_sync(0xffffffffu, t1, 16);
-    t2 += __shfl_xor_sync(0xffffffffu, t2, 16);
-    const float m1 = t1 * (1.0f / 128.0f);
-    const float var = fmaxf(fmaf(-m1, m1, t2 * (1.0f / 128.0f)), 0.f);
-    const float rstd = rsqrtf(var + eps);
-    const float nmr = -(shift + m1) * rstd;
-    const f32x2 rstd2 = f2_pack(rstd, rstd), nmr2 = f2_pack(nmr, nmr);
-#pragma unroll 2
-    for (int i = 0; i < 8; ++i) {
-        const int ch = (i >> 2) * 64 + (4 * h + (i & 3)) * 8;
-        const float4 g0 = *reinterpret_cast<const float4*>(sGamma + ch);
-        const float4 g1 = *reinterpret_cast<const float4*>(sGamma + ch + 4);
-        const float4 b0 = *reinterpret_cast<const float4*>(sBeta + ch);
-        const float4 b1 = *reinterpret_cast<const float4*>(sBeta + ch + 4);
-        uint4 o;
-        o.x = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[i].x), rstd2, nmr2), f2_pack(g0.x, g0.y), f2_pack(b0.x, b0.y)));
-        o.y = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[i].y), rstd2, nmr2), f2_pack(g0.z, g0.w), f2_pack(b0.z, b0.w)));
-        o.z = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[i].z), rstd2, nmr2), f2_pack(g1.x, g1.y), f2_pack(b1.x, b1.y)));
-        o.w = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[i].w), rstd2, nmr2), f2_pack(g1.z, g1.w), f2_pack(b1.z, b1.w)));
-        if (zero_row) o = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(rowp + (i >> 2) * sub_bytes + ((((uint32_t)(4 * h + (i & 3))) ^ swz) << 4)) = o;
-    }
-}
-
-// Thread-per-row LayerNorm that keeps the row (16 x 16 bytes) in registers between the statistics
-// and the normalisation: one shared-memory read and one write per element instead of two reads
-// and a write.  Needs about 100 registers, so only kernels with at most 576 threads can use it.
-__device__ __forceinline__ void ln_row_inplace_regs(uint8_t* tile, int sub_bytes, int row, const float* sGamma,
-                                                    const float* sBeta, float eps, bool zero_row) {
-    const uint32_t swz = (uint32_t)(row & 7);
-    uint8_t* rowp = tile + row * 128;
-    uint4 v[16];
-#pragma unroll
-    for (int i = 0; i < 16; ++i)
-        v[i] = *reinterpret_cast<const uint4*>(rowp + (i >> 3) * sub_bytes + ((((uint32_t)(i & 7)) ^ swz) << 4));
-    const float shift = bf16_lo(v[0].x);
-    const f32x2 nshift = f2_pack(-shift, -shift);
-    f32x2 s1[4] = {0ull, 0ull, 0ull, 0ull}, s2[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const f32x2 d = f2_add(f2_from_bf16x2(w4[e]), nshift);
-            s1[e] = f2_add(s1[e], d);
-            s2[e] = f2_fma(d, d, s2[e]);
-        }
-    }
-    const float m1 = f2_hsum(f2_add(f2_add(s1[0], s1[1]), f2_add(s1[2], s1[3]))) * (1.0f / 128.0f);
-    const float q1 = f2_hsum(f2_add(f2_add(s2[0], s2[1]), f2_add(s2[2], s2[3])));
-    const float var = fmaxf(fmaf(-m1, m1, q1 * (1.0f / 128.0f)), 0.f);
-    const float rstd = rsqrtf(var + eps);
-    const float nmr = -(shift + m1) * rstd;
-    const f32x2 rstd2 = f2_pack(rstd, rstd), nmr2 = f2_pack(nmr, nmr);
-#pragma unroll
-    for (int i = 0; i < 16; ++i) {
-        const int ch = i * 8;
-        const float4 g0 = *reinterpret_cast<const float4*>(sGamma + ch);
-        const float4 g1 = *reinterpret_cast<const float4*>(sGamma + ch + 4);
-        const float4 b0 = *reinterpret_cast<const float4*>(sBeta + ch);
-        const float4 b1 = *reinterpret_cast<const float4*>(sBeta + ch + 4);
-        uint4 o;
-        o.x = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[i].x), rstd2, nmr2), f2_pack(g0.x, g0.y), f2_pack(b0.x, b0.y)));
-        o.y = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[i].y), rstd2, nmr2), f2_pack(g0.z, g0.w), f2_pack(b0.z, b0.w)));
-        o.z = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[i].z), rstd2, nmr2), f2_pack(g1.x, g1.y), f2_pack(b1.x, b1.y)));
-        o.w = f2_to_bf16x2(f2_fma(f2_fma(f2_from_bf16x2(v[i].w), rstd2, nmr2), f2_pack(g1.z, g1.w), f2_pack(b1.z, b1.w)));
-        if (zero_row) o = make_uint4(0u, 0u, 0u, 0u);
-        *reinterpret_cast<uint4*>(rowp + (i >> 3) * sub_bytes + ((((uint32_t)(i & 7)) ^ swz) << 4)) = o;
-    }
-}
-
 // Mean / rstd of one 128-channel row of a swizzled z tile (one pass, sums shifted by the row's
 // first element so the variance does not cancel).  Returns rstd and t = -mean * rstd.
 __device__ __forceinline__ void row_stats(const uint8_t* tile, int sub_bytes, int row, float eps, float& rstd,

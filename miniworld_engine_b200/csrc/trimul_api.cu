@@ -8,6 +8,7 @@
 
 #include "../../include/trimul_b200.h"
 
+#include <atomic>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
@@ -103,9 +104,28 @@ int sm_count() {
     return n;
 }
 
+// Opt the kernel in to `bytes` of dynamic shared memory — once per kernel and device: the
+// attribute call is not free and these entry points sit on latency-sensitive host paths.
+bool ensure_smem_once(const void* fn, int bytes) {
+    struct Entry { const void* fn; uint64_t devices; };
+    static Entry table[32];
+    static int used = 0;
+    static std::mutex mu;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return false;
+    std::lock_guard<std::mutex> lock(mu);
+    Entry* e = nullptr;
+    for (int i = 0; i < used; ++i)
+        if (table[i].fn == fn) e = &table[i];
+    if (e != nullptr && dev < 64 && ((e->devices >> dev) & 1u)) return true;
+    if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return false;
+    if (e == nullptr && used < 32) { e = &table[used++]; e->fn = fn; e->devices = 0; }
+    if (e != nullptr && dev < 64) e->devices |= 1ull << dev;
+    return true;
+}
 template <typename K>
 bool ensure_smem(K kernel, int bytes) {
-    return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess;
+    return ensure_smem_once(reinterpret_cast<const void*>(kernel), bytes);
 }
 
 inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
@@ -216,7 +236,7 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
         if (!encode_bf16(&tmW[m], ws[m], 2, dims, strides, box, 128)) return TRIMUL_E_CUDA;
     }
     const int planes = d->B * 128;
-    ScatterMaps scA, scB;
+    ScatterMaps scA{}, scB{};
     const int planes_per_dest = n_dest > 0 ? planes / n_dest : planes;
     if (n_dest > 0) {
         // stores of a and b: 64 positions x one destination's share of the 128 planes per box
@@ -313,7 +333,7 @@ bool fast_contract_ok(const trimul_planes* a, const trimul_planes* b, const trim
 int run_fast_contract(int planes, const trimul_planes* a, const trimul_planes* b, const trimul_planes* t,
                       cudaStream_t st, int32_t* status, bool pair, int n_dest = 0) {
     CUtensorMap tmA, tmB, tmD;
-    ScatterMaps sc;
+    ScatterMaps sc{};
     if (!encode_planes(&tmA, *a, planes, kCtBK, kCtBM, 1)) return TRIMUL_E_CUDA;
     if (!encode_planes(&tmB, *b, planes, kCtBK, pair ? 128 : kCtBN, 1)) return TRIMUL_E_CUDA;
     for (int k = 0; k < n_dest; ++k)
