@@ -92,9 +92,12 @@ typedef struct trimul_desc {
     int32_t  B;              /* batch                                                               */
     int32_t  N;              /* tokens: z is N x N positions per batch                              */
     int32_t  c;              /* d_pair = channels of z and of the output                            */
-    int32_t  c_hidden;       /* width of a/b/tri; must equal c (reference.py:51-59 builds the four
-                                input projections c-wide regardless, so only c_hidden == c is
-                                self-consistent there)                                              */
+    int32_t  c_hidden;       /* width of a/b/tri.  Equal to c everywhere (reference.py:51-59 builds the
+                                four input projections c-wide regardless, so only c_hidden == c is
+                                self-consistent there), except that stage 3 alone also takes
+                                c_hidden == 2c: the bidirectional block's tri = [outgoing | incoming]
+                                planes, LayerNorm_out over 2c channels, w_out [c, 2c]
+                                (bidirectional.py:73-84,150-156)                                    */
     int32_t  dtype;          /* TRIMUL_DTYPE_*                                                      */
     int32_t  direction;      /* TRIMUL_OUTGOING / TRIMUL_INCOMING                                   */
     int32_t  mask_kind;      /* TRIMUL_MASK_*                                                       */

@@ -179,6 +179,7 @@ __global__ void __launch_bounds__(256) plain_contract_kernel(PlaneView a, PlaneV
 
 struct PlainTm2Params {
     int B, rows, N, c;
+    int h;      // channels of tri / LayerNorm_out / in_features of w_out (c, or 2c for the bidirectional block)
     const float *gamma_in, *beta_in, *gamma_out, *beta_out;
     float eps_in, eps_out;
     const void *w_gate, *w_out;
@@ -191,7 +192,7 @@ __global__ void __launch_bounds__(kPlainThreads)
 plain_tm2_kernel(const T* __restrict__ z, T* __restrict__ out, const T* __restrict__ residual, PlainTm2Params p) {
     __shared__ float xs[kPlainPos * kPlainMaxC];
     __shared__ float ts[kPlainPos * kPlainMaxC];
-    const int c = p.c;
+    const int c = p.c, h = p.h;
     const int tiles = (p.N + kPlainPos - 1) / kPlainPos;
     const int s0 = (blockIdx.x % tiles) * kPlainPos;
     const int br = blockIdx.x / tiles;
@@ -200,13 +201,13 @@ plain_tm2_kernel(const T* __restrict__ z, T* __restrict__ out, const T* __restri
     const int npos = min(kPlainPos, p.N - s0);
     const long long pos0 = (((long long)b * p.rows + r) * p.N + s0);
     for (int i = threadIdx.x; i < npos * c; i += blockDim.x) xs[i] = load_f<T>(z + pos0 * c + i);
-    for (int i = threadIdx.x; i < npos * c; i += blockDim.x) {
+    for (int i = threadIdx.x; i < npos * h; i += blockDim.x) {
         const int ch = i / npos, q = i % npos;   // consecutive threads walk the contiguous position axis
-        ts[q * c + ch] = load_f<T>((const T*)p.tri.base + p.tri.offset((long long)b * c + ch, r, s0 + q));
+        ts[q * h + ch] = load_f<T>((const T*)p.tri.base + p.tri.offset((long long)b * h + ch, r, s0 + q));
     }
     __syncthreads();
     plain_layernorm_rows<T>(xs, npos, c, p.gamma_in, p.beta_in, p.eps_in);
-    plain_layernorm_rows<T>(ts, npos, c, p.gamma_out, p.beta_out, p.eps_out);
+    plain_layernorm_rows<T>(ts, npos, h, p.gamma_out, p.beta_out, p.eps_out);
     __syncthreads();
     const T* Wg = (const T*)p.w_gate;
     const T* Wo = (const T*)p.w_out;
@@ -216,12 +217,13 @@ plain_tm2_kernel(const T* __restrict__ z, T* __restrict__ out, const T* __restri
         for (int q = 0; q < kPlainPos; ++q) g[q] = v[q] = 0.f;
         for (int k = 0; k < c; ++k) {
             const float wg = load_f<T>(Wg + (long long)o * c + k);
-            const float wo = load_f<T>(Wo + (long long)o * c + k);
 #pragma unroll
-            for (int q = 0; q < kPlainPos; ++q) {
-                g[q] = fmaf(wg, xs[q * c + k], g[q]);
-                v[q] = fmaf(wo, ts[q * c + k], v[q]);
-            }
+            for (int q = 0; q < kPlainPos; ++q) g[q] = fmaf(wg, xs[q * c + k], g[q]);
+        }
+        for (int k = 0; k < h; ++k) {
+            const float wo = load_f<T>(Wo + (long long)o * h + k);
+#pragma unroll
+            for (int q = 0; q < kPlainPos; ++q) v[q] = fmaf(wo, ts[q * h + k], v[q]);
         }
         for (int q = 0; q < npos; ++q) {
             float y = sigmoid_ref(g[q]) * v[q];

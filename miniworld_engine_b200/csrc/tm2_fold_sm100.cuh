@@ -36,6 +36,12 @@
 //                 up with the sums of ONE position
 // Before the first tile the epilogue threads fold gamma and 1/2 into Wg and Wo in shared memory
 // and leave per-channel (rowsum, bias) pairs for the epilogue.
+//
+// kKH = 2 is the last stage of the BIDIRECTIONAL block (bidirectional.py:150-156): tri has 256
+// channel planes per batch ([outgoing | incoming]), LayerNorm_out runs over all 256 and Wo is
+// [128, 256].  The tri tile then arrives as two 128-channel halves, each in one slot of the tri
+// ring (so a tile occupies the whole ring and the z ring is two deep: Wo takes 32 KB more); the
+// projection accumulates over both halves and the tri statistics are summed over both.
 #pragma once
 
 #include "tm2_sm100.cuh"
@@ -45,13 +51,18 @@ namespace trimul {
 constexpr int kG2Threads = 640;
 constexpr int kG2EpiThreads = 256;      // warps 4..11, two groups of 128
 constexpr int kG2StatThreads = 128;     // each of the two statistics groups
-constexpr int kG2ZStages = 3;
-constexpr int kG2OffZ = kT2WBytes;                          // 3 x 32 KB z ring
-constexpr int kG2OffT = kG2OffZ + kG2ZStages * kT2XBytes;   // 2 x 32 KB tri ring; once a tile's tri data is dead its
-                                                            // first 2 KB hold [128 positions] (r_in, t_in, r_out, t_out)
-constexpr int kG2OffConst = kG2OffT + 2 * kT2TBytes;        // [2 matrices][64 channel pairs] (s0, s1, b0, b1)
-constexpr int kG2OffBars = kG2OffConst + 2048;
-constexpr int kG2SmemBytes = kG2OffBars + 256;
+template <int kKH>
+struct G2Layout {
+    static constexpr int kWBytes = (2 + 2 * kKH) * kT2SubTile;   // Wg: 2 K sub-tiles, Wo: 2 per 128 hidden channels
+    static constexpr int kZStages = kKH == 1 ? 3 : 2;
+    static constexpr int kOffZ = kWBytes;                        // z ring, 32 KB per stage
+    static constexpr int kOffT = kOffZ + kZStages * kT2XBytes;   // 2 x 32 KB tri ring; once a tile's tri data is dead the
+                                                                 // first 2 KB of its first slot hold [128 positions]
+                                                                 // (r_in, t_in, r_out, t_out)
+    static constexpr int kOffConst = kOffT + 2 * kT2TBytes;      // [2 matrices][64 channel pairs] (s0, s1, b0, b1)
+    static constexpr int kOffBars = kOffConst + 2048;
+    static constexpr int kSmemBytes = kOffBars + 256;
+};
 constexpr int kG2StatInBarrier = 2;
 constexpr int kG2StatOutBarrier = 3;
 constexpr int kG2EpiBarrier = 4;        // 4: channels 0..63, 5: channels 64..127
@@ -61,15 +72,15 @@ struct Tm2FoldParams {
     int residual_is_z;    // add the z tile to the result (the block's `pair + update` form)
 };
 
-// Fold one row (output channel n) of a weight matrix that lies in shared memory as two swizzled
+// Fold one row (output channel n) of a weight matrix that lies in shared memory as `nsub` swizzled
 // 64-column sub-tiles: w[k] <- bf16(w[k] * gamma[k] / 2).  Returns the sum of the rounded row and
 // 0.5 * sum_k w[k] * beta[k].
 __device__ __forceinline__ void fold_row_smem(uint8_t* wbase, int n, const float* gamma, const float* beta,
-                                              float& s, float& bias) {
+                                              int nsub, float& s, float& bias) {
     float ssum = 0.f, bsum = 0.f;
     const uint32_t swz = (uint32_t)(n & 7);
 #pragma unroll 1
-    for (int kh = 0; kh < 2; ++kh) {
+    for (int kh = 0; kh < nsub; ++kh) {
 #pragma unroll 2
         for (int j = 0; j < 8; ++j) {
             uint4* ptr = reinterpret_cast<uint4*>(wbase + kh * kT2SubTile + n * 128 + ((((uint32_t)j) ^ swz) << 4));
@@ -98,7 +109,7 @@ __device__ __forceinline__ void fold_row_smem(uint8_t* wbase, int n, const float
     bias = 0.5f * bsum;
 }
 
-template <bool kResidualIsZ>
+template <bool kResidualIsZ, int kKH>
 __global__ void __launch_bounds__(kG2Threads, 1)
 tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWg,
                       const __grid_constant__ CUtensorMap tmWo, const __grid_constant__ CUtensorMap tmOut,
@@ -109,19 +120,21 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         if (threadIdx.x == 0) report_timeout(p.status, kStageIdTm2, 900);
         return;
     }
+    using L = G2Layout<kKH>;
+    constexpr int kG2ZStages = L::kZStages;
     uint8_t* sW = smem;
-    uint8_t* sZ = smem + kG2OffZ;
-    uint8_t* sT = smem + kG2OffT;
-    float4* sConst = reinterpret_cast<float4*>(smem + kG2OffConst);
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kG2OffBars);
+    uint8_t* sZ = smem + L::kOffZ;
+    uint8_t* sT = smem + L::kOffT;
+    float4* sConst = reinterpret_cast<float4*>(smem + L::kOffConst);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kOffBars);
     uint64_t* w_full = bars;            // weights landed
     uint64_t* w_ready = bars + 1;       // weights folded (256 arrivals)
     uint64_t* z_full = bars + 2;        // [3] z tile landed
     uint64_t* z_empty = bars + 5;       // [3] the store of the tile written over the z tile has read it (1 arrival)
     uint64_t* box_ready = bars + 8;     // [3 stages][2 halves] result half written (4 arrivals)
-    uint64_t* t_full = bars + 14;       // [2] tri tile landed
-    uint64_t* tri_dead = bars + 16;     // [2] the tile's UMMAs retired + its 128 statistics threads done reading
-    uint64_t* t_empty = bars + 18;      // [2] the epilogue has taken the statistics out of the buffer (8 arrivals)
+    uint64_t* t_full = bars + 14;       // [2] tri slot landed (a slot = 128 channel planes of a tile)
+    uint64_t* tri_dead = bars + 16;     // [2] the slot's UMMAs retired + its 128 statistics threads done reading
+    uint64_t* t_empty = bars + 18;      // [2] the epilogue has taken the statistics out of the slot (8 arrivals)
     uint64_t* acc_full = bars + 20;     // [2]
     uint64_t* acc_empty = bars + 22;    // [2] (8 arrivals)
     uint64_t* stat_in = bars + 24;      // [2] z statistics written into the tri buffer (128 arrivals)
@@ -168,27 +181,37 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
-            mbar_arrive_expect_tx(w_full, kT2WBytes);
-            for (int kh = 0; kh < 2; ++kh) {
-                tma_load_2d(sW + kh * kT2SubTile, &tmWg, w_full, kh * 64, 0);
-                tma_load_2d(sW + (2 + kh) * kT2SubTile, &tmWo, w_full, kh * 64, 0);
-            }
+            mbar_arrive_expect_tx(w_full, L::kWBytes);
+            for (int kh = 0; kh < 2; ++kh) tma_load_2d(sW + kh * kT2SubTile, &tmWg, w_full, kh * 64, 0);
+            for (int kh = 0; kh < 2 * kKH; ++kh) tma_load_2d(sW + (2 + kh) * kT2SubTile, &tmWo, w_full, kh * 64, 0);
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
-                const int s = it & 1;
-                const uint32_t ph = (it >> 1) & 1u;
                 const int zs = it % kG2ZStages;
                 const uint32_t zph = (it / kG2ZStages) & 1u;
                 const int j0 = (tile % p.tiles_per_row) * kT2P;
                 const int br = tile / p.tiles_per_row;
                 const int r = br % p.rows;
                 const int b = br / p.rows;
-                if (!mbar_wait<true>(&t_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm2, 100 + s)) break;
-                // tri planes viewed as (column, row, plane, chunk): 64 columns x 128 planes per box
-                mbar_arrive_expect_tx(&t_full[s], kT2TBytes);
-                uint8_t* dt = sT + s * kT2TBytes;
-                tma_load_4d(dt, &tmTri, &t_full[s], j0, r, b * kT2C, 0);
-                tma_load_4d(dt + kT2SubTile, &tmTri, &t_full[s], j0 + 64, r, b * kT2C, 0);
+                bool okp = true;
+                for (int h = 0; h < kKH; ++h) {
+                    // tri slot of this 128-channel half: slots are used round-robin, use n = u >> 1
+                    const uint32_t u = it * kKH + h;
+                    const int ts = u & 1;
+                    const uint32_t tph = (u >> 1) & 1u;
+                    // a tile's first slot carries the statistics and is released by the epilogue; any
+                    // other slot is free as soon as its readers are done
+                    uint64_t* freed = h == 0 ? &t_empty[ts] : &tri_dead[ts];
+                    if (!mbar_wait<true>(freed, tph ^ 1u, abort_flag, p.status, kStageIdTm2, 100 + ts)) {
+                        okp = false;
+                        break;
+                    }
+                    // tri planes viewed as (column, row, plane, chunk): 64 columns x 128 planes per box
+                    mbar_arrive_expect_tx(&t_full[ts], kT2TBytes);
+                    uint8_t* dt = sT + ts * kT2TBytes;
+                    tma_load_4d(dt, &tmTri, &t_full[ts], j0, r, (b * kKH + h) * kT2C, 0);
+                    tma_load_4d(dt + kT2SubTile, &tmTri, &t_full[ts], j0 + 64, r, (b * kKH + h) * kT2C, 0);
+                }
+                if (!okp) break;
                 if (!mbar_wait<true>(&z_empty[zs], zph ^ 1u, abort_flag, p.status, kStageIdTm2, 110 + zs)) break;
                 TRIMUL_STAMP(0, it, 0);
                 mbar_arrive_expect_tx(&z_full[zs], kT2XBytes);
@@ -215,19 +238,28 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 const uint32_t wo = wg + 2 * kT2SubTile;
                 const uint32_t d_g = tmem_base + s * 256;
                 const uint32_t d_p = d_g + 128;
-                if (!mbar_wait<true>(&t_full[s], ph, abort_flag, p.status, kStageIdTm2, 230 + s)) break;
-                tcgen05_fence_after();
-                TRIMUL_STAMP(1, it, 0);
-                const uint32_t ts = smem_u32(sT + s * kT2TBytes);
+                for (int h = 0; ok && h < kKH; ++h) {
+                    const uint32_t u = it * kKH + h;
+                    const int tsl = u & 1;
+                    if (!mbar_wait<true>(&t_full[tsl], (u >> 1) & 1u, abort_flag, p.status, kStageIdTm2, 230 + tsl)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    TRIMUL_STAMP(1, it, 0);
+                    const uint32_t ts = smem_u32(sT + tsl * kT2TBytes);
+                    const uint32_t woh = wo + h * 2 * kT2SubTile;       // Wo columns of this half
 #pragma unroll 2
-                for (int kk = 0; kk < kT2C / 16; ++kk) {
-                    // tri tile: rows are channels (K), 128 bytes = 64 positions per row, the second
-                    // 64 positions one sub-tile further; a K step of 16 is two 8-row groups = 2048 B
-                    umma_bf16_ss(d_p, umma_smem_desc_mn_sw128(ts + kk * 2048, kT2SubTile, 1024),
-                                 umma_smem_desc_sw128(wo + (kk >> 2) * kT2SubTile) + (kk & 3) * kDescKStep, idesc_mn,
-                                 kk != 0);
+                    for (int kk = 0; kk < kT2C / 16; ++kk) {
+                        // tri slot: rows are channels (K), 128 bytes = 64 positions per row, the second
+                        // 64 positions one sub-tile further; a K step of 16 is two 8-row groups = 2048 B
+                        umma_bf16_ss(d_p, umma_smem_desc_mn_sw128(ts + kk * 2048, kT2SubTile, 1024),
+                                     umma_smem_desc_sw128(woh + (kk >> 2) * kT2SubTile) + (kk & 3) * kDescKStep,
+                                     idesc_mn, (kk | h) != 0);
+                    }
+                    umma_commit(&tri_dead[tsl]);
                 }
-                umma_commit(&tri_dead[s]);
+                if (!ok) break;
                 const int zs = it % kG2ZStages;
                 if (!mbar_wait<true>(&z_full[zs], (it / kG2ZStages) & 1u, abort_flag, p.status, kStageIdTm2, 220 + zs)) break;
                 tcgen05_fence_after();
@@ -287,7 +319,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             const int m = e >> 7, n = e & 127;
             float s_, b_;
             fold_row_smem(sW + m * 2 * kT2SubTile, n, m == 0 ? p.gamma_in : p.gamma_out,
-                          m == 0 ? p.beta_in : p.beta_out, s_, b_);
+                          m == 0 ? p.beta_in : p.beta_out, m == 0 ? 2 : 2 * kKH, s_, b_);
             float* c = reinterpret_cast<float*>(&sConst[m * 64 + (n >> 1)]);
             c[n & 1] = s_;
             c[2 + (n & 1)] = b_;
@@ -314,9 +346,10 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             if (!named_barrier_all(bar_id, 128, ok)) break;
             tcgen05_fence_after();
             if (e == 0) TRIMUL_STAMP(4, it, 0);
-            const float4 st = reinterpret_cast<const float4*>(sT + s * kT2TBytes)[row];
+            const int slot0 = (it * kKH) & 1;           // the tile's first tri slot carries its statistics
+            const float4 st = reinterpret_cast<const float4*>(sT + slot0 * kT2TBytes)[row];
             __syncwarp();
-            if (lane == 0) mbar_arrive(&t_empty[s]);    // this warp has its statistics: the tri buffer may be refilled
+            if (lane == 0) mbar_arrive(&t_empty[slot0]);    // this warp has its statistics: the slot may be refilled
             const f32x2 rin = f2_pack(st.x, st.x), tin = f2_pack(st.y, st.y);
             const f32x2 rout = f2_pack(st.z, st.z), tout = f2_pack(st.w, st.w);
             const uint32_t t_g = tmem_base + s * 256 + grp * 64 + lane_bits;     // gate; proj 128 columns on
@@ -379,7 +412,6 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
-            const uint32_t ph = (it >> 1) & 1u;
             const int zs = it % kG2ZStages;
             if (!group_wait<true>(&z_full[zs], (it / kG2ZStages) & 1u, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag,
                             p.status, kStageIdTm2, 300 + zs))
@@ -387,11 +419,13 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             if (pos == 0) TRIMUL_STAMP(3, it, 0);
             float rstd, t;
             row_stats(sZ + zs * kT2XBytes, kT2SubTile, pos, p.eps_in, rstd, t);
-            // the statistics go into the tile's tri buffer once nothing reads the tri data any more
-            if (!group_wait<true>(&tri_dead[s], ph, pos == 0, kG2StatInBarrier, kG2StatThreads, abort_flag, p.status,
-                            kStageIdTm2, 310 + s))
+            // the statistics go into the tile's first tri slot once nothing reads the tri data there any more
+            const uint32_t u0 = it * kKH;
+            const int slot0 = u0 & 1;
+            if (!group_wait<true>(&tri_dead[slot0], (u0 >> 1) & 1u, pos == 0, kG2StatInBarrier, kG2StatThreads,
+                                  abort_flag, p.status, kStageIdTm2, 310 + slot0))
                 break;
-            *reinterpret_cast<float2*>(reinterpret_cast<float4*>(sT + s * kT2TBytes) + pos) = make_float2(rstd, t);
+            *reinterpret_cast<float2*>(reinterpret_cast<float4*>(sT + slot0 * kT2TBytes) + pos) = make_float2(rstd, t);
             mbar_arrive(&stat_in[s]);
             if (pos == 0) TRIMUL_STAMP(3, it, 1);
         }
@@ -407,37 +441,48 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         const int rs = lane & 7;
         const int cq = 4 * tw + ql;
         const uint32_t col_off = (uint32_t)(cq >> 3) * kT2SubTile + ((((uint32_t)cq & 7u) ^ (uint32_t)rs) << 4);
-        const float inv_c = 1.0f / (float)kT2C;
+        const float inv_c = 1.0f / (float)(kT2C * kKH);
         uint32_t it = 0;
-        for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
+        bool alive = true;
+        for (int tile = blockIdx.x; alive && tile < p.total_tiles; tile += gridDim.x, ++it) {
             const int s = it & 1;
-            const uint32_t ph = (it >> 1) & 1u;
-            if (!group_wait<true>(&t_full[s], ph, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag, p.status,
-                            kStageIdTm2, 500 + s))
-                break;
-            if (tid == 0) TRIMUL_STAMP(5, it, 0);
-            const uint8_t* base = sT + s * kT2TBytes + col_off + rs * 128;
-            // common shift of each position: its channel 0 (row 0, held by the rs == 0 lane)
-            const uint4 v0 = *reinterpret_cast<const uint4*>(base);
-            uint32_t sh[4];
-            sh[0] = __shfl_sync(0xffffffffu, v0.x, lane & 24);
-            sh[1] = __shfl_sync(0xffffffffu, v0.y, lane & 24);
-            sh[2] = __shfl_sync(0xffffffffu, v0.z, lane & 24);
-            sh[3] = __shfl_sync(0xffffffffu, v0.w, lane & 24);
-            f32x2 nsh[4], a[4] = {0ull, 0ull, 0ull, 0ull}, qq[4] = {0ull, 0ull, 0ull, 0ull};
-#pragma unroll
-            for (int w = 0; w < 4; ++w) nsh[w] = f2_pack(-bf16_lo(sh[w]), -bf16_hi(sh[w]));
-#pragma unroll 4
-            for (int m = 0; m < 16; ++m) {
-                const uint4 v = *reinterpret_cast<const uint4*>(base + m * 1024);
-                const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
-#pragma unroll
-                for (int w = 0; w < 4; ++w) {
-                    const f32x2 d = f2_add(f2_from_bf16x2(w4[w]), nsh[w]);
-                    a[w] = f2_add(a[w], d);
-                    qq[w] = f2_fma(d, d, qq[w]);
+            uint32_t sh[4] = {0u, 0u, 0u, 0u};
+            f32x2 nsh[4] = {0ull, 0ull, 0ull, 0ull}, a[4] = {0ull, 0ull, 0ull, 0ull}, qq[4] = {0ull, 0ull, 0ull, 0ull};
+#pragma unroll 1
+            for (int h = 0; h < kKH; ++h) {           // the tile's 128-channel halves, one tri slot each
+                const uint32_t u = it * kKH + h;
+                const int ts = u & 1;
+                if (!group_wait<true>(&t_full[ts], (u >> 1) & 1u, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag,
+                                      p.status, kStageIdTm2, 500 + ts)) {
+                    alive = false;
+                    break;
                 }
+                if (tid == 0) TRIMUL_STAMP(5, it, 0);
+                const uint8_t* base = sT + ts * kT2TBytes + col_off + rs * 128;
+                if (h == 0) {
+                    // common shift of each position: its channel 0 (row 0, held by the rs == 0 lane)
+                    const uint4 v0 = *reinterpret_cast<const uint4*>(base);
+                    sh[0] = __shfl_sync(0xffffffffu, v0.x, lane & 24);
+                    sh[1] = __shfl_sync(0xffffffffu, v0.y, lane & 24);
+                    sh[2] = __shfl_sync(0xffffffffu, v0.z, lane & 24);
+                    sh[3] = __shfl_sync(0xffffffffu, v0.w, lane & 24);
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) nsh[w] = f2_pack(-bf16_lo(sh[w]), -bf16_hi(sh[w]));
+                }
+#pragma unroll 4
+                for (int m = 0; m < 16; ++m) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(base + m * 1024);
+                    const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int w = 0; w < 4; ++w) {
+                        const f32x2 d = f2_add(f2_from_bf16x2(w4[w]), nsh[w]);
+                        a[w] = f2_add(a[w], d);
+                        qq[w] = f2_fma(d, d, qq[w]);
+                    }
+                }
+                mbar_arrive(&tri_dead[ts]);             // this thread is done with the slot's tri data
             }
+            if (!alive) break;
             float s1[8], s2[8];
 #pragma unroll
             for (int w = 0; w < 4; ++w) {
@@ -462,12 +507,14 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             const float m1 = s1[0] * inv_c;
             const float rstd = rsqrtf(fmaxf(fmaf(-m1, m1, s2[0] * inv_c), 0.f) + p.eps_out);
             const float t = -(shift + m1) * rstd;
-            mbar_arrive(&tri_dead[s]);                  // this thread is done with the tri data
-            if (!group_wait<true>(&tri_dead[s], ph, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag, p.status,
-                            kStageIdTm2, 510 + s))
+            // the statistics go into the tile's first tri slot once nothing reads the tri data there any more
+            const uint32_t u0 = it * kKH;
+            const int slot0 = u0 & 1;
+            if (!group_wait<true>(&tri_dead[slot0], (u0 >> 1) & 1u, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag,
+                                  p.status, kStageIdTm2, 510 + slot0))
                 break;
             // position 8 cq + rs == tid
-            *(reinterpret_cast<float2*>(reinterpret_cast<float4*>(sT + s * kT2TBytes) + tid) + 1) = make_float2(rstd, t);
+            *(reinterpret_cast<float2*>(reinterpret_cast<float4*>(sT + slot0 * kT2TBytes) + tid) + 1) = make_float2(rstd, t);
             mbar_arrive(&stat_out[s]);
             if (tid == 0) TRIMUL_STAMP(5, it, 1);
         }

@@ -133,7 +133,8 @@ inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 // ---------------------------------------------------------------------------------------
 // validation
 // ---------------------------------------------------------------------------------------
-int check_desc(const trimul_desc* d) {
+// `wide_ok`: the caller (stage 3) accepts c_hidden == 2c, the bidirectional block's layout.
+int check_desc(const trimul_desc* d, bool wide_ok = false) {
     if (d == nullptr || d->struct_bytes != sizeof(trimul_desc)) return TRIMUL_E_INVALID;
     if (d->B <= 0 || d->N <= 0 || d->c <= 0 || d->rows <= 0 || d->row0 < 0) return TRIMUL_E_INVALID;
     if (d->row0 + d->rows > d->N) return TRIMUL_E_INVALID;
@@ -141,9 +142,9 @@ int check_desc(const trimul_desc* d) {
     if (d->direction != TRIMUL_OUTGOING && d->direction != TRIMUL_INCOMING) return TRIMUL_E_INVALID;
     if (d->mask_kind < TRIMUL_MASK_NONE || d->mask_kind > TRIMUL_MASK_PAIR) return TRIMUL_E_INVALID;
     if (!(d->eps_in > 0.f) || !(d->eps_out > 0.f)) return TRIMUL_E_INVALID;
-    if (d->c_hidden != d->c) return TRIMUL_E_UNSUPPORTED;
-    if (d->c > kPlainMaxC || (d->c % 8) != 0) return TRIMUL_E_UNSUPPORTED;
-    if ((int64_t)d->B * d->c > 65535) return TRIMUL_E_UNSUPPORTED;
+    if (d->c_hidden != d->c && !(wide_ok && d->c_hidden == 2 * d->c)) return TRIMUL_E_UNSUPPORTED;
+    if (d->c_hidden > kPlainMaxC || (d->c % 8) != 0) return TRIMUL_E_UNSUPPORTED;
+    if ((int64_t)d->B * d->c_hidden > 65535) return TRIMUL_E_UNSUPPORTED;
     if (d->N > 16384) return TRIMUL_E_UNSUPPORTED;
     return TRIMUL_OK;
 }
@@ -382,7 +383,7 @@ template <typename T>
 int run_plain_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
                   const void* residual, cudaStream_t st) {
     PlainTm2Params p;
-    p.B = d->B; p.rows = d->rows; p.N = d->N; p.c = d->c;
+    p.B = d->B; p.rows = d->rows; p.N = d->N; p.c = d->c; p.h = d->c_hidden;
     p.gamma_in = w->ln_in_weight; p.beta_in = w->ln_in_bias;
     p.gamma_out = w->ln_out_weight; p.beta_out = w->ln_out_bias;
     p.eps_in = d->eps_in; p.eps_out = d->eps_out;
@@ -403,18 +404,21 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     if (!encode_bf16(&tmZ, z, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
     if (!encode_bf16(&tmOut, out, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
     if (!encode_bf16(&tmRes, residual ? residual : z, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    const int kh = d->c_hidden / 128;          // 1, or 2 for the bidirectional block's last stage
     const uint64_t wdims[2] = {128, 128};
     const uint64_t wstrides[1] = {128};
+    const uint64_t wodims[2] = {(uint64_t)d->c_hidden, 128};
+    const uint64_t wostrides[1] = {(uint64_t)d->c_hidden};
     const uint32_t wbox[2] = {64, 128};
     if (!encode_bf16(&tmWg, w->w_gate, 2, wdims, wstrides, wbox, 128)) return TRIMUL_E_CUDA;
-    if (!encode_bf16(&tmWo, w->w_out, 2, wdims, wstrides, wbox, 128)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmWo, w->w_out, 2, wodims, wostrides, wbox, 128)) return TRIMUL_E_CUDA;
     Tm2Params p;
     p.B = d->B; p.rows = d->rows; p.N = d->N;
     p.tiles_per_row = (d->N + kT2P - 1) / kT2P;
     const int64_t total = (int64_t)d->B * d->rows * p.tiles_per_row;
     if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
     p.total_tiles = (int)total;
-    if (!encode_planes(&tmTri, *tri, d->B * 128, 64, 1, 128)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmTri, *tri, d->B * d->c_hidden, 64, 1, 128)) return TRIMUL_E_CUDA;
     p.gamma_in = w->ln_in_weight; p.beta_in = w->ln_in_bias;
     p.gamma_out = w->ln_out_weight; p.beta_out = w->ln_out_bias;
     p.eps_in = d->eps_in; p.eps_out = d->eps_out;
@@ -427,15 +431,23 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
         Tm2FoldParams fp;
         fp.base = p;
         fp.residual_is_z = residual != nullptr;
-        if (residual != nullptr) {
-            if (!ensure_smem(tm2_fold_sm100_kernel<true>, kG2SmemBytes)) return TRIMUL_E_CUDA;
-            tm2_fold_sm100_kernel<true><<<grid, kG2Threads, kG2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmTri, fp);
+#define TRIMUL_LAUNCH_TM2_FOLD(RES, KH)                                                                          \
+    do {                                                                                                          \
+        if (!ensure_smem(tm2_fold_sm100_kernel<RES, KH>, G2Layout<KH>::kSmemBytes)) return TRIMUL_E_CUDA;          \
+        tm2_fold_sm100_kernel<RES, KH><<<grid, kG2Threads, G2Layout<KH>::kSmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, \
+                                                                                          tmTri, fp);             \
+    } while (0)
+        if (kh == 2) {
+            if (residual != nullptr) TRIMUL_LAUNCH_TM2_FOLD(true, 2);
+            else TRIMUL_LAUNCH_TM2_FOLD(false, 2);
         } else {
-            if (!ensure_smem(tm2_fold_sm100_kernel<false>, kG2SmemBytes)) return TRIMUL_E_CUDA;
-            tm2_fold_sm100_kernel<false><<<grid, kG2Threads, kG2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmTri, fp);
+            if (residual != nullptr) TRIMUL_LAUNCH_TM2_FOLD(true, 1);
+            else TRIMUL_LAUNCH_TM2_FOLD(false, 1);
         }
+#undef TRIMUL_LAUNCH_TM2_FOLD
         return launch_status();
     }
+    if (kh != 1) return TRIMUL_E_UNSUPPORTED;      // the in-place variant below is 128 hidden channels only
     if (!ensure_smem(tm2_sm100_kernel, kT2SmemBytes)) return TRIMUL_E_CUDA;
     tm2_sm100_kernel<<<grid, kT2Threads, kT2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmRes, tmTri, p);
     return launch_status();
@@ -608,7 +620,7 @@ int trimul_b200_contract_scatter(int32_t dtype, uint32_t flags, int32_t planes, 
 
 int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes* tri, const trimul_weights* w,
                     void* out, const void* residual, void* stream, int32_t* status) {
-    int rc = check_desc(desc);
+    int rc = check_desc(desc, true);
     if (rc != TRIMUL_OK) return rc;
     if ((rc = check_weights(w)) != TRIMUL_OK) return rc;
     if (z == nullptr || out == nullptr || out == z || !aligned16(z) || !aligned16(out)) return TRIMUL_E_INVALID;
@@ -618,7 +630,12 @@ int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes*
     if (desc->dtype == TRIMUL_DTYPE_FP32) return run_plain_tm2<float>(desc, z, tri, w, out, residual, st);
     const bool plain_layout = tri->row_chunk >= tri->rows && tri->col_chunk >= tri->cols &&
                               (reinterpret_cast<uintptr_t>(tri->base) & 127u) == 0;
-    if (tensor_core_path(desc) && plain_layout) return run_fast_tm2(desc, z, tri, w, out, residual, st, status);
+    if (tensor_core_path(desc) && plain_layout) {
+        // the wide (2c) form exists only in the folded kernel, which takes no residual but z itself
+        const bool wide = desc->c_hidden != desc->c;
+        const bool folded_ok = (desc->flags & TRIMUL_FLAG_INPLACE_NORM_STAGE3) == 0 && (residual == nullptr || residual == z);
+        if (!wide || folded_ok) return run_fast_tm2(desc, z, tri, w, out, residual, st, status);
+    }
     return run_plain_tm2<__nv_bfloat16>(desc, z, tri, w, out, residual, st);
 }
 

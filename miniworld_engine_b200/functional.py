@@ -88,13 +88,15 @@ def workspace_bytes(B: int, N: int, c: int, dtype: torch.dtype, outgoing: bool =
 
 
 def _weights_struct(c, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_right_gate,
-                    ln_out_w, ln_out_b, w_gate, w_out, device):
-    """Validate and pin the parameter tensors; returns (struct, keep-alive list)."""
+                    ln_out_w, ln_out_b, w_gate, w_out, device, c_hidden=None):
+    """Validate and pin the parameter tensors; returns (struct, keep-alive list).  ``c_hidden``
+    (default ``c``) is the width of the output LayerNorm and the input width of ``to_out``."""
     keep = []
+    h = c if c_hidden is None else c_hidden
 
-    def lin(t, name):
-        if tuple(t.shape) != (c, c):
-            raise ValueError(f"{name} must have shape ({c}, {c}), got {tuple(t.shape)}")
+    def lin(t, name, cols=c):
+        if tuple(t.shape) != (c, cols):
+            raise ValueError(f"{name} must have shape ({c}, {cols}), got {tuple(t.shape)}")
         _require_cuda(t, name)
         t = t.detach()
         if t.dtype != dtype or not t.is_contiguous():
@@ -102,9 +104,9 @@ def _weights_struct(c, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_
         keep.append(t)
         return t.data_ptr()
 
-    def vec(t, name):
-        if tuple(t.shape) != (c,):
-            raise ValueError(f"{name} must have shape ({c},), got {tuple(t.shape)}")
+    def vec(t, name, n=c):
+        if tuple(t.shape) != (n,):
+            raise ValueError(f"{name} must have shape ({n},), got {tuple(t.shape)}")
         _require_cuda(t, name)
         t = t.detach()
         if t.dtype != torch.float32 or not t.is_contiguous():
@@ -116,8 +118,8 @@ def _weights_struct(c, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_
         vec(ln_in_w, "norm_in_weight"), vec(ln_in_b, "norm_in_bias"),
         lin(w_left, "to_left.weight"), lin(w_left_gate, "to_left_gate.weight"),
         lin(w_right, "to_right.weight"), lin(w_right_gate, "to_right_gate.weight"),
-        vec(ln_out_w, "norm_out_weight"), vec(ln_out_b, "norm_out_bias"),
-        lin(w_gate, "to_gate.weight"), lin(w_out, "to_out.weight"))
+        vec(ln_out_w, "norm_out_weight", h), vec(ln_out_b, "norm_out_bias", h),
+        lin(w_gate, "to_gate.weight"), lin(w_out, "to_out.weight", h))
     return w, keep
 
 

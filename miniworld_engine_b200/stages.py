@@ -98,9 +98,9 @@ def dense_to_planes(spec: PlaneSpec, dense: torch.Tensor) -> None:
 
 
 def _desc(x, N, outgoing, mask_kind, eps_in, eps_out, plain, row0, pair_stage1=False, folded_stage1=False,
-          inplace_norm=False):
+          inplace_norm=False, c_hidden=None):
     B, rows, _, c = x.shape
-    return _lib.make_desc(B, N, c, dtype=_dtype_code(x),
+    return _lib.make_desc(B, N, c, c_hidden=c_hidden, dtype=_dtype_code(x),
                           direction=_lib.OUTGOING if outgoing else _lib.INCOMING, mask_kind=mask_kind,
                           eps_in=eps_in, eps_out=eps_out,
                           flags=(_lib.FLAG_PLAIN_KERNELS if plain else 0) |
@@ -205,11 +205,15 @@ def contract_scatter(a: PlaneSpec, b: PlaneSpec, tri_dest) -> None:
 def tm2(z_slab: torch.Tensor, tri: PlaneSpec, weights: dict, *, residual=None, row0: int = 0,
         eps_in: float = 1e-5, eps_out: float = 1e-5, plain_kernels: bool = False,
         inplace_norm: bool = False) -> torch.Tensor:
-    """Stage 3 on a ``[B, rows, N, c]`` slab; returns the matching output slab."""
+    """Stage 3 on a ``[B, rows, N, c]`` slab; returns the matching output slab.  The hidden width
+    is read off ``weights["w_out"]`` (``[c, c_hidden]``): ``c``, or ``2c`` for the bidirectional
+    block, whose ``tri`` holds ``B * 2c`` planes (per batch: outgoing planes, then incoming)."""
     _require_cuda(z_slab, "z")
     B, rows, N, c = z_slab.shape
-    d = _desc(z_slab, N, True, _lib.MASK_NONE, eps_in, eps_out, plain_kernels, row0, False, False, inplace_norm)
-    w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, **weights)
+    h = int(weights["w_out"].shape[1])
+    d = _desc(z_slab, N, True, _lib.MASK_NONE, eps_in, eps_out, plain_kernels, row0, False, False, inplace_norm,
+              c_hidden=h)
+    w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, c_hidden=h, **weights)
     out = torch.empty_like(z_slab)
     st = _status_words(z_slab.device)
     with torch.cuda.device(z_slab.device):

@@ -21,6 +21,10 @@ What is restated (paths are relative to the reference project root):
   dtype, affine parameters kept in fp32 under any module cast
   ``src/miniworld_engine/modules/primitives.py:70-88,146-153``
 * sigmoid gate ``src/miniworld_engine/modules/ops.py:11-16``
+* bidirectional block, eager branch: doubled-width input projections, outgoing contraction on
+  the first half of the hidden channels and incoming on the second, one LayerNorm over both,
+  residual always added
+  ``src/miniworld_engine/modules/triangle_multiplication/bidirectional.py:134-156``
 
 Arithmetic notes that matter for parity:
 
@@ -50,6 +54,8 @@ __all__ = [
     "trimul_forward",
     "trimul_forward_functional",
     "trimul_stages",
+    "make_bidir_weights",
+    "bidir_forward",
     "rel_rms",
     "block_flops",
 ]
@@ -249,6 +255,52 @@ def trimul_forward_functional(
         eps_in=eps, eps_out=eps,
     )
     return trimul_stages(x, None, w, direction == "outgoing", pair_mask=mask)["out"]
+
+
+# --------------------------------------------------------------------------- #
+# bidirectional block
+# --------------------------------------------------------------------------- #
+def make_bidir_weights(d: int, h: int | None = None, seed: int = 0, *, affine: str = "unit") -> TrimulWeights:
+    """Seeded weights with the shapes of the reference's bidirectional module
+    (``bidirectional.py:73-84``): ``to_left``, ``to_left_gate``, ``to_right``, ``to_right_gate``
+    are ``[2h, d]`` (rows ``[:h]`` feed the outgoing contraction, ``[h:]`` the incoming one),
+    ``ln_out`` has ``2h`` channels, ``to_gate`` is ``[d, d]`` and ``to_out`` ``[d, 2h]``.  Same
+    field names as ``TrimulWeights``, so ``.to()`` and ``.state_dict()`` apply unchanged."""
+    h = d if h is None else h
+    g = torch.Generator().manual_seed(seed)
+    lin = [torch.randn(2 * h, d, generator=g) * d ** -0.5 for _ in range(4)]
+    to_gate = torch.randn(d, d, generator=g) * d ** -0.5
+    to_out = torch.randn(d, 2 * h, generator=g) * (2 * h) ** -0.5
+    if affine == "unit":
+        gi, bi, go, bo = torch.ones(d), torch.zeros(d), torch.ones(2 * h), torch.zeros(2 * h)
+    elif affine == "random":
+        gi = 1.0 + 0.3 * torch.randn(d, generator=g)
+        bi = 0.2 * torch.randn(d, generator=g)
+        go = 1.0 + 0.3 * torch.randn(2 * h, generator=g)
+        bo = 0.2 * torch.randn(2 * h, generator=g)
+    else:
+        raise ValueError(f"affine must be unit|random, got {affine!r}")
+    return TrimulWeights(gi, bi, lin[0], lin[1], lin[2], lin[3], go, bo, to_gate, to_out)
+
+
+@torch.no_grad()
+def bidir_forward(z: torch.Tensor, token_mask: torch.Tensor | None, w: TrimulWeights,
+                  add_residual: bool = True) -> torch.Tensor:
+    """``pair + bidir_trimul(pair)`` as the eager branch of the reference computes it
+    (``bidirectional.py:134-156``; the residual is unconditional there, ``:105-116``)."""
+    h = w.to_left.shape[0] // 2
+    x_n = _layer_norm(z, w.ln_pair_weight, w.ln_pair_bias, w.eps_in)
+    left = _gate(F.linear(x_n, w.to_left_gate), F.linear(x_n, w.to_left))
+    right = _gate(F.linear(x_n, w.to_right_gate), F.linear(x_n, w.to_right))
+    if token_mask is not None:
+        m2 = (token_mask.unsqueeze(-1) & token_mask.unsqueeze(-2)).unsqueeze(-1)
+        left, right = left * m2, right * m2
+    out_outgoing = torch.einsum("bikd,bjkd->bijd", left[..., :h], right[..., :h])
+    out_incoming = torch.einsum("bkid,bkjd->bijd", left[..., h:], right[..., h:])
+    tri = torch.cat([out_outgoing, out_incoming], dim=-1)
+    tri_n = _layer_norm(tri, w.ln_out_weight, w.ln_out_bias, w.eps_out)
+    out = _gate(F.linear(x_n, w.to_gate), F.linear(tri_n, w.to_out))
+    return out + z if add_residual else out
 
 
 # --------------------------------------------------------------------------- #

@@ -4,9 +4,10 @@ Run where the reference tree is available (it cannot travel to a GPU box):
 
     python tests/golden/make_golden.py --reference /path/to/miniworld-engine
 
-It imports the reference's ``TriangleMultiplicationReference`` and
-``triangle_multiplicative_update_pytorch`` unmodified
-(``src/miniworld_engine/modules/triangle_multiplication/reference.py:32-122``),
+It imports the reference's ``TriangleMultiplicationReference``,
+``triangle_multiplicative_update_pytorch``
+(``src/miniworld_engine/modules/triangle_multiplication/reference.py:32-122``) and
+``BidirectionalTriangleMultiplication`` (``.../bidirectional.py:93-156``, eager branch) unmodified,
 runs them on CPU on the seeded inputs produced by ``oracle/trimul_oracle.py``'s
 generators, and writes one ``.npz`` per case: the inputs actually fed (so a
 change in a random generator cannot silently move the fixture) and the
@@ -40,6 +41,29 @@ CASES = [
     ("func_out_fp32_n10_c32_pairmask", "functional", "fp32", 2, 10, 32, "outgoing", "pair", "random", 30, 31),
     ("func_in_bf16_n10_c32_pairmask", "functional", "bf16", 1, 10, 32, "incoming", "pair", "random", 32, 33),
 ]
+
+
+# bidirectional module (bidirectional.py:93-156): name, dtype, B, N, d, mask kind, affine, weight seed, input seed
+BIDIR_CASES = [
+    ("bidir_fp32_n12_d32_tail3_aff", "fp32", 2, 12, 32, "tail3", "random", 40, 41),
+    ("bidir_bf16_n16_d64_rand5_aff", "bf16", 1, 16, 64, "rand5", "random", 42, 43),
+    ("bidir_bf16_n20_d128_nomask", "bf16", 1, 20, 128, "none", "unit", 44, 45),
+]
+
+
+def run_bidir_reference(case):
+    from miniworld_engine.modules.triangle_multiplication.bidirectional import BidirectionalTriangleMultiplication
+    name, dt, B, N, d, mkind, affine, wseed, zseed = case
+    dtype = torch.float32 if dt == "fp32" else torch.bfloat16
+    w = O.make_bidir_weights(d, d, wseed, affine=affine)
+    z = O.make_input(B, N, d, zseed)
+    mask = None if mkind == "none" else O.make_token_mask(B, N, mkind, seed=zseed + 100)
+    with torch.no_grad():
+        m = BidirectionalTriangleMultiplication(d)
+        m.load_state_dict(w.state_dict())
+        m = m.to(dtype).eval()
+        y = m(z.to(dtype), mask)
+    return z, mask, w, y
 
 
 def build_case(case):
@@ -98,6 +122,17 @@ def main():
                       "z_sum": np.float64(z.double().sum().item()),
                       "z_abs_sum": np.float64(z.double().abs().sum().item()),
                       "w_sum": np.float64(sum(v.double().sum().item() for v in w.state_dict().values()))}
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print(f"{name}: out shape {tuple(y.shape)} dtype {y.dtype} -> {os.path.getsize(path)} B")
+    for case in BIDIR_CASES:
+        name = case[0]
+        z, mask, w, y = run_bidir_reference(case)
+        arrays = {"z": z.numpy(), "out": y.float().numpy()}
+        if mask is not None:
+            arrays["mask"] = mask.numpy()
+        for k, v in w.state_dict().items():
+            arrays["w:" + k] = v.numpy()
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **arrays)
         print(f"{name}: out shape {tuple(y.shape)} dtype {y.dtype} -> {os.path.getsize(path)} B")

@@ -39,11 +39,29 @@ def run_block(z, mask, w, outgoing, dtype, dev, **kw):
     return y.cpu()
 
 
+def run_bidir(z, mask, w, dtype, dev, **kw):
+    """The bidirectional block (residual included, as the reference module returns it)."""
+    from miniworld_engine_b200 import bidir_trimul_forward, read_status
+    wd = w.to(dtype)
+    t = lambda x: x.to(dev)
+    y = bidir_trimul_forward(
+        z.to(dtype).to(dev), None if mask is None else mask.to(dev),
+        ln_in_weight=t(wd.ln_pair_weight), ln_in_bias=t(wd.ln_pair_bias), w_left=t(wd.to_left),
+        w_left_gate=t(wd.to_left_gate), w_right=t(wd.to_right), w_right_gate=t(wd.to_right_gate),
+        ln_out_weight=t(wd.ln_out_weight), ln_out_bias=t(wd.ln_out_bias), w_gate=t(wd.to_gate), w_out=t(wd.to_out),
+        eps_in=w.eps_in, eps_out=w.eps_out, **kw)
+    st = read_status(dev)
+    assert st[0] == 0, f"device status {st}"
+    return y.cpu()
+
+
 @pytest.mark.parametrize("path", FILES, ids=[os.path.basename(f)[:-4] for f in FILES])
 def test_golden_fixture(path, dev):
     name, z, mask, w, gold, dtype, direction, form = load_case(path)
     if form == "module":
         y = run_block(z, mask, w, direction == "outgoing", dtype, dev)
+    elif form == "bidir":
+        y = run_bidir(z, mask, w, dtype, dev)
     else:
         from miniworld_engine_b200 import triangle_multiplicative_update_b200 as f
         wd = w.to(dtype)
@@ -294,3 +312,59 @@ def test_cuda_graph_capture_and_replay(dev):
         torch.cuda.synchronize(dev)
         assert torch.equal(out, eager)
     assert read_status(dev)[0] == 0
+
+
+@pytest.mark.parametrize("B,N,mask_kind,affine", [(1, 128, "ones", "unit"), (1, 200, "tail9", "random"),
+                                                  (2, 96, "rand5", "random")])
+def test_bidirectional_block_bf16_tensor_core_path(dev, B, N, mask_kind, affine):
+    """d = h = 128, bf16: stage 1 twice (one direction each), one contraction over 256 planes per
+    batch element, the wide last stage (LayerNorm over 256 channels folded into a [128, 256]
+    projection).  Oracle: the eager branch of the reference's bidirectional module."""
+    w = O.make_bidir_weights(128, 128, 7, affine=affine)
+    z = O.make_input(B, N, 128, 8)
+    m = O.make_token_mask(B, N, mask_kind, seed=9)
+    ref = O.bidir_forward(z.bfloat16(), m, w.to(torch.bfloat16)).float()
+    y = run_bidir(z, m, w, torch.bfloat16, dev).float()
+    err = O.rel_rms(y, ref)
+    assert err <= TOL_BF16, f"rel-RMS {err:.3e}"
+    # the block's own contribution (without the residual that dominates the norm) must agree too
+    zb = z.bfloat16().float()
+    e_upd = O.rel_rms(y - zb, ref - zb)
+    assert e_upd <= 2e-2, f"update-only rel-RMS {e_upd:.3e}"
+    # tensor-core kernels against the CUDA-core kernels of the same library
+    y_plain = run_bidir(z, m, w, torch.bfloat16, dev, plain_kernels=True).float()
+    assert O.rel_rms(y - zb, y_plain - zb) <= 1.5e-2
+    # without the residual
+    y_nores = run_bidir(z, m, w, torch.bfloat16, dev, add_residual=False).float()
+    ref_nores = O.bidir_forward(z.bfloat16(), m, w.to(torch.bfloat16), add_residual=False).float()
+    assert O.rel_rms(y_nores, ref_nores) <= TOL_BF16
+
+
+def test_bidirectional_block_fp32(dev):
+    w = O.make_bidir_weights(64, 64, 3, affine="random")
+    z = O.make_input(2, 40, 64, 4)
+    m = O.make_token_mask(2, 40, "tail5")
+    y = run_bidir(z, m, w, torch.float32, dev)
+    err = O.rel_rms(y, O.bidir_forward(z, m, w))
+    assert err <= TOL_FP32, f"rel-RMS {err:.3e}"
+
+
+def test_bidirectional_module_mirrors_the_reference_interface(dev):
+    from miniworld_engine_b200 import BidirectionalTriangleMultiplicationB200
+    w = O.make_bidir_weights(128, 128, 11)
+    mod = BidirectionalTriangleMultiplicationB200(128)
+    assert set(mod.state_dict().keys()) == set(w.state_dict().keys())
+    # freshly constructed: gates and to_out are zero, so the block returns its input (residual only)
+    z = O.make_input(1, 64, 128, 2).bfloat16().to(dev)
+    fresh = BidirectionalTriangleMultiplicationB200(128).to(dev).to(torch.bfloat16).eval()
+    with torch.no_grad():
+        assert torch.equal(fresh(z), z)
+    mod.load_state_dict(w.state_dict())
+    mod = mod.to(dev).to(torch.bfloat16).eval()
+    assert mod.ln_pair.weight.dtype == torch.float32 and mod.ln_out.weight.shape == (256,)
+    with torch.no_grad():
+        y = mod(z).float().cpu()
+    ref = O.bidir_forward(z.cpu(), None, w.to(torch.bfloat16)).float()
+    assert O.rel_rms(y, ref) <= TOL_BF16
+    with pytest.raises(NotImplementedError):
+        mod(z.requires_grad_(True))

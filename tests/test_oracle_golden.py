@@ -1,6 +1,6 @@
 """The CPU oracle restates the reference exactly: check it against the golden
 fixtures that ``tests/golden/make_golden.py`` produced by running the reference's
-own ``reference.py`` (module and functional forms)."""
+own ``reference.py`` (module and functional forms) and its bidirectional module."""
 
 import glob
 import os
@@ -41,14 +41,15 @@ def load_case(path):
         mask = torch.from_numpy(d["mask"]) if "mask" in d.files else None
     dtype = torch.bfloat16 if "bf16" in name else torch.float32
     direction = "incoming" if ("in_" in name.split("fp32")[0].split("bf16")[0]) else "outgoing"
-    form = "functional" if name.startswith("func") else "module"
+    form = "functional" if name.startswith("func") else "bidir" if name.startswith("bidir") else "module"
     return name, z, mask, w, torch.from_numpy(d["out"]), dtype, direction, form
 
 
 def test_fixture_set_is_complete():
     names = {os.path.basename(f)[:-4] for f in FILES}
     assert "cfg1_out_fp32_n32_c128" in names
-    assert len(names) >= 9
+    assert len(names) >= 12
+    assert sum(n.startswith("bidir") for n in names) >= 3
 
 
 @pytest.mark.parametrize("path", FILES, ids=[os.path.basename(f)[:-4] for f in FILES])
@@ -58,6 +59,8 @@ def test_oracle_matches_reference_output(path):
     wd = w.to(dtype)
     if form == "module":
         y = O.trimul_forward(z.to(dtype), mask, wd, outgoing=(direction == "outgoing"))
+    elif form == "bidir":
+        y = O.bidir_forward(z.to(dtype), mask, wd)
     else:
         y = O.trimul_forward_functional(
             z.to(dtype), direction, mask, wd.ln_pair_weight, wd.ln_pair_bias,
