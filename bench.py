@@ -53,6 +53,13 @@ WORKLOADS = {
     "n1024_outgoing": (1, 1024, 128, True, "ones"),
     "n2048_outgoing": (1, 2048, 128, True, "rand5"),
 }
+# The bidirectional block (outgoing contraction on the first 128 hidden channels, incoming on the
+# second 128, one LayerNorm over all 256, residual added): single GPU, stage split by CUDA events.
+BIDIR_WORKLOADS = {
+    "n768_bidirectional": (1, 768, 128, "ones"),
+    "n512_bidirectional": (1, 512, 128, "ones"),
+    "n384_bidirectional": (1, 384, 128, "ones"),
+}
 # Outgoing block then incoming block on its output, output rows sharded over the ranks
 # (BASELINE config 5 at N=2048; the smaller ones are quick checks).  Strong scaling.
 PAIR_WORKLOADS = {
@@ -600,13 +607,112 @@ def run_sharded_pair(args):
         dist.destroy_process_group()
 
 
+def run_bidirectional(args):
+    """One bidirectional block per step on one GPU (the reference's pair-track variant,
+    modules/triangle_multiplication/bidirectional.py:93-156), inputs resident in HBM."""
+    import torch
+    from oracle import trimul_oracle as O
+    from miniworld_engine_b200 import read_status, stages as S
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the b200 arm has no CPU path (use --impl reference)")
+    if int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        raise SystemExit("bench.py: the bidirectional workloads are single-GPU")
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    B, N, d, mask_kind = BIDIR_WORKLOADS[args.workload]
+    h = d
+    w = O.make_bidir_weights(d, h, 0).to(torch.bfloat16)
+    z = O.make_input(B, N, d, 1).to(torch.bfloat16).to(dev)
+    m = O.make_token_mask(B, N, mask_kind).to(dev)
+    t = lambda x: x.to(dev)
+    ln_in = (t(w.ln_pair_weight), t(w.ln_pair_bias))
+    wl, wlg, wr, wrg = t(w.to_left), t(w.to_left_gate), t(w.to_right), t(w.to_right_gate)
+    w_gate, w_out = t(w.to_gate), t(w.to_out)
+    planes = B * 2 * h
+    a = S.alloc_planes(planes, N, N, torch.bfloat16, dev)
+    b = S.alloc_planes(planes, N, N, torch.bfloat16, dev)
+    tri = S.alloc_planes(planes, N, N, torch.bfloat16, dev)
+    wd3 = dict(ln_in_w=ln_in[0], ln_in_b=ln_in[1], w_left=w_gate, w_left_gate=w_gate, w_right=w_gate,
+               w_right_gate=w_gate, ln_out_w=t(w.ln_out_weight), ln_out_b=t(w.ln_out_bias), w_gate=w_gate, w_out=w_out)
+    wd1 = []
+    for direction in (0, 1):
+        rows = slice(direction * h, (direction + 1) * h)
+        wd1.append(dict(ln_in_w=ln_in[0], ln_in_b=ln_in[1], w_left=wl[rows], w_left_gate=wlg[rows], w_right=wr[rows],
+                        w_right_gate=wrg[rows], ln_out_w=ln_in[0], ln_out_b=ln_in[1], w_gate=w_gate, w_out=w_gate))
+    views = []
+    for direction in (0, 1):
+        first = direction * h * a.plane_stride
+        views.append(tuple(S.PlaneSpec(sp.buf[first:], h, N, N, sp.pitch, sp.plane_stride) for sp in (a, b)))
+
+    def step(ev=None):
+        mark = (lambda: (ev.append(torch.cuda.Event(enable_timing=True)), ev[-1].record())) if ev is not None else (lambda: None)
+        mark()
+        for direction in (0, 1):
+            S.tm1(z, m, wd1[direction], views[direction][0], views[direction][1], outgoing=(direction == 0))
+        mark()
+        S.contract(a, b, tri)
+        mark()
+        y = S.tm2(z, tri, wd3, residual=z)
+        mark()
+        return y
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(dev)
+    sampler = ClockSampler(0)
+    all_ev = []
+    for _ in range(args.steps):
+        ev = []
+        step(ev)
+        all_ev.append(ev)
+    torch.cuda.synchronize(dev)
+    clocks = sampler.stop()
+    if read_status(dev)[0] != 0:
+        raise SystemExit(f"bench.py: device status {read_status(dev)}: timing is invalid")
+    ms = all_ev[0][0].elapsed_time(all_ev[-1][-1]) / args.steps
+    stage_ms = [sum(e[i].elapsed_time(e[i + 1]) for e in all_ev) / args.steps for i in range(3)]
+    M = B * N * N
+    flops = 22.0 * M * d * d + 4.0 * B * N ** 3 * d      # 4 [2h,d] + [d,d] + [d,2h] projections; 2h planes contracted
+    S_bytes = M * d * 2
+    peaks = measured_peaks()
+    # algorithmic bytes: stage 1 reads z twice and writes 4 S; contraction reads 4 S, writes 2 S; stage 3 reads 3 S, writes S
+    alg = {"tm1 x2": 6 * S_bytes, "contract": None, "tm2 (wide)": 4 * S_bytes}
+    stages = {}
+    for name, v in zip(alg, stage_ms):
+        if alg[name] is None:
+            ach = 4.0 * B * N ** 3 * d / (v * 1e-3) / 1e12
+            stages[name] = {"ms": v, "bound": "tensor", "achieved": ach, "unit": "TFLOP/s",
+                            "peak": peaks["bf16_tflops_sustained"], "frac": ach / peaks["bf16_tflops_sustained"]}
+        else:
+            ach = alg[name] / (v * 1e-3) / 1e9
+            stages[name] = {"ms": v, "bound": "hbm", "achieved": ach, "unit": "GB/s", "peak": peaks["hbm_gbs"],
+                            "frac": ach / peaks["hbm_gbs"]}
+    dom = max(stages, key=lambda k: stages[k]["ms"])
+    line = {
+        "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": 1, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "calls_per_s": 1e3 / ms, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic (seeded randn pair tensor and weights, all-ones LayerNorm gamma)",
+        "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "config": {"workload": args.workload, "B": B, "N": N, "c": d, "c_hidden": 2 * h,
+                   "direction": "bidirectional (outgoing + incoming halves), residual added", "mask": mask_kind,
+                   "parallelism": "single GPU",
+                   "l2": "working set exceeds the 126 MB L2 for N >= 512; no flush"},
+        "gpu_launches": 4 * args.steps,
+        "roofline": dict(stages[dom], kernel=dom, peak_source=peaks["source"], traffic=None),
+        "stages": stages, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=None)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="n768_outgoing", choices=sorted(WORKLOADS) + sorted(PAIR_WORKLOADS))
+    ap.add_argument("--workload", default="n768_outgoing", choices=sorted(WORKLOADS) + sorted(PAIR_WORKLOADS) + sorted(BIDIR_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--shard-mode", default="rows", choices=["rows", "channels", "peer"],
                     help="exchange pattern of the *_pair_sharded workloads")
@@ -620,6 +726,8 @@ def main():
         args.warmup = 5 if args.warmup is None else args.warmup
         if args.workload in PAIR_WORKLOADS:
             run_sharded_pair(args)
+        elif args.workload in BIDIR_WORKLOADS:
+            run_bidirectional(args)
         else:
             run_b200(args)
 
