@@ -233,6 +233,24 @@ int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes*
                     void* stream, int32_t* status);
 
 /*
+ * The whole BIDIRECTIONAL block (bidirectional.py:93-156): one input LayerNorm, the four gated
+ * projections of width 2c (rows [0,c) of each weight feed an outgoing contraction, rows [c,2c) an
+ * incoming one), one LayerNorm over the 2c result channels, to_out [c,2c] gated by to_gate(x_n);
+ * `add_residual` != 0 adds z (what the reference module always returns).
+ * `desc`: c_hidden = 2c, rows = N, row0 = 0; `direction` is ignored; mask kinds as in the
+ * single-direction block.  `w`: w_left, w_left_gate, w_right, w_right_gate are [2c, c]; ln_out_*
+ * have 2c entries; w_gate is [c, c]; w_out is [c, 2c].  The workspace holds three plane sets of
+ * B*2c planes (trimul_b200_bidir_workspace_bytes); per batch element planes [0,c) belong to the
+ * outgoing half and [c,2c) to the incoming half.  Replaces the sm_100 path
+ * BidirectionalTriangleMultiplication._forward_cute (bidirectional.py:118-132;
+ * kernels/trimul_inproj/cute/bidirectional_sm100.py:33-71).
+ */
+int trimul_b200_bidir_workspace_bytes(const trimul_desc* desc, size_t* bytes);
+int trimul_b200_forward_bidir(const trimul_desc* desc, const void* z, const uint8_t* mask,
+                              const trimul_weights* w, void* out, int32_t add_residual,
+                              void* workspace, size_t workspace_bytes, void* stream, int32_t* status);
+
+/*
  * The whole block for callers that have no device memory to offer as a workspace.
  * (No counterpart in the reference: its launchers allocate their intermediates with torch.)
  *

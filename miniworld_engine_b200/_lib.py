@@ -37,6 +37,8 @@ EXPORTED_SYMBOLS = (
     "trimul_b200_tm2",
     "trimul_b200_forward_static",
     "trimul_b200_tm1_scatter",
+    "trimul_b200_bidir_workspace_bytes",
+    "trimul_b200_forward_bidir",
     "trimul_b200_contract_scatter",
 )
 
@@ -99,6 +101,11 @@ def load():
     lib.trimul_b200_contract_scatter.restype = C.c_int
     lib.trimul_b200_contract_scatter.argtypes = [C.c_int32, C.c_uint32, C.c_int32, PP, PP, C.c_int32, PP, C.c_void_p,
                                                  C.c_void_p]
+    lib.trimul_b200_bidir_workspace_bytes.restype = C.c_int
+    lib.trimul_b200_bidir_workspace_bytes.argtypes = [PD, C.POINTER(C.c_size_t)]
+    lib.trimul_b200_forward_bidir.restype = C.c_int
+    lib.trimul_b200_forward_bidir.argtypes = [PD, C.c_void_p, C.c_void_p, PW, C.c_void_p, C.c_int32, C.c_void_p,
+                                              C.c_size_t, C.c_void_p, C.c_void_p]
     lib.trimul_b200_tm2.restype = C.c_int
     lib.trimul_b200_tm2.argtypes = [PD, C.c_void_p, PP, PW, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     lib.trimul_b200_forward_static.restype = C.c_int

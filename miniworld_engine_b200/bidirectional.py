@@ -6,7 +6,8 @@ LayerNorm, left/right gated projections of width ``2h`` (rows ``[:h]`` of each w
 OUTGOING contraction, rows ``[h:]`` an INCOMING one), one LayerNorm over the ``2h`` concatenated
 result channels, ``to_out: 2h -> d`` gated by ``to_gate(x_n)``, residual always added.
 
-It is assembled from the stage entry points of the C-ABI library (``include/trimul_b200.h``):
+``trimul_b200_forward_bidir`` of the C-ABI library (``include/trimul_b200.h``) assembles it from
+the stage entry points:
 
 * stage 1 runs twice per batch element, once per direction, each call with its half of the
   projection weights (a contiguous row block of the ``[2h, d]`` matrices) and writing its ``h``
@@ -22,10 +23,13 @@ the CUDA-core kernels (``2h <= 256``).
 
 from __future__ import annotations
 
+import ctypes as C
+
 import torch
 import torch.nn as nn
 
-from . import stages as S
+from . import _lib
+from .functional import _dtype_code, _mask_bytes, _require_cuda, _status_words, _workspace
 from .module import PinnedLayerNormParams
 
 __all__ = ["bidir_trimul_forward", "BidirectionalTriangleMultiplicationB200"]
@@ -62,33 +66,66 @@ def bidir_trimul_forward(
         raise ValueError(f"w_out must be [{d}, {h2}] and w_gate [{d}, {d}]")
     if mask is not None and tuple(mask.shape) != (B, N):
         raise ValueError(f"mask must be [B, N], got {tuple(mask.shape)}")
+    _require_cuda(x, "x")
     x = x.detach().contiguous()
-    dev, dt = x.device, x.dtype
-    cast = lambda t: t.detach().to(dt).contiguous()
-    w_left, w_left_gate, w_right, w_right_gate = map(cast, (w_left, w_left_gate, w_right, w_right_gate))
-    w_gate, w_out = cast(w_gate), cast(w_out)
+    mask_kind, mask_u8 = _lib.MASK_NONE, None
+    if mask is not None:
+        _require_cuda(mask, "mask")
+        mask_kind, mask_u8 = _lib.MASK_TOKEN, _mask_bytes(mask)
+    desc = _lib.make_desc(B, N, d, c_hidden=h2, dtype=_dtype_code(x), direction=_lib.OUTGOING, mask_kind=mask_kind,
+                          eps_in=eps_in, eps_out=eps_out, flags=_lib.FLAG_PLAIN_KERNELS if plain_kernels else 0)
+    w, keep = _bidir_weights_struct(d, h2, x.dtype, ln_in_weight, ln_in_bias, w_left, w_left_gate, w_right,
+                                    w_right_gate, ln_out_weight, ln_out_bias, w_gate, w_out)
+    lib = _lib.load()
+    nbytes = C.c_size_t()
+    _lib.check(lib.trimul_b200_bidir_workspace_bytes(C.byref(desc), C.byref(nbytes)),
+               "trimul_b200_bidir_workspace_bytes")
+    with torch.cuda.device(x.device):
+        ws = _workspace(x.device, nbytes.value)
+        out = torch.empty_like(x)
+        st = _status_words(x.device)
+        rc = lib.trimul_b200_forward_bidir(
+            C.byref(desc), x.data_ptr(), mask_u8.data_ptr() if mask_u8 is not None else None, C.byref(w),
+            out.data_ptr(), 1 if add_residual else 0, ws.data_ptr(), ws.numel(),
+            torch.cuda.current_stream(x.device).cuda_stream, st.data_ptr())
+    _lib.check(rc, "trimul_b200_forward_bidir")
+    for t in keep:      # parameter copies made above must outlive the enqueued kernels
+        t.record_stream(torch.cuda.current_stream(x.device))
+    return out
 
-    planes = B * h2
-    a = S.alloc_planes(planes, N, N, dt, dev)
-    b = S.alloc_planes(planes, N, N, dt, dev)
-    tri = S.alloc_planes(planes, N, N, dt, dev)
-    for bi in range(B):
-        zb = x[bi:bi + 1]
-        mb = None if mask is None else mask[bi:bi + 1]
-        for direction in (0, 1):          # 0: outgoing half, 1: incoming half
-            rows = slice(direction * h, (direction + 1) * h)
-            first = (bi * h2 + direction * h) * a.plane_stride
-            view = lambda spec: S.PlaneSpec(spec.buf[first:], h, N, N, spec.pitch, spec.plane_stride)
-            # stage 1 reads only the input-side parameters; the output-side slots get placeholders
-            wd = dict(ln_in_w=ln_in_weight, ln_in_b=ln_in_bias, w_left=w_left[rows], w_left_gate=w_left_gate[rows],
-                      w_right=w_right[rows], w_right_gate=w_right_gate[rows], ln_out_w=ln_in_weight,
-                      ln_out_b=ln_in_bias, w_gate=w_gate, w_out=w_gate)
-            S.tm1(zb, mb, wd, view(a), view(b), outgoing=(direction == 0), eps=eps_in, plain_kernels=plain_kernels)
-    S.contract(a, b, tri, plain_kernels=plain_kernels)
-    wd3 = dict(ln_in_w=ln_in_weight, ln_in_b=ln_in_bias, w_left=w_gate, w_left_gate=w_gate, w_right=w_gate,
-               w_right_gate=w_gate, ln_out_w=ln_out_weight, ln_out_b=ln_out_bias, w_gate=w_gate, w_out=w_out)
-    return S.tm2(x, tri, wd3, residual=x if add_residual else None, eps_in=eps_in, eps_out=eps_out,
-                 plain_kernels=plain_kernels)
+
+def _bidir_weights_struct(d, h2, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_right_gate,
+                          ln_out_w, ln_out_b, w_gate, w_out):
+    """Validate and pin the bidirectional block's parameters; returns (struct, keep-alive list)."""
+    keep = []
+
+    def lin(t, name, shape):
+        if tuple(t.shape) != shape:
+            raise ValueError(f"{name} must have shape {shape}, got {tuple(t.shape)}")
+        _require_cuda(t, name)
+        t = t.detach()
+        if t.dtype != dtype or not t.is_contiguous():
+            t = t.to(dtype).contiguous()
+        keep.append(t)
+        return t.data_ptr()
+
+    def vec(t, name, n):
+        if tuple(t.shape) != (n,):
+            raise ValueError(f"{name} must have shape ({n},), got {tuple(t.shape)}")
+        _require_cuda(t, name)
+        t = t.detach()
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            t = t.float().contiguous()
+        keep.append(t)
+        return t.data_ptr()
+
+    w = _lib.Weights(
+        vec(ln_in_w, "ln_pair.weight", d), vec(ln_in_b, "ln_pair.bias", d),
+        lin(w_left, "to_left.weight", (h2, d)), lin(w_left_gate, "to_left_gate.weight", (h2, d)),
+        lin(w_right, "to_right.weight", (h2, d)), lin(w_right_gate, "to_right_gate.weight", (h2, d)),
+        vec(ln_out_w, "ln_out.weight", h2), vec(ln_out_b, "ln_out.bias", h2),
+        lin(w_gate, "to_gate.weight", (d, d)), lin(w_out, "to_out.weight", (d, h2)))
+    return w, keep
 
 
 class BidirectionalTriangleMultiplicationB200(nn.Module):

@@ -666,6 +666,66 @@ int trimul_b200_forward(const trimul_desc* desc, const void* z, const uint8_t* m
     return trimul_b200_tm2(desc, z, &t, w, out, residual, stream, status);
 }
 
+int trimul_b200_bidir_workspace_bytes(const trimul_desc* desc, size_t* bytes) {
+    int rc = check_desc(desc, true);
+    if (rc != TRIMUL_OK) return rc;
+    if (bytes == nullptr || desc->c_hidden != 2 * desc->c) return TRIMUL_E_INVALID;
+    if (desc->rows != desc->N || desc->row0 != 0) return TRIMUL_E_INVALID;
+    const int64_t esz = desc->dtype == TRIMUL_DTYPE_BF16 ? 2 : 4;
+    const int64_t set_bytes = round_up((int64_t)desc->B * desc->c_hidden * desc->N * round_up(desc->N, 8) * esz, 1024);
+    *bytes = (size_t)(3 * set_bytes);
+    return TRIMUL_OK;
+}
+
+int trimul_b200_forward_bidir(const trimul_desc* desc, const void* z, const uint8_t* mask, const trimul_weights* w,
+                              void* out, int32_t add_residual, void* workspace, size_t workspace_bytes, void* stream,
+                              int32_t* status) {
+    size_t need = 0;
+    int rc = trimul_b200_bidir_workspace_bytes(desc, &need);
+    if (rc != TRIMUL_OK) return rc;
+    if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255u) != 0) return TRIMUL_E_INVALID;
+    if (workspace_bytes < need) return TRIMUL_E_WORKSPACE;
+    if ((rc = check_weights(w)) != TRIMUL_OK) return rc;
+    if (z == nullptr || out == nullptr || out == z || !aligned16(z) || !aligned16(out)) return TRIMUL_E_INVALID;
+    if (desc->mask_kind != TRIMUL_MASK_NONE && mask == nullptr) return TRIMUL_E_INVALID;
+    const int64_t esz = desc->dtype == TRIMUL_DTYPE_BF16 ? 2 : 4;
+    const int64_t N = desc->N, c = desc->c, pitch = round_up(N, 8), plane = N * pitch;
+    const int64_t set_bytes = (int64_t)(need / 3);
+    uint8_t* base = static_cast<uint8_t*>(workspace);
+    // stage 1: per batch element and direction, with that direction's rows of the [2c, c] weights
+    trimul_desc d1 = *desc;
+    d1.B = 1;
+    d1.c_hidden = desc->c;
+    for (int bi = 0; bi < desc->B; ++bi) {
+        const uint8_t* zb = static_cast<const uint8_t*>(z) + (int64_t)bi * N * N * c * esz;
+        const uint8_t* mb = mask == nullptr ? nullptr
+                          : mask + (int64_t)bi * (desc->mask_kind == TRIMUL_MASK_PAIR ? N * N : N);
+        for (int dir = 0; dir < 2; ++dir) {
+            d1.direction = dir == 0 ? TRIMUL_OUTGOING : TRIMUL_INCOMING;
+            trimul_weights w1 = *w;
+            const int64_t wofs = (int64_t)dir * c * c * esz;
+            w1.w_left = static_cast<const uint8_t*>(w->w_left) + wofs;
+            w1.w_left_gate = static_cast<const uint8_t*>(w->w_left_gate) + wofs;
+            w1.w_right = static_cast<const uint8_t*>(w->w_right) + wofs;
+            w1.w_right_gate = static_cast<const uint8_t*>(w->w_right_gate) + wofs;
+            const int64_t first = ((int64_t)bi * 2 * c + (int64_t)dir * c) * plane * esz;
+            trimul_planes pa = {base + first, N, N, pitch, plane, 0, N, N};
+            trimul_planes pb = pa;
+            pb.base = base + set_bytes + first;
+            if ((rc = trimul_b200_tm1(&d1, zb, mb, &w1, &pa, &pb, stream, status)) != TRIMUL_OK) return rc;
+        }
+    }
+    // stage 2: one contraction over all B * 2c planes; stage 3: the wide last stage
+    trimul_planes a = {base, N, N, pitch, plane, 0, N, N};
+    trimul_planes b = a, t = a;
+    b.base = base + set_bytes;
+    t.base = base + 2 * set_bytes;
+    if ((rc = trimul_b200_contract(desc->dtype, desc->flags, desc->B * desc->c_hidden, &a, &b, &t, stream, status)) !=
+        TRIMUL_OK)
+        return rc;
+    return trimul_b200_tm2(desc, z, &t, w, out, add_residual ? z : nullptr, stream, status);
+}
+
 // ---------------------------------------------------------------------------------------
 // built-in scratch: device address of g_static_scratch, looked up once per device
 // ---------------------------------------------------------------------------------------

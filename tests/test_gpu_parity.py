@@ -368,3 +368,35 @@ def test_bidirectional_module_mirrors_the_reference_interface(dev):
     assert O.rel_rms(y, ref) <= TOL_BF16
     with pytest.raises(NotImplementedError):
         mod(z.requires_grad_(True))
+
+
+def test_bidirectional_entry_point_equals_the_stage_calls_it_is_made_of(dev):
+    """trimul_b200_forward_bidir = stage 1 per direction with its rows of the [2h, d] weights, one
+    contraction over 2h planes, the wide last stage: assembling the same calls by hand must give
+    the same bits."""
+    from miniworld_engine_b200 import stages as S
+    N, d = 160, 128
+    w = O.make_bidir_weights(d, d, 21, affine="random").to(torch.bfloat16)
+    z = O.make_input(1, N, d, 22).bfloat16().to(dev)
+    m = O.make_token_mask(1, N, "tail11").to(dev)
+    y = run_bidir(z.cpu().float(), m.cpu(), w, torch.bfloat16, dev)
+    t = lambda x: x.to(dev)
+    a = S.alloc_planes(2 * d, N, N, torch.bfloat16, dev)
+    b = S.alloc_planes(2 * d, N, N, torch.bfloat16, dev)
+    tri = S.alloc_planes(2 * d, N, N, torch.bfloat16, dev)
+    w_gate = t(w.to_gate)
+    for direction in (0, 1):
+        rows = slice(direction * d, (direction + 1) * d)
+        first = direction * d * a.plane_stride
+        va, vb = (S.PlaneSpec(sp.buf[first:], d, N, N, sp.pitch, sp.plane_stride) for sp in (a, b))
+        wd = dict(ln_in_w=t(w.ln_pair_weight), ln_in_b=t(w.ln_pair_bias), w_left=t(w.to_left)[rows],
+                  w_left_gate=t(w.to_left_gate)[rows], w_right=t(w.to_right)[rows],
+                  w_right_gate=t(w.to_right_gate)[rows], ln_out_w=t(w.ln_pair_weight), ln_out_b=t(w.ln_pair_bias),
+                  w_gate=w_gate, w_out=w_gate)
+        S.tm1(z, m, wd, va, vb, outgoing=(direction == 0))
+    S.contract(a, b, tri)
+    wd3 = dict(ln_in_w=t(w.ln_pair_weight), ln_in_b=t(w.ln_pair_bias), w_left=w_gate, w_left_gate=w_gate,
+               w_right=w_gate, w_right_gate=w_gate, ln_out_w=t(w.ln_out_weight), ln_out_b=t(w.ln_out_bias),
+               w_gate=w_gate, w_out=t(w.to_out))
+    y2 = S.tm2(z, tri, wd3, residual=z).cpu()
+    assert torch.equal(y, y2)
