@@ -57,7 +57,7 @@ struct G2Layout {
     static constexpr int kZStages = kKH == 1 ? 3 : 2;
     static constexpr int kOffZ = kWBytes;                        // z ring, 32 KB per stage
     static constexpr int kOffT = kOffZ + kZStages * kT2XBytes;   // 2 x 32 KB tri ring; once a tile's tri data is dead the
-                                                                 // first 2 KB of its first slot hold [128 positions]
+                                                                 // first 2 KB of its last slot hold [128 positions]
                                                                  // (r_in, t_in, r_out, t_out)
     static constexpr int kOffConst = kOffT + 2 * kT2TBytes;      // [2 matrices][64 channel pairs] (s0, s1, b0, b1)
     static constexpr int kOffBars = kOffConst + 2048;
@@ -198,9 +198,10 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                     const uint32_t u = it * kKH + h;
                     const int ts = u & 1;
                     const uint32_t tph = (u >> 1) & 1u;
-                    // a tile's first slot carries the statistics and is released by the epilogue; any
-                    // other slot is free as soon as its readers are done
-                    uint64_t* freed = h == 0 ? &t_empty[ts] : &tri_dead[ts];
+                    // a tile's LAST slot carries the statistics and is released by the epilogue; any
+                    // other slot is free as soon as its readers are done (so the next tile's first half
+                    // streams in while this tile's last half is still being worked on)
+                    uint64_t* freed = h == kKH - 1 ? &t_empty[ts] : &tri_dead[ts];
                     if (!mbar_wait<true>(freed, tph ^ 1u, abort_flag, p.status, kStageIdTm2, 100 + ts)) {
                         okp = false;
                         break;
@@ -328,6 +329,8 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         mbar_arrive(w_ready);
         // every channel's constants are needed by every epilogue thread
         run = run && mbar_wait<true>(w_ready, 0, abort_flag, p.status, kStageIdTm2, 160);
+        // one verdict per group: a thread that gave up must not leave the others at the group's barrier
+        run = named_barrier_all(bar_id, 128, run);
 
         const uint32_t lane_bits = (uint32_t)(q * 32) << 16;
         const ulonglong2* cG = reinterpret_cast<const ulonglong2*>(sConst) + grp * 32;
@@ -346,7 +349,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             if (!named_barrier_all(bar_id, 128, ok)) break;
             tcgen05_fence_after();
             if (e == 0) TRIMUL_STAMP(4, it, 0);
-            const int slot0 = (it * kKH) & 1;           // the tile's first tri slot carries its statistics
+            const int slot0 = (it * kKH + kKH - 1) & 1;     // the tile's last tri slot carries its statistics
             const float4 st = reinterpret_cast<const float4*>(sT + slot0 * kT2TBytes)[row];
             __syncwarp();
             if (lane == 0) mbar_arrive(&t_empty[slot0]);    // this warp has its statistics: the slot may be refilled
@@ -419,8 +422,8 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             if (pos == 0) TRIMUL_STAMP(3, it, 0);
             float rstd, t;
             row_stats(sZ + zs * kT2XBytes, kT2SubTile, pos, p.eps_in, rstd, t);
-            // the statistics go into the tile's first tri slot once nothing reads the tri data there any more
-            const uint32_t u0 = it * kKH;
+            // the statistics go into the tile's last tri slot once nothing reads the tri data there any more
+            const uint32_t u0 = it * kKH + kKH - 1;
             const int slot0 = u0 & 1;
             if (!group_wait<true>(&tri_dead[slot0], (u0 >> 1) & 1u, pos == 0, kG2StatInBarrier, kG2StatThreads,
                                   abort_flag, p.status, kStageIdTm2, 310 + slot0))
@@ -507,8 +510,8 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             const float m1 = s1[0] * inv_c;
             const float rstd = rsqrtf(fmaxf(fmaf(-m1, m1, s2[0] * inv_c), 0.f) + p.eps_out);
             const float t = -(shift + m1) * rstd;
-            // the statistics go into the tile's first tri slot once nothing reads the tri data there any more
-            const uint32_t u0 = it * kKH;
+            // the statistics go into the tile's last tri slot once nothing reads the tri data there any more
+            const uint32_t u0 = it * kKH + kKH - 1;
             const int slot0 = u0 & 1;
             if (!group_wait<true>(&tri_dead[slot0], (u0 >> 1) & 1u, tid == 0, kG2StatOutBarrier, kG2StatThreads, abort_flag,
                                   p.status, kStageIdTm2, 510 + slot0))
