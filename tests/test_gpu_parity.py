@@ -400,3 +400,38 @@ def test_bidirectional_entry_point_equals_the_stage_calls_it_is_made_of(dev):
                w_gate=w_gate, w_out=t(w.to_out))
     y2 = S.tm2(z, tri, wd3, residual=z).cpu()
     assert torch.equal(y, y2)
+
+
+def test_full_size_symmetric_input_makes_both_directions_identical(dev):
+    """Size-independent property, checked at a full benchmark size (N = 1024, no oracle run needed):
+    for a pair tensor with z[i,j] = z[j,i] the incoming operands a'[i][k] = a[k,i] equal the outgoing
+    ones bit for bit, the contraction sums over k in the same order, and the last stage is the
+    same — so the two directions must return identical tensors."""
+    N = 1024
+    w = O.make_weights(128, 4, affine="random")
+    g = torch.Generator().manual_seed(12)
+    z = torch.randn(1, N, N, 128, generator=g)
+    z = (0.5 * (z + z.transpose(1, 2))).bfloat16()
+    assert torch.equal(z, z.transpose(1, 2))
+    m = O.make_token_mask(1, N, "rand5", seed=3)
+    out = run_block(z.float(), m, w, True, torch.bfloat16, dev)
+    inc = run_block(z.float(), m, w, False, torch.bfloat16, dev)
+    assert torch.equal(out, inc)
+    assert float(out.float().abs().max()) > 0
+
+
+def test_full_size_token_permutation_equivariance(dev):
+    """Relabelling the tokens (z'[i,j] = z[p(i),p(j)], mask' = mask[p]) must relabel the output the
+    same way; only the order of the k-summation changes, so the agreement is to accumulation
+    noise, far inside the bf16 tolerance.  N = 768, the headline size."""
+    N = 768
+    w = O.make_weights(128, 0)
+    z = O.make_input(1, N, 128, 1).bfloat16()
+    m = O.make_token_mask(1, N, "tail77")
+    p = torch.randperm(N, generator=torch.Generator().manual_seed(8))
+    zp = z[:, p][:, :, p].contiguous()
+    for outgoing in (True, False):
+        y = run_block(z.float(), m, w, outgoing, torch.bfloat16, dev)
+        yp = run_block(zp.float(), m[:, p], w, outgoing, torch.bfloat16, dev)
+        err = O.rel_rms(yp.float(), y[:, p][:, :, p].float())
+        assert err <= 3e-3, f"outgoing={outgoing}: rel-RMS {err:.3e}"
