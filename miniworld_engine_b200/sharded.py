@@ -265,6 +265,20 @@ class PeerShardContext:
     after its contraction of block t.
     """
 
+    @staticmethod
+    def supported(B: int, N: int, c: int, dtype: torch.dtype, world: int) -> bool:
+        """Whether the scattering kernels exist for this problem on ``world`` ranks: bf16, c = 128
+        (tensor-core kernels), at most 8 ranks, a rank's share of the ``B*c`` planes a multiple of
+        8 that divides or is a multiple of 128, and ``N/world`` rows per rank a multiple of 128.
+        Otherwise use ``trimul_forward_sharded(mode="channels")``, which does the same exchanges
+        with NCCL all-to-alls."""
+        if dtype != torch.bfloat16 or c != 128 or not 1 <= world <= 8:
+            return False
+        if N % world or (B * c) % world:
+            return False
+        per, rows = B * c // world, N // world
+        return per % 8 == 0 and (128 % per == 0 or per % 128 == 0) and rows % 128 == 0
+
     def __init__(self, B: int, N: int, c: int, dtype: torch.dtype, device, group=None):
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
@@ -273,6 +287,9 @@ class PeerShardContext:
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.B, self.N, self.c, self.dtype, self.device = B, N, c, dtype, torch.device(device)
+        if not self.supported(B, N, c, dtype, self.world):
+            raise ValueError(f"no scattering kernels for B={B}, N={N}, c={c}, {dtype} on {self.world} rank(s); "
+                             "use trimul_forward_sharded(mode='channels')")
         plans = [ChannelShardPlan(B, N, c, self.world, self.rank, o) for o in (True, False)]
         n_op = max(p.planes * p._op_plane_elems() for p in plans)
         n_tri = plans[0].planes * plans[0].R * plans[0].pitch_full

@@ -162,3 +162,15 @@ def test_peer_destinations_are_the_chunks_the_contraction_reads(world, outgoing)
             S.dense_to_planes(t_d[d], tri_full[r * Pp:(r + 1) * Pp, d * R:(d + 1) * R])
     for r, p in enumerate(plans):
         assert torch.equal(S.planes_to_dense(p.tri_spec(bufs[r])), tri_full[:, r * R:(r + 1) * R])
+
+
+def test_peer_scheme_support_matrix():
+    from miniworld_engine_b200.sharded import PeerShardContext as P
+    bf16, f32 = torch.bfloat16, torch.float32
+    assert P.supported(1, 2048, 128, bf16, 8)        # the benchmark configuration: 16 planes, 256 rows per rank
+    assert P.supported(1, 1024, 128, bf16, 8) and P.supported(1, 512, 128, bf16, 2) and P.supported(2, 256, 128, bf16, 2)
+    assert not P.supported(1, 768, 128, bf16, 8)     # 96 rows per rank: a contraction tile would straddle two ranks
+    assert not P.supported(1, 2048, 128, f32, 8)     # no fp32 tensor-core kernels
+    assert not P.supported(1, 2048, 64, bf16, 8)
+    assert not P.supported(1, 2048, 128, bf16, 16)
+    assert not P.supported(1, 1000, 128, bf16, 8)
