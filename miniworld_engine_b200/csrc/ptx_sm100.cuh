@@ -692,4 +692,42 @@ __device__ __forceinline__ void row_stats(const uint8_t* tile, int sub_bytes, in
 }
 
 
+// Fold one row (output channel n) of a weight matrix that lies in shared memory as `nsub` swizzled
+// 64-column sub-tiles (`sub_bytes` apart): w[k] <- bf16(w[k] * gamma[k] / 2).  Returns the sum of the rounded row and
+// 0.5 * sum_k w[k] * beta[k].
+__device__ __forceinline__ void fold_row_smem(uint8_t* wbase, int sub_bytes, int n, const float* gamma,
+                                              const float* beta, int nsub, float& s, float& bias) {
+    float ssum = 0.f, bsum = 0.f;
+    const uint32_t swz = (uint32_t)(n & 7);
+#pragma unroll 1
+    for (int kh = 0; kh < nsub; ++kh) {
+#pragma unroll 2
+        for (int j = 0; j < 8; ++j) {
+            uint4* ptr = reinterpret_cast<uint4*>(wbase + kh * sub_bytes + n * 128 + ((((uint32_t)j) ^ swz) << 4));
+            const uint4 v = *ptr;
+            const int k0 = kh * 64 + j * 8;
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + k0));
+            const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + k0 + 4));
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + k0));
+            const float4 b1 = __ldg(reinterpret_cast<const float4*>(beta + k0 + 4));
+            const float ga[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+            const float be[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            const uint32_t w4[4] = {v.x, v.y, v.z, v.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float w0 = bf16_lo(w4[e]), w1 = bf16_hi(w4[e]);
+                const uint32_t f = pack_bf16x2(w0 * ga[2 * e] * 0.5f, w1 * ga[2 * e + 1] * 0.5f);
+                ssum += bf16_lo(f) + bf16_hi(f);
+                bsum = fmaf(w0, be[2 * e], fmaf(w1, be[2 * e + 1], bsum));
+                o[e] = f;
+            }
+            *ptr = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+    s = ssum;
+    bias = 0.5f * bsum;
+}
+
+
 }  // namespace trimul
