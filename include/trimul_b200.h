@@ -92,12 +92,15 @@ typedef struct trimul_desc {
     int32_t  B;              /* batch                                                               */
     int32_t  N;              /* tokens: z is N x N positions per batch                              */
     int32_t  c;              /* d_pair = channels of z and of the output                            */
-    int32_t  c_hidden;       /* width of a/b/tri.  Equal to c everywhere (reference.py:51-59 builds the
-                                four input projections c-wide regardless, so only c_hidden == c is
-                                self-consistent there), except that stage 3 alone also takes
-                                c_hidden == 2c: the bidirectional block's tri = [outgoing | incoming]
-                                planes, LayerNorm_out over 2c channels, w_out [c, 2c]
-                                (bidirectional.py:73-84,150-156)                                    */
+    int32_t  c_hidden;       /* h = d_hidden: the number of a/b/tri planes per batch element, the rows
+                                of the four input projections, the width of LayerNorm_out and the
+                                in_features of w_out (kernels/trimul_inproj/whole_op.py:203-209).  A
+                                multiple of 8, at most 256; the reference module only ever builds
+                                h == c (reference.py:51-59), the functional op and the bidirectional
+                                block (bidirectional.py:73-84, where this field is 2 * d_hidden) also
+                                other widths.  The tensor-core kernels cover c == 128 with h == 128
+                                (stage 1) and h == 128 or 256 (stage 3); every other width runs that
+                                stage on the CUDA-core kernels                                       */
     int32_t  dtype;          /* TRIMUL_DTYPE_*                                                      */
     int32_t  direction;      /* TRIMUL_OUTGOING / TRIMUL_INCOMING                                   */
     int32_t  mask_kind;      /* TRIMUL_MASK_*                                                       */
@@ -113,19 +116,19 @@ typedef struct trimul_desc {
 typedef struct trimul_weights {
     const float* ln_in_weight;    /* ln_pair.weight  [c] */
     const float* ln_in_bias;      /* ln_pair.bias    [c] */
-    const void*  w_left;          /* to_left.weight        [c,c] */
-    const void*  w_left_gate;     /* to_left_gate.weight   [c,c] */
-    const void*  w_right;         /* to_right.weight       [c,c] */
-    const void*  w_right_gate;    /* to_right_gate.weight  [c,c] */
-    const float* ln_out_weight;   /* ln_out.weight   [c] */
-    const float* ln_out_bias;     /* ln_out.bias     [c] */
+    const void*  w_left;          /* to_left.weight        [h,c]   (h = c_hidden) */
+    const void*  w_left_gate;     /* to_left_gate.weight   [h,c] */
+    const void*  w_right;         /* to_right.weight       [h,c] */
+    const void*  w_right_gate;    /* to_right_gate.weight  [h,c] */
+    const float* ln_out_weight;   /* ln_out.weight   [h] */
+    const float* ln_out_bias;     /* ln_out.bias     [h] */
     const void*  w_gate;          /* to_gate.weight        [c,c] */
-    const void*  w_out;           /* to_out.weight         [c,c] */
+    const void*  w_out;           /* to_out.weight         [c,h] */
 } trimul_weights;
 
 /*
  * Channel-major operand planes: the layout of a, b and tri between the stages.
- * Logical shape [planes = B*c][rows][cols]; element (p, r, q) lives at
+ * Logical shape [planes = B*c_hidden][rows][cols]; element (p, r, q) lives at
  *     base + (r / row_chunk) * chunk_stride + p * plane_stride + (r % row_chunk) * pitch + q       (row-chunked)
  *     base + (q / col_chunk) * chunk_stride + p * plane_stride + r * pitch + (q % col_chunk)       (col-chunked)
  * in elements.  row_chunk == rows and col_chunk == cols (chunk_stride ignored) is the plain
@@ -177,8 +180,8 @@ int trimul_b200_forward(const trimul_desc* desc, const void* z, const uint8_t* m
 /*
  * Stage 1: LayerNorm_in + mask + the two sigmoid-gated projections.  Reads the z slab
  * [B, rows, N, c]; writes a and b as channel-major planes.  Outgoing: plane element
- * (r, k) is position (row0+r, k), planes are [B*c][rows][N].  Incoming: the planes are
- * stored transposed, element (i, k) is position (row0+k, i), planes are [B*c][N][rows],
+ * (r, k) is position (row0+r, k), planes are [B*c_hidden][rows][N].  Incoming: the planes are
+ * stored transposed, element (i, k) is position (row0+k, i), planes are [B*c_hidden][N][rows],
  * so that the contraction is "rows times rows over a contiguous k" in both directions.
  * Replaces fused_ln_mask + tm1_cute_forward(out_layout="bdll_sm100")
  * (module.py:422-438; kernels/tm1/cute/sm100_gate_gemm_collective.py:586-647).
@@ -224,7 +227,7 @@ int trimul_b200_contract_scatter(int32_t dtype, uint32_t flags, int32_t planes,
 /*
  * Stage 3: LayerNorm_out over the channels of tri, the output projection, the output gate
  * computed from a fresh LayerNorm_in of the z slab (unmasked, reference.py:83), optional
- * residual; writes out [B, rows, N, c].  tri planes are [B*c][rows][N] for both directions.
+ * residual; writes out [B, rows, N, c].  tri planes are [B*c_hidden][rows][N] for both directions.
  * Replaces trimul_back_split_sm100 + the residual add (module.py:445-453;
  * kernels/trimul_inproj/cute/back_split_sm100.py:26-34).
  */
@@ -234,14 +237,15 @@ int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes*
 
 /*
  * The whole BIDIRECTIONAL block (bidirectional.py:93-156): one input LayerNorm, the four gated
- * projections of width 2c (rows [0,c) of each weight feed an outgoing contraction, rows [c,2c) an
- * incoming one), one LayerNorm over the 2c result channels, to_out [c,2c] gated by to_gate(x_n);
+ * projections of width 2h (rows [0,h) of each weight feed an outgoing contraction, rows [h,2h) an
+ * incoming one), one LayerNorm over the 2h result channels, to_out [c,2h] gated by to_gate(x_n);
  * `add_residual` != 0 adds z (what the reference module always returns).
- * `desc`: c_hidden = 2c, rows = N, row0 = 0; `direction` is ignored; mask kinds as in the
- * single-direction block.  `w`: w_left, w_left_gate, w_right, w_right_gate are [2c, c]; ln_out_*
- * have 2c entries; w_gate is [c, c]; w_out is [c, 2c].  The workspace holds three plane sets of
- * B*2c planes (trimul_b200_bidir_workspace_bytes); per batch element planes [0,c) belong to the
- * outgoing half and [c,2c) to the incoming half.  Replaces the sm_100 path
+ * `desc`: c_hidden = 2h (h = d_hidden a multiple of 8, 2h <= 256), rows = N, row0 = 0; `direction`
+ * is ignored; mask kinds as in the single-direction block.  `w`: w_left, w_left_gate, w_right,
+ * w_right_gate are [2h, c]; ln_out_* have 2h entries; w_gate is [c, c]; w_out is [c, 2h].  The
+ * workspace holds three plane sets of B*2h planes (trimul_b200_bidir_workspace_bytes); per batch
+ * element planes [0,h) belong to the outgoing half and [h,2h) to the incoming half.  bf16 with
+ * c = h = 128 runs every stage on the tensor cores.  Replaces the sm_100 path
  * BidirectionalTriangleMultiplication._forward_cute (bidirectional.py:118-132;
  * kernels/trimul_inproj/cute/bidirectional_sm100.py:33-71).
  */

@@ -14,11 +14,16 @@ the stage entry points:
   planes of the shared ``a`` / ``b`` plane sets — for the incoming half the kernel's strided TMA
   box stores the operands transposed, so
 * stage 2 is ONE contraction over all ``B * 2h`` planes, and
-* stage 3 is the wide form of the last stage (``c_hidden = 2c``): LayerNorm over ``2h`` channels
-  folded into a ``[d, 2h]`` projection, the tri tile consumed as two 128-channel halves.
+* stage 3 is the last stage with ``c_hidden = 2h``: LayerNorm over ``2h`` channels folded into a
+  ``[d, 2h]`` projection (for ``h = 128`` the tri tile is consumed as two 128-channel halves).
 
-bf16 with ``d = h = 128`` takes the tensor-core kernels in every stage; other widths and fp32 take
-the CUDA-core kernels (``2h <= 256``).
+bf16 with ``d = h = 128`` takes the tensor-core kernels in every stage.  ``d_hidden != d_pair``
+(``h`` a multiple of 8, ``2h <= 256``) is served too: stage 1 then runs on the CUDA-core kernel,
+the contraction stays on the tensor cores for bf16, and stage 3 does when ``d = 128`` and
+``2h`` is 128 or 256.  fp32 takes the CUDA-core kernels throughout.
+
+``bidirectional_triangle_multiplicative_update_b200`` is the same call under the argument names of
+the reference's functional op (``kernels/trimul_inproj/whole_op.py:243-262``).
 """
 
 from __future__ import annotations
@@ -32,7 +37,8 @@ from . import _lib
 from .functional import _dtype_code, _mask_bytes, _require_cuda, _status_words, _workspace
 from .module import PinnedLayerNormParams
 
-__all__ = ["bidir_trimul_forward", "BidirectionalTriangleMultiplicationB200"]
+__all__ = ["bidir_trimul_forward", "bidirectional_triangle_multiplicative_update_b200",
+           "BidirectionalTriangleMultiplicationB200"]
 
 
 @torch.no_grad()
@@ -58,10 +64,9 @@ def bidir_trimul_forward(
     h2 = int(w_left.shape[0])
     if h2 % 2 or any(tuple(t.shape) != (h2, d) for t in (w_left, w_left_gate, w_right, w_right_gate)):
         raise ValueError("the four input projection weights must all be [2h, d]")
-    h = h2 // 2
-    if h != d:
-        # the stage-1 kernels produce as many planes as z has channels
-        raise NotImplementedError(f"d_hidden ({h}) != d_pair ({d}) is not supported")
+    if h2 % 16 or d % 8 or h2 > 256 or d > 256:
+        raise NotImplementedError(
+            f"d_pair ({d}) and d_hidden ({h2 // 2}) must be multiples of 8 with d_pair, 2*d_hidden <= 256")
     if tuple(w_out.shape) != (d, h2) or tuple(w_gate.shape) != (d, d):
         raise ValueError(f"w_out must be [{d}, {h2}] and w_gate [{d}, {d}]")
     if mask is not None and tuple(mask.shape) != (B, N):
@@ -92,6 +97,26 @@ def bidir_trimul_forward(
     for t in keep:      # parameter copies made above must outlive the enqueued kernels
         t.record_stream(torch.cuda.current_stream(x.device))
     return out
+
+
+def bidirectional_triangle_multiplicative_update_b200(
+    x: torch.Tensor,
+    mask: torch.Tensor | None = None,
+    *,
+    norm_in_weight, norm_in_bias, to_left_weight, to_left_gate_weight, to_right_weight, to_right_gate_weight,
+    norm_out_weight, norm_out_bias, to_out_weight, to_gate_weight,
+    eps: float = 1e-5,
+) -> torch.Tensor:
+    """Drop-in for ``ops.bidirectional_triangle_multiplicative_update``
+    (``kernels/trimul_inproj/whole_op.py:243-262``): ``x (B,L,L,d_pair)``, ``mask (B,L)`` or None, the
+    four input projections ``(2*d_hidden, d_pair)``, ``norm_out_* (2*d_hidden,)``, ``to_out_weight
+    (d_pair, 2*d_hidden)``, ``to_gate_weight (d_pair, d_pair)``.  Returns the update WITHOUT the
+    residual, like the op it replaces (the module adds it)."""
+    return bidir_trimul_forward(
+        x, mask, ln_in_weight=norm_in_weight, ln_in_bias=norm_in_bias, w_left=to_left_weight,
+        w_left_gate=to_left_gate_weight, w_right=to_right_weight, w_right_gate=to_right_gate_weight,
+        ln_out_weight=norm_out_weight, ln_out_bias=norm_out_bias, w_gate=to_gate_weight, w_out=to_out_weight,
+        eps_in=eps, eps_out=eps, add_residual=False)
 
 
 def _bidir_weights_struct(d, h2, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_right_gate,

@@ -74,6 +74,7 @@ __device__ __forceinline__ void plain_layernorm_rows(float* xs, int npos, int c,
 
 struct PlainTm1Params {
     int B, rows, N, c, row0, incoming, mask_kind;
+    int h;      // planes per batch element = rows of the four [h, c] projection matrices
     const uint8_t* mask;
     const float *gamma, *beta;
     float eps;
@@ -108,7 +109,7 @@ __global__ void __launch_bounds__(kPlainThreads) plain_tm1_kernel(const T* __res
     plain_layernorm_rows<T>(xs, npos, c, p.gamma, p.beta, p.eps);
     __syncthreads();
     const T* W[4] = {(const T*)p.w_left, (const T*)p.w_left_gate, (const T*)p.w_right, (const T*)p.w_right_gate};
-    for (int o = threadIdx.x; o < c; o += blockDim.x) {
+    for (int o = threadIdx.x; o < p.h; o += blockDim.x) {
         float acc[4][kPlainPos];
 #pragma unroll
         for (int m = 0; m < 4; ++m)
@@ -125,7 +126,7 @@ __global__ void __launch_bounds__(kPlainThreads) plain_tm1_kernel(const T* __res
                 for (int m = 0; m < 4; ++m) acc[m][q] = fmaf(w[m], x, acc[m][q]);
             }
         }
-        const long long plane = (long long)b * c + o;
+        const long long plane = (long long)b * p.h + o;
         for (int q = 0; q < npos; ++q) {
             const float left = acc[0][q] * sigmoid_ref(acc[1][q]) * keep[q];
             const float right = acc[2][q] * sigmoid_ref(acc[3][q]) * keep[q];

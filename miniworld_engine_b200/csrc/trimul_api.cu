@@ -133,8 +133,7 @@ inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 // ---------------------------------------------------------------------------------------
 // validation
 // ---------------------------------------------------------------------------------------
-// `wide_ok`: the caller (stage 3) accepts c_hidden == 2c, the bidirectional block's layout.
-int check_desc(const trimul_desc* d, bool wide_ok = false) {
+int check_desc(const trimul_desc* d) {
     if (d == nullptr || d->struct_bytes != sizeof(trimul_desc)) return TRIMUL_E_INVALID;
     if (d->B <= 0 || d->N <= 0 || d->c <= 0 || d->rows <= 0 || d->row0 < 0) return TRIMUL_E_INVALID;
     if (d->row0 + d->rows > d->N) return TRIMUL_E_INVALID;
@@ -142,8 +141,9 @@ int check_desc(const trimul_desc* d, bool wide_ok = false) {
     if (d->direction != TRIMUL_OUTGOING && d->direction != TRIMUL_INCOMING) return TRIMUL_E_INVALID;
     if (d->mask_kind < TRIMUL_MASK_NONE || d->mask_kind > TRIMUL_MASK_PAIR) return TRIMUL_E_INVALID;
     if (!(d->eps_in > 0.f) || !(d->eps_out > 0.f)) return TRIMUL_E_INVALID;
-    if (d->c_hidden != d->c && !(wide_ok && d->c_hidden == 2 * d->c)) return TRIMUL_E_UNSUPPORTED;
-    if (d->c_hidden > kPlainMaxC || (d->c % 8) != 0) return TRIMUL_E_UNSUPPORTED;
+    if (d->c_hidden <= 0) return TRIMUL_E_INVALID;
+    if (d->c > kPlainMaxC || d->c_hidden > kPlainMaxC || (d->c % 8) != 0 || (d->c_hidden % 8) != 0)
+        return TRIMUL_E_UNSUPPORTED;
     if ((int64_t)d->B * d->c_hidden > 65535) return TRIMUL_E_UNSUPPORTED;
     if (d->N > 16384) return TRIMUL_E_UNSUPPORTED;
     return TRIMUL_OK;
@@ -189,6 +189,7 @@ PlaneView view_of(const trimul_planes& pl) {
 // chunk sizes as the tensor-core kernels use them: the full extent when not chunked
 inline int eff_chunk(int64_t chunk, int64_t extent) { return (int)(chunk < extent ? chunk : extent); }
 
+// bf16 with 128 channels of z; each stage adds its own condition on c_hidden
 bool tensor_core_path(const trimul_desc* d) {
     return d->dtype == TRIMUL_DTYPE_BF16 && d->c == 128 && (d->flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0;
 }
@@ -202,7 +203,7 @@ template <typename T>
 int run_plain_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
                   const trimul_planes* a, const trimul_planes* b, cudaStream_t st) {
     PlainTm1Params p;
-    p.B = d->B; p.rows = d->rows; p.N = d->N; p.c = d->c; p.row0 = d->row0;
+    p.B = d->B; p.rows = d->rows; p.N = d->N; p.c = d->c; p.row0 = d->row0; p.h = d->c_hidden;
     p.incoming = d->direction == TRIMUL_INCOMING;
     p.mask_kind = mask ? d->mask_kind : 0;
     p.mask = mask;
@@ -490,7 +491,7 @@ int trimul_b200_workspace_bytes(const trimul_desc* desc, size_t* bytes, trimul_p
     if (rc != TRIMUL_OK) return rc;
     if (bytes == nullptr) return TRIMUL_E_INVALID;
     const int64_t esz = desc->dtype == TRIMUL_DTYPE_BF16 ? 2 : 4;
-    const int64_t planes = (int64_t)desc->B * desc->c;
+    const int64_t planes = (int64_t)desc->B * desc->c_hidden;
     const bool inc = desc->direction == TRIMUL_INCOMING;
     // a, b: outgoing [planes][rows][N], incoming [planes][N][rows];  tri: [planes][rows][N]
     const int64_t ab_rows = inc ? desc->N : desc->rows, ab_cols = inc ? desc->rows : desc->N;
@@ -525,7 +526,8 @@ int trimul_b200_tm1(const trimul_desc* desc, const void* z, const uint8_t* mask,
     const bool chunks_ok = (a->col_chunk >= a->cols || a->col_chunk % 64 == 0) &&
                            (b->col_chunk >= b->cols || b->col_chunk % 64 == 0) &&
                            ((reinterpret_cast<uintptr_t>(a->base) | reinterpret_cast<uintptr_t>(b->base)) & 127u) == 0;
-    if (tensor_core_path(desc) && chunks_ok) return run_fast_tm1(desc, z, mask, w, a, b, st, status);
+    if (tensor_core_path(desc) && desc->c_hidden == 128 && chunks_ok)
+        return run_fast_tm1(desc, z, mask, w, a, b, st, status);
     return run_plain_tm1<__nv_bfloat16>(desc, z, mask, w, a, b, st);
 }
 
@@ -583,7 +585,7 @@ int trimul_b200_tm1_scatter(const trimul_desc* desc, const void* z, const uint8_
     }
     if (!same_geometry(a_dest, n_dest) || !same_geometry(b_dest, n_dest)) return TRIMUL_E_INVALID;
     // tensor-core kernel only: a destination's share must be whole 8-plane groups of a 128-plane tile
-    if (!tensor_core_path(desc)) return TRIMUL_E_UNSUPPORTED;
+    if (!tensor_core_path(desc) || desc->c_hidden != 128) return TRIMUL_E_UNSUPPORTED;
     if (per % 8 != 0 || !(128 % per == 0 || per % 128 == 0)) return TRIMUL_E_UNSUPPORTED;
     if ((a_dest->col_chunk < a_dest->cols && a_dest->col_chunk % 64) ||
         (b_dest->col_chunk < b_dest->cols && b_dest->col_chunk % 64))
@@ -620,7 +622,7 @@ int trimul_b200_contract_scatter(int32_t dtype, uint32_t flags, int32_t planes, 
 
 int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes* tri, const trimul_weights* w,
                     void* out, const void* residual, void* stream, int32_t* status) {
-    int rc = check_desc(desc, true);
+    int rc = check_desc(desc);
     if (rc != TRIMUL_OK) return rc;
     if ((rc = check_weights(w)) != TRIMUL_OK) return rc;
     if (z == nullptr || out == nullptr || out == z || !aligned16(z) || !aligned16(out)) return TRIMUL_E_INVALID;
@@ -630,7 +632,7 @@ int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes*
     if (desc->dtype == TRIMUL_DTYPE_FP32) return run_plain_tm2<float>(desc, z, tri, w, out, residual, st);
     const bool plain_layout = tri->row_chunk >= tri->rows && tri->col_chunk >= tri->cols &&
                               (reinterpret_cast<uintptr_t>(tri->base) & 127u) == 0;
-    if (tensor_core_path(desc) && plain_layout) {
+    if (tensor_core_path(desc) && plain_layout && (desc->c_hidden == 128 || desc->c_hidden == 256)) {
         // the wide (2c) form exists only in the folded kernel, which takes no residual but z itself
         const bool wide = desc->c_hidden != desc->c;
         const bool folded_ok = (desc->flags & TRIMUL_FLAG_INPLACE_NORM_STAGE3) == 0 && (residual == nullptr || residual == z);
@@ -660,16 +662,16 @@ int trimul_b200_forward(const trimul_desc* desc, const void* z, const uint8_t* m
     if (residual != nullptr && (!aligned16(residual) || residual == out)) return TRIMUL_E_INVALID;
     if (desc->mask_kind != TRIMUL_MASK_NONE && mask == nullptr) return TRIMUL_E_INVALID;
     if ((rc = trimul_b200_tm1(desc, z, mask, w, &a, &b, stream, status)) != TRIMUL_OK) return rc;
-    if ((rc = trimul_b200_contract(desc->dtype, desc->flags, desc->B * desc->c, &a, &b, &t, stream, status)) !=
+    if ((rc = trimul_b200_contract(desc->dtype, desc->flags, desc->B * desc->c_hidden, &a, &b, &t, stream, status)) !=
         TRIMUL_OK)
         return rc;
     return trimul_b200_tm2(desc, z, &t, w, out, residual, stream, status);
 }
 
 int trimul_b200_bidir_workspace_bytes(const trimul_desc* desc, size_t* bytes) {
-    int rc = check_desc(desc, true);
+    int rc = check_desc(desc);
     if (rc != TRIMUL_OK) return rc;
-    if (bytes == nullptr || desc->c_hidden != 2 * desc->c) return TRIMUL_E_INVALID;
+    if (bytes == nullptr || desc->c_hidden % 16 != 0) return TRIMUL_E_INVALID;   // 2h, h a multiple of 8
     if (desc->rows != desc->N || desc->row0 != 0) return TRIMUL_E_INVALID;
     const int64_t esz = desc->dtype == TRIMUL_DTYPE_BF16 ? 2 : 4;
     const int64_t set_bytes = round_up((int64_t)desc->B * desc->c_hidden * desc->N * round_up(desc->N, 8) * esz, 1024);
@@ -689,13 +691,13 @@ int trimul_b200_forward_bidir(const trimul_desc* desc, const void* z, const uint
     if (z == nullptr || out == nullptr || out == z || !aligned16(z) || !aligned16(out)) return TRIMUL_E_INVALID;
     if (desc->mask_kind != TRIMUL_MASK_NONE && mask == nullptr) return TRIMUL_E_INVALID;
     const int64_t esz = desc->dtype == TRIMUL_DTYPE_BF16 ? 2 : 4;
-    const int64_t N = desc->N, c = desc->c, pitch = round_up(N, 8), plane = N * pitch;
+    const int64_t N = desc->N, c = desc->c, h = desc->c_hidden / 2, pitch = round_up(N, 8), plane = N * pitch;
     const int64_t set_bytes = (int64_t)(need / 3);
     uint8_t* base = static_cast<uint8_t*>(workspace);
-    // stage 1: per batch element and direction, with that direction's rows of the [2c, c] weights
+    // stage 1: per batch element and direction, with that direction's rows of the [2h, c] weights
     trimul_desc d1 = *desc;
     d1.B = 1;
-    d1.c_hidden = desc->c;
+    d1.c_hidden = (int32_t)h;
     for (int bi = 0; bi < desc->B; ++bi) {
         const uint8_t* zb = static_cast<const uint8_t*>(z) + (int64_t)bi * N * N * c * esz;
         const uint8_t* mb = mask == nullptr ? nullptr
@@ -703,19 +705,19 @@ int trimul_b200_forward_bidir(const trimul_desc* desc, const void* z, const uint
         for (int dir = 0; dir < 2; ++dir) {
             d1.direction = dir == 0 ? TRIMUL_OUTGOING : TRIMUL_INCOMING;
             trimul_weights w1 = *w;
-            const int64_t wofs = (int64_t)dir * c * c * esz;
+            const int64_t wofs = (int64_t)dir * h * c * esz;
             w1.w_left = static_cast<const uint8_t*>(w->w_left) + wofs;
             w1.w_left_gate = static_cast<const uint8_t*>(w->w_left_gate) + wofs;
             w1.w_right = static_cast<const uint8_t*>(w->w_right) + wofs;
             w1.w_right_gate = static_cast<const uint8_t*>(w->w_right_gate) + wofs;
-            const int64_t first = ((int64_t)bi * 2 * c + (int64_t)dir * c) * plane * esz;
+            const int64_t first = ((int64_t)bi * 2 * h + (int64_t)dir * h) * plane * esz;
             trimul_planes pa = {base + first, N, N, pitch, plane, 0, N, N};
             trimul_planes pb = pa;
             pb.base = base + set_bytes + first;
             if ((rc = trimul_b200_tm1(&d1, zb, mb, &w1, &pa, &pb, stream, status)) != TRIMUL_OK) return rc;
         }
     }
-    // stage 2: one contraction over all B * 2c planes; stage 3: the wide last stage
+    // stage 2: one contraction over all B * 2h planes; stage 3: LayerNorm_out over 2h channels
     trimul_planes a = {base, N, N, pitch, plane, 0, N, N};
     trimul_planes b = a, t = a;
     b.base = base + set_bytes;

@@ -88,15 +88,18 @@ def workspace_bytes(B: int, N: int, c: int, dtype: torch.dtype, outgoing: bool =
 
 
 def _weights_struct(c, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_right_gate,
-                    ln_out_w, ln_out_b, w_gate, w_out, device, c_hidden=None):
+                    ln_out_w, ln_out_b, w_gate, w_out, device, c_hidden=None, c_proj=None):
     """Validate and pin the parameter tensors; returns (struct, keep-alive list).  ``c_hidden``
-    (default ``c``) is the width of the output LayerNorm and the input width of ``to_out``."""
+    (default ``c``) is the width of the output LayerNorm and the input width of ``to_out``;
+    ``c_proj`` (default ``c``) the number of rows of the four input projections, i.e. the number
+    of operand planes stage 1 produces per batch element."""
     keep = []
     h = c if c_hidden is None else c_hidden
+    hp = c if c_proj is None else c_proj
 
-    def lin(t, name, cols=c):
-        if tuple(t.shape) != (c, cols):
-            raise ValueError(f"{name} must have shape ({c}, {cols}), got {tuple(t.shape)}")
+    def lin(t, name, rows=c, cols=c):
+        if tuple(t.shape) != (rows, cols):
+            raise ValueError(f"{name} must have shape ({rows}, {cols}), got {tuple(t.shape)}")
         _require_cuda(t, name)
         t = t.detach()
         if t.dtype != dtype or not t.is_contiguous():
@@ -116,10 +119,10 @@ def _weights_struct(c, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_
 
     w = _lib.Weights(
         vec(ln_in_w, "norm_in_weight"), vec(ln_in_b, "norm_in_bias"),
-        lin(w_left, "to_left.weight"), lin(w_left_gate, "to_left_gate.weight"),
-        lin(w_right, "to_right.weight"), lin(w_right_gate, "to_right_gate.weight"),
+        lin(w_left, "to_left.weight", hp), lin(w_left_gate, "to_left_gate.weight", hp),
+        lin(w_right, "to_right.weight", hp), lin(w_right_gate, "to_right_gate.weight", hp),
         vec(ln_out_w, "norm_out_weight", h), vec(ln_out_b, "norm_out_bias", h),
-        lin(w_gate, "to_gate.weight"), lin(w_out, "to_out.weight", h))
+        lin(w_gate, "to_gate.weight"), lin(w_out, "to_out.weight", c, h))
     return w, keep
 
 
@@ -140,12 +143,18 @@ def trimul_forward(
     ``[B,N,N]`` pair mask or None; ``residual`` (same shape/dtype as ``x``) is added to the
     result when given.  Passing ``x`` itself as the residual (the block's ``pair + update`` form)
     costs nothing extra: the last stage adds the tile it already holds.  ``plain_kernels`` and
-    ``inplace_norm`` select cross-checking variants of the kernels (see the flags in the C header)."""
+    ``inplace_norm`` select cross-checking variants of the kernels (see the flags in the C header).
+
+    The hidden width ``h`` is read off the weights: the four input projections are ``[h, c]``,
+    ``ln_out_*`` have ``h`` entries and ``w_out`` is ``[c, h]`` (``whole_op.py:203-209``).  bf16 with
+    ``c = h = 128`` runs on the tensor-core kernels; any other multiple of 8 up to 256 runs stage 1
+    (and, unless ``c = 128`` and ``h`` is 128 or 256, stage 3) on the CUDA-core kernels."""
     if x.dim() != 4 or x.shape[1] != x.shape[2]:
         raise ValueError(f"x must be [B, N, N, c], got {tuple(x.shape)}")
     _require_cuda(x, "x")
     B, N, _, c = x.shape
     code = _dtype_code(x)
+    h = int(w_out.shape[-1])
     x = x.detach()
     if not x.is_contiguous():
         x = x.contiguous()
@@ -166,12 +175,12 @@ def trimul_forward(
         residual = residual.detach().contiguous()
 
     lib = _lib.load()
-    desc = _lib.make_desc(B, N, c, dtype=code, direction=_lib.OUTGOING if outgoing else _lib.INCOMING,
+    desc = _lib.make_desc(B, N, c, c_hidden=h, dtype=code, direction=_lib.OUTGOING if outgoing else _lib.INCOMING,
                           mask_kind=mask_kind, eps_in=eps_in, eps_out=eps_out,
                           flags=(_lib.FLAG_PLAIN_KERNELS if plain_kernels else 0) |
                           (_lib.FLAG_INPLACE_NORM_STAGE3 if inplace_norm else 0))
     w, keep = _weights_struct(c, x.dtype, ln_in_weight, ln_in_bias, w_left, w_left_gate, w_right, w_right_gate,
-                              ln_out_weight, ln_out_bias, w_gate, w_out, x.device)
+                              ln_out_weight, ln_out_bias, w_gate, w_out, x.device, c_hidden=h, c_proj=h)
     nbytes = C.c_size_t()
     _lib.check(lib.trimul_b200_workspace_bytes(C.byref(desc), C.byref(nbytes), None, None, None),
                "trimul_b200_workspace_bytes")
@@ -210,15 +219,19 @@ def triangle_multiplicative_update_b200(
     ``x (B,I,J,D)``; ``direction`` "outgoing" | "incoming" (anything else raises
     ``ValueError`` like ``reference.py:118-119``); ``mask`` a ``(B,I,J)`` pair mask, a
     ``(B,L)`` token mask (accepted by the shipped op, ``whole_op.py:56-58``) or None;
-    ``p_in_weight (2D,D) = [to_left; to_right]``, ``g_in_weight (2D,D) = [to_left_gate;
-    to_right_gate]``, ``p_out_weight = to_out.weight``, ``g_out_weight = to_gate.weight``.
-    No residual is added.
+    ``p_in_weight (2H,D) = [to_left; to_right]``, ``g_in_weight (2H,D) = [to_left_gate;
+    to_right_gate]``, ``norm_out_* (H,)``, ``p_out_weight (D,H) = to_out.weight``,
+    ``g_out_weight (D,D) = to_gate.weight``; ``H = d_hidden`` is read off ``p_in_weight`` and an
+    odd leading dimension raises ``ValueError`` (``whole_op.py:203-209``).  No residual is added.
     """
     if direction not in ("outgoing", "incoming"):
         raise ValueError(f"direction must be outgoing|incoming, got {direction!r}")
-    D = x.shape[-1]
-    if tuple(p_in_weight.shape) != (2 * D, D) or tuple(g_in_weight.shape) != (2 * D, D):
-        raise ValueError(f"p_in_weight and g_in_weight must be ({2 * D}, {D})")
+    two_h, d_in = int(p_in_weight.shape[0]), x.shape[-1]
+    if two_h % 2 != 0:
+        raise ValueError(f"p_in_weight leading dim must be 2*d_hidden (even), got {two_h}")
+    D = two_h // 2
+    if tuple(p_in_weight.shape) != (two_h, d_in) or tuple(g_in_weight.shape) != (two_h, d_in):
+        raise ValueError(f"p_in_weight and g_in_weight must be ({two_h}, {d_in})")
     return trimul_forward(
         x, mask, outgoing=(direction == "outgoing"),
         ln_in_weight=norm_in_weight, ln_in_bias=norm_in_bias,

@@ -129,8 +129,10 @@ def tm1(z_slab: torch.Tensor, mask, weights: dict, a: PlaneSpec, b: PlaneSpec, *
     _require_cuda(z_slab, "z")
     B, rows, N, c = z_slab.shape
     kind, mask_u8 = _mask_arg(mask, B, N)
-    d = _desc(z_slab, N, outgoing, kind, eps, eps, plain_kernels, row0, pair_stage1, folded_stage1)
-    w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, **weights)
+    hp = int(weights["w_left"].shape[0])      # operand planes per batch element (d_hidden)
+    d = _desc(z_slab, N, outgoing, kind, eps, eps, plain_kernels, row0, pair_stage1, folded_stage1, c_hidden=hp)
+    w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, c_proj=hp,
+                              c_hidden=int(weights["w_out"].shape[1]), **weights)
     st = _status_words(z_slab.device)
     with torch.cuda.device(z_slab.device):
         rc = _lib.load().trimul_b200_tm1(
@@ -213,7 +215,8 @@ def tm2(z_slab: torch.Tensor, tri: PlaneSpec, weights: dict, *, residual=None, r
     h = int(weights["w_out"].shape[1])
     d = _desc(z_slab, N, True, _lib.MASK_NONE, eps_in, eps_out, plain_kernels, row0, False, False, inplace_norm,
               c_hidden=h)
-    w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, c_hidden=h, **weights)
+    w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, c_hidden=h,
+                              c_proj=int(weights["w_left"].shape[0]), **weights)
     out = torch.empty_like(z_slab)
     st = _status_words(z_slab.device)
     with torch.cuda.device(z_slab.device):

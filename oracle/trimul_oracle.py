@@ -120,7 +120,7 @@ class TrimulWeights:
         }
 
 
-def make_weights(c: int, seed: int = 0, *, affine: str = "unit") -> TrimulWeights:
+def make_weights(c: int, seed: int = 0, *, affine: str = "unit", h: int | None = None) -> TrimulWeights:
     """Seeded synthetic weights.
 
     The six Linear weights are drawn in the fixed order ``to_left, to_left_gate,
@@ -131,16 +131,24 @@ def make_weights(c: int, seed: int = 0, *, affine: str = "unit") -> TrimulWeight
     ``affine="unit"`` gives gamma=1, beta=0; ``affine="random"`` draws non-trivial
     LayerNorm parameters (after the Linear weights, so the Linear draws do not
     depend on this switch) to expose mask/gate ordering mistakes.
+
+    ``h`` (default ``c``) is the hidden width of the functional op
+    (``kernels/trimul_inproj/whole_op.py:203-209``): the four input projections become
+    ``[h, c]``, ``ln_out`` gets ``h`` channels and ``to_out`` is ``[c, h]``; with ``h == c`` the
+    draws are exactly those of the module form.
     """
+    h = c if h is None else h
     g = torch.Generator().manual_seed(seed)
-    lin = [torch.randn(c, c, generator=g) * c ** -0.5 for _ in range(6)]
+    lin = [torch.randn(h, c, generator=g) * c ** -0.5 for _ in range(4)]
+    lin.append(torch.randn(c, c, generator=g) * c ** -0.5)
+    lin.append(torch.randn(c, h, generator=g) * h ** -0.5)
     if affine == "unit":
-        gi, bi, go, bo = torch.ones(c), torch.zeros(c), torch.ones(c), torch.zeros(c)
+        gi, bi, go, bo = torch.ones(c), torch.zeros(c), torch.ones(h), torch.zeros(h)
     elif affine == "random":
         gi = 1.0 + 0.3 * torch.randn(c, generator=g)
         bi = 0.2 * torch.randn(c, generator=g)
-        go = 1.0 + 0.3 * torch.randn(c, generator=g)
-        bo = 0.2 * torch.randn(c, generator=g)
+        go = 1.0 + 0.3 * torch.randn(h, generator=g)
+        bo = 0.2 * torch.randn(h, generator=g)
     else:
         raise ValueError(f"affine must be unit|random, got {affine!r}")
     return TrimulWeights(gi, bi, lin[0], lin[1], lin[2], lin[3], go, bo, lin[4], lin[5])
@@ -244,10 +252,13 @@ def trimul_forward_functional(
     eps: float = 1e-5,
 ) -> torch.Tensor:
     """Functional form with ``p_in = [to_left; to_right]``, ``g_in = [to_left_gate;
-    to_right_gate]`` and a ``[B,I,J]`` pair mask, ``reference.py:86-122``."""
+    to_right_gate]`` and a ``[B,I,J]`` pair mask, ``reference.py:86-122``.  The split point is
+    the hidden width ``p_in_weight.shape[0] // 2`` as in the shipped op
+    (``kernels/trimul_inproj/whole_op.py:203-209``); ``reference.py:99`` writes it as ``D`` and so
+    only covers ``d_hidden == d_pair``."""
     if direction not in ("outgoing", "incoming"):
         raise ValueError(f"direction must be outgoing|incoming, got {direction!r}")
-    D = x.shape[-1]
+    D = p_in_weight.shape[0] // 2
     w = TrimulWeights(
         norm_in_weight, norm_in_bias,
         p_in_weight[:D], g_in_weight[:D], p_in_weight[D:], g_in_weight[D:],

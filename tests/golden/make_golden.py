@@ -43,23 +43,28 @@ CASES = [
 ]
 
 
-# bidirectional module (bidirectional.py:93-156): name, dtype, B, N, d, mask kind, affine, weight seed, input seed
+# bidirectional module (bidirectional.py:93-156): name, dtype, B, N, d, mask kind, affine, weight seed,
+# input seed[, d_hidden (default d)]
 BIDIR_CASES = [
     ("bidir_fp32_n12_d32_tail3_aff", "fp32", 2, 12, 32, "tail3", "random", 40, 41),
     ("bidir_bf16_n16_d64_rand5_aff", "bf16", 1, 16, 64, "rand5", "random", 42, 43),
     ("bidir_bf16_n20_d128_nomask", "bf16", 1, 20, 128, "none", "unit", 44, 45),
+    ("bidir_fp32_n11_d32_h16_tail3_aff", "fp32", 2, 11, 32, "tail3", "random", 46, 47, 16),
+    ("bidir_bf16_n14_d128_h64_rand5_aff", "bf16", 1, 14, 128, "rand5", "random", 48, 49, 64),
+    ("bidir_bf16_n12_d64_h128_tail2_aff", "bf16", 1, 12, 64, "tail2", "random", 50, 51, 128),
 ]
 
 
 def run_bidir_reference(case):
     from miniworld_engine.modules.triangle_multiplication.bidirectional import BidirectionalTriangleMultiplication
-    name, dt, B, N, d, mkind, affine, wseed, zseed = case
+    name, dt, B, N, d, mkind, affine, wseed, zseed = case[:9]
+    h = case[9] if len(case) > 9 else d
     dtype = torch.float32 if dt == "fp32" else torch.bfloat16
-    w = O.make_bidir_weights(d, d, wseed, affine=affine)
+    w = O.make_bidir_weights(d, h, wseed, affine=affine)
     z = O.make_input(B, N, d, zseed)
     mask = None if mkind == "none" else O.make_token_mask(B, N, mkind, seed=zseed + 100)
     with torch.no_grad():
-        m = BidirectionalTriangleMultiplication(d)
+        m = BidirectionalTriangleMultiplication(d, h)
         m.load_state_dict(w.state_dict())
         m = m.to(dtype).eval()
         y = m(z.to(dtype), mask)

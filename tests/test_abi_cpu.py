@@ -64,8 +64,22 @@ def test_validation_without_gpu(lib):
     assert lib.trimul_b200_workspace_bytes(C.byref(bad), C.byref(n), None, None, None) == _lib.E_INVALID
     bad = _lib.make_desc(1, 8, 128, dtype=7, direction=0)
     assert lib.trimul_b200_workspace_bytes(C.byref(bad), C.byref(n), None, None, None) == _lib.E_INVALID
-    bad = _lib.make_desc(1, 8, 128, dtype=0, direction=0, c_hidden=64)
+    bad = _lib.make_desc(1, 8, 128, dtype=0, direction=0, c_hidden=60)
     assert lib.trimul_b200_workspace_bytes(C.byref(bad), C.byref(n), None, None, None) == _lib.E_UNSUPPORTED
+    bad = _lib.make_desc(1, 8, 128, dtype=0, direction=0, c_hidden=264)
+    assert lib.trimul_b200_workspace_bytes(C.byref(bad), C.byref(n), None, None, None) == _lib.E_UNSUPPORTED
+    # d_hidden != d_pair: the scratch holds B * c_hidden planes per operand
+    half = _lib.make_desc(1, 8, 128, dtype=0, direction=0, c_hidden=64)
+    full = _lib.make_desc(1, 8, 128, dtype=0, direction=0)
+    n_half, n_full = C.c_size_t(), C.c_size_t()
+    assert lib.trimul_b200_workspace_bytes(C.byref(half), C.byref(n_half), None, None, None) == _lib.OK
+    assert lib.trimul_b200_workspace_bytes(C.byref(full), C.byref(n_full), None, None, None) == _lib.OK
+    assert 0 < n_half.value < n_full.value
+    # the bidirectional block takes c_hidden = 2h, h a multiple of 8
+    assert lib.trimul_b200_bidir_workspace_bytes(C.byref(_lib.make_desc(1, 8, 128, dtype=0, direction=0, c_hidden=128)),
+                                                 C.byref(n)) == _lib.OK
+    assert lib.trimul_b200_bidir_workspace_bytes(C.byref(_lib.make_desc(1, 8, 128, dtype=0, direction=0, c_hidden=72)),
+                                                 C.byref(n)) == _lib.E_INVALID
     bad = _lib.make_desc(1, 8, 100, dtype=0, direction=0)
     assert lib.trimul_b200_workspace_bytes(C.byref(bad), C.byref(n), None, None, None) == _lib.E_UNSUPPORTED
     ok = _lib.make_desc(1, 8, 128, dtype=0, direction=0)

@@ -349,6 +349,73 @@ def test_bidirectional_block_fp32(dev):
     assert err <= TOL_FP32, f"rel-RMS {err:.3e}"
 
 
+@pytest.mark.parametrize("dtype,d,h,B,N,mask_kind", [
+    (torch.float32, 32, 16, 2, 21, "tail3"),
+    (torch.float32, 64, 128, 1, 18, None),
+    (torch.bfloat16, 128, 64, 1, 150, "rand5"),     # CUDA-core stage 1, tensor-core contraction and stage 3
+    (torch.bfloat16, 64, 32, 2, 37, "tail5"),
+    (torch.bfloat16, 128, 96, 1, 40, "tail4"),      # 2h = 192: CUDA-core stage 3 as well
+], ids=["fp32_d32_h16", "fp32_d64_h128", "bf16_d128_h64", "bf16_d64_h32", "bf16_d128_h96"])
+def test_bidirectional_block_with_d_hidden_unequal_d_pair(dev, dtype, d, h, B, N, mask_kind):
+    """``BidirectionalTriangleMultiplication(d_pair, d_hidden)`` with ``d_hidden != d_pair``
+    (bidirectional.py:73-84): projections [2h, d], LayerNorm_out over 2h, to_out [d, 2h]."""
+    w = O.make_bidir_weights(d, h, 61, affine="random")
+    z = O.make_input(B, N, d, 62)
+    m = None if mask_kind is None else O.make_token_mask(B, N, mask_kind)
+    y = run_bidir(z, m, w, dtype, dev).float()
+    ref = O.bidir_forward(z.to(dtype), m, w.to(dtype)).float()
+    zb = z.to(dtype).float()
+    if dtype == torch.float32:
+        assert O.rel_rms(y, ref) <= TOL_FP32
+        assert O.rel_rms(y - zb, ref - zb) <= 2e-5
+    else:
+        assert O.rel_rms(y, ref) <= TOL_BF16
+        assert O.rel_rms(y - zb, ref - zb) <= 2e-2      # the update alone, without the dominating residual
+
+
+@pytest.mark.parametrize("direction", ["outgoing", "incoming"])
+@pytest.mark.parametrize("dtype,d,h,B,N", [
+    (torch.float32, 32, 16, 2, 19),
+    (torch.float32, 32, 64, 1, 17),
+    (torch.bfloat16, 128, 64, 1, 130),
+    (torch.bfloat16, 128, 256, 1, 72),      # tensor-core contraction and (2 x 128-channel) stage 3
+    (torch.bfloat16, 64, 32, 2, 33),
+], ids=["fp32_d32_h16", "fp32_d32_h64", "bf16_d128_h64", "bf16_d128_h256", "bf16_d64_h32"])
+def test_functional_op_with_d_hidden_unequal_d_pair(dev, dtype, d, h, B, N, direction):
+    """The functional op reads d_hidden off the packed projections, p_in / g_in [2h, d], norm_out (h,),
+    p_out [d, h] (whole_op.py:170-209); pair mask [B, L, L]."""
+    from miniworld_engine_b200 import read_status, triangle_multiplicative_update_b200 as f
+    w = O.make_weights(d, 71, affine="random", h=h).to(dtype)
+    z = O.make_input(B, N, d, 72).to(dtype)
+    g = torch.Generator().manual_seed(73)
+    pm = torch.rand(B, N, N, generator=g) > 0.15
+    args = (w.ln_pair_weight, w.ln_pair_bias, torch.cat([w.to_left, w.to_right]),
+            torch.cat([w.to_left_gate, w.to_right_gate]), w.ln_out_weight, w.ln_out_bias, w.to_out, w.to_gate)
+    ref = O.trimul_forward_functional(z, direction, pm, *args).float()
+    y = f(z.to(dev), direction, pm.to(dev), *(a.to(dev) for a in args)).cpu().float()
+    assert read_status(dev)[0] == 0
+    assert tuple(y.shape) == (B, N, N, d)
+    err = O.rel_rms(y, ref)
+    assert err <= (TOL_FP32 if dtype == torch.float32 else TOL_BF16), f"rel-RMS {err:.3e}"
+    with pytest.raises(ValueError):      # odd leading dimension of the packed projections
+        f(z.to(dev), direction, None, args[0].to(dev), args[1].to(dev), args[2][:-1].to(dev), args[3][:-1].to(dev),
+          *(a.to(dev) for a in args[4:]))
+
+
+def test_bidirectional_functional_op_has_the_reference_argument_names(dev):
+    from miniworld_engine_b200 import bidirectional_triangle_multiplicative_update_b200 as f
+    w = O.make_bidir_weights(128, 128, 81, affine="random").to(torch.bfloat16)
+    z = O.make_input(1, 96, 128, 82).bfloat16()
+    m = O.make_token_mask(1, 96, "tail9")
+    t = lambda x: x.to(dev)
+    y = f(t(z), t(m), norm_in_weight=t(w.ln_pair_weight), norm_in_bias=t(w.ln_pair_bias), to_left_weight=t(w.to_left),
+          to_left_gate_weight=t(w.to_left_gate), to_right_weight=t(w.to_right),
+          to_right_gate_weight=t(w.to_right_gate), norm_out_weight=t(w.ln_out_weight),
+          norm_out_bias=t(w.ln_out_bias), to_out_weight=t(w.to_out), to_gate_weight=t(w.to_gate)).cpu().float()
+    ref = O.bidir_forward(z, m, w, add_residual=False).float()
+    assert O.rel_rms(y, ref) <= TOL_BF16
+
+
 def test_bidirectional_module_mirrors_the_reference_interface(dev):
     from miniworld_engine_b200 import BidirectionalTriangleMultiplicationB200
     w = O.make_bidir_weights(128, 128, 11)

@@ -48,8 +48,9 @@ def load_case(path):
 def test_fixture_set_is_complete():
     names = {os.path.basename(f)[:-4] for f in FILES}
     assert "cfg1_out_fp32_n32_c128" in names
-    assert len(names) >= 12
-    assert sum(n.startswith("bidir") for n in names) >= 3
+    assert len(names) >= 15
+    assert sum(n.startswith("bidir") for n in names) >= 6
+    assert sum("_h" in n for n in names) >= 3      # d_hidden != d_pair
 
 
 @pytest.mark.parametrize("path", FILES, ids=[os.path.basename(f)[:-4] for f in FILES])
