@@ -112,3 +112,21 @@ def test_module_mirrors_reference_parameters():
     assert mod.to_out.weight.dtype == torch.bfloat16 and torch.equal(mod.to_out.weight.data, wb.to_out)
     with pytest.raises(ValueError):
         TriangleMultiplicationB200(64, d_hidden=32)
+
+
+def test_functional_op_reads_d_hidden_off_the_packed_projections():
+    """Argument checks that need no device: an odd leading dimension of p_in_weight and a width
+    mismatch raise ValueError (whole_op.py:203-207); a consistent d_hidden != d_pair passes them
+    and then fails loudly on the CPU tensor."""
+    import torch
+    from miniworld_engine_b200 import triangle_multiplicative_update_b200 as f
+    d, h = 32, 16
+    x = torch.zeros(1, 4, 4, d)
+    v_d, v_h = torch.ones(d), torch.ones(h)
+    p_in, p_out, g_out = torch.zeros(2 * h, d), torch.zeros(d, h), torch.zeros(d, d)
+    with pytest.raises(ValueError, match="even"):
+        f(x, "outgoing", None, v_d, v_d, p_in[:-1], p_in[:-1], v_h, v_h, p_out, g_out)
+    with pytest.raises(ValueError):
+        f(x, "outgoing", None, v_d, v_d, p_in, torch.zeros(2 * h, d + 8), v_h, v_h, p_out, g_out)
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        f(x, "outgoing", None, v_d, v_d, p_in, p_in, v_h, v_h, p_out, g_out)
