@@ -34,7 +34,7 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .functional import _dtype_code, _mask_bytes, _require_cuda, _status_words, _workspace
+from .functional import _dtype_code, _mask_bytes, _pinned_weights, _require_cuda, _status_words, _workspace
 from .module import PinnedLayerNormParams
 
 __all__ = ["bidir_trimul_forward", "bidirectional_triangle_multiplicative_update_b200",
@@ -121,36 +121,13 @@ def bidirectional_triangle_multiplicative_update_b200(
 
 def _bidir_weights_struct(d, h2, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_right_gate,
                           ln_out_w, ln_out_b, w_gate, w_out):
-    """Validate and pin the bidirectional block's parameters; returns (struct, keep-alive list)."""
-    keep = []
-
-    def lin(t, name, shape):
-        if tuple(t.shape) != shape:
-            raise ValueError(f"{name} must have shape {shape}, got {tuple(t.shape)}")
-        _require_cuda(t, name)
-        t = t.detach()
-        if t.dtype != dtype or not t.is_contiguous():
-            t = t.to(dtype).contiguous()
-        keep.append(t)
-        return t.data_ptr()
-
-    def vec(t, name, n):
-        if tuple(t.shape) != (n,):
-            raise ValueError(f"{name} must have shape ({n},), got {tuple(t.shape)}")
-        _require_cuda(t, name)
-        t = t.detach()
-        if t.dtype != torch.float32 or not t.is_contiguous():
-            t = t.float().contiguous()
-        keep.append(t)
-        return t.data_ptr()
-
-    w = _lib.Weights(
-        vec(ln_in_w, "ln_pair.weight", d), vec(ln_in_b, "ln_pair.bias", d),
-        lin(w_left, "to_left.weight", (h2, d)), lin(w_left_gate, "to_left_gate.weight", (h2, d)),
-        lin(w_right, "to_right.weight", (h2, d)), lin(w_right_gate, "to_right_gate.weight", (h2, d)),
-        vec(ln_out_w, "ln_out.weight", h2), vec(ln_out_b, "ln_out.bias", h2),
-        lin(w_gate, "to_gate.weight", (d, d)), lin(w_out, "to_out.weight", (d, h2)))
-    return w, keep
+    """Validate and pin the bidirectional block's parameters; returns (struct, copies to keep alive)."""
+    return _pinned_weights(dtype, (d, h2, h2), (
+        (ln_in_w, "ln_pair.weight", (d,)), (ln_in_b, "ln_pair.bias", (d,)),
+        (w_left, "to_left.weight", (h2, d)), (w_left_gate, "to_left_gate.weight", (h2, d)),
+        (w_right, "to_right.weight", (h2, d)), (w_right_gate, "to_right_gate.weight", (h2, d)),
+        (ln_out_w, "ln_out.weight", (h2,)), (ln_out_b, "ln_out.bias", (h2,)),
+        (w_gate, "to_gate.weight", (d, d)), (w_out, "to_out.weight", (d, h2))))
 
 
 class BidirectionalTriangleMultiplicationB200(nn.Module):

@@ -87,43 +87,58 @@ def workspace_bytes(B: int, N: int, c: int, dtype: torch.dtype, outgoing: bool =
     return n.value
 
 
+_struct_cache: dict = {}
+_STRUCT_CACHE_MAX = 256
+
+
+def _pinned_weights(dtype, dims, specs):
+    """``specs``: ten ``(tensor, name, expected shape)`` in the field order of ``trimul_weights``;
+    1-D entries are the LayerNorm vectors (always fp32), 2-D ones Linear weights of ``dtype``.
+    Validates, converts where dtype or layout differ, and returns ``(struct, copies)``: ``copies``
+    are the conversions made here, which must outlive the enqueued kernels.
+
+    A parameter set that needed no conversion is remembered under its addresses, dtypes, shapes and
+    contiguity (all the struct depends on), so that the next call with the same parameters skips the
+    validation: for the small problems a block call is otherwise bound by this host code."""
+    key = [dtype, dims]
+    for t, _, _ in specs:
+        key += (t.data_ptr(), t.dtype, t.shape, t.is_contiguous())
+    key = tuple(key)
+    hit = _struct_cache.get(key)
+    if hit is not None:
+        return hit, []
+    copies, ptrs = [], []
+    for t, name, shape in specs:
+        if tuple(t.shape) != shape:
+            raise ValueError(f"{name} must have shape {shape}, got {tuple(t.shape)}")
+        _require_cuda(t, name)
+        want = torch.float32 if len(shape) == 1 else dtype
+        if t.dtype != want or not t.is_contiguous():
+            t = t.detach().to(want).contiguous()
+            copies.append(t)
+        ptrs.append(t.data_ptr())
+    w = _lib.Weights(*ptrs)
+    if not copies:
+        if len(_struct_cache) >= _STRUCT_CACHE_MAX:
+            _struct_cache.clear()
+        _struct_cache[key] = w
+    return w, copies
+
+
 def _weights_struct(c, dtype, ln_in_w, ln_in_b, w_left, w_left_gate, w_right, w_right_gate,
                     ln_out_w, ln_out_b, w_gate, w_out, device, c_hidden=None, c_proj=None):
-    """Validate and pin the parameter tensors; returns (struct, keep-alive list).  ``c_hidden``
+    """Validate and pin the parameter tensors; returns (struct, copies to keep alive).  ``c_hidden``
     (default ``c``) is the width of the output LayerNorm and the input width of ``to_out``;
     ``c_proj`` (default ``c``) the number of rows of the four input projections, i.e. the number
     of operand planes stage 1 produces per batch element."""
-    keep = []
     h = c if c_hidden is None else c_hidden
     hp = c if c_proj is None else c_proj
-
-    def lin(t, name, rows=c, cols=c):
-        if tuple(t.shape) != (rows, cols):
-            raise ValueError(f"{name} must have shape ({rows}, {cols}), got {tuple(t.shape)}")
-        _require_cuda(t, name)
-        t = t.detach()
-        if t.dtype != dtype or not t.is_contiguous():
-            t = t.to(dtype).contiguous()
-        keep.append(t)
-        return t.data_ptr()
-
-    def vec(t, name, n=c):
-        if tuple(t.shape) != (n,):
-            raise ValueError(f"{name} must have shape ({n},), got {tuple(t.shape)}")
-        _require_cuda(t, name)
-        t = t.detach()
-        if t.dtype != torch.float32 or not t.is_contiguous():
-            t = t.float().contiguous()
-        keep.append(t)
-        return t.data_ptr()
-
-    w = _lib.Weights(
-        vec(ln_in_w, "norm_in_weight"), vec(ln_in_b, "norm_in_bias"),
-        lin(w_left, "to_left.weight", hp), lin(w_left_gate, "to_left_gate.weight", hp),
-        lin(w_right, "to_right.weight", hp), lin(w_right_gate, "to_right_gate.weight", hp),
-        vec(ln_out_w, "norm_out_weight", h), vec(ln_out_b, "norm_out_bias", h),
-        lin(w_gate, "to_gate.weight"), lin(w_out, "to_out.weight", c, h))
-    return w, keep
+    return _pinned_weights(dtype, (c, h, hp), (
+        (ln_in_w, "norm_in_weight", (c,)), (ln_in_b, "norm_in_bias", (c,)),
+        (w_left, "to_left.weight", (hp, c)), (w_left_gate, "to_left_gate.weight", (hp, c)),
+        (w_right, "to_right.weight", (hp, c)), (w_right_gate, "to_right_gate.weight", (hp, c)),
+        (ln_out_w, "norm_out_weight", (h,)), (ln_out_b, "norm_out_bias", (h,)),
+        (w_gate, "to_gate.weight", (c, c)), (w_out, "to_out.weight", (c, h))))
 
 
 def trimul_forward(

@@ -130,3 +130,35 @@ def test_functional_op_reads_d_hidden_off_the_packed_projections():
         f(x, "outgoing", None, v_d, v_d, p_in, torch.zeros(2 * h, d + 8), v_h, v_h, p_out, g_out)
     with pytest.raises(RuntimeError, match="no CPU path"):
         f(x, "outgoing", None, v_d, v_d, p_in, p_in, v_h, v_h, p_out, g_out)
+
+
+def test_parameter_struct_cache_is_keyed_by_what_the_struct_depends_on(monkeypatch):
+    """The validated parameter struct is remembered under addresses, dtypes, shapes and contiguity:
+    the same tensors hit it, a reshaped or transposed view of the same memory does not (and is
+    validated afresh), and parameter sets that needed a conversion are never remembered."""
+    import torch
+    from miniworld_engine_b200 import functional as F
+    monkeypatch.setattr(F, "_require_cuda", lambda t, name: None)      # CPU tensors stand in
+    monkeypatch.setattr(F, "_struct_cache", {})
+    c, h = 16, 8
+    vec = lambda n: torch.ones(n)
+    lin = lambda r, k: torch.zeros(r, k, dtype=torch.bfloat16)
+    p = dict(ln_in_w=vec(c), ln_in_b=vec(c), w_left=lin(h, c), w_left_gate=lin(h, c), w_right=lin(h, c),
+             w_right_gate=lin(h, c), ln_out_w=vec(h), ln_out_b=vec(h), w_gate=lin(c, c), w_out=lin(c, h))
+    w1, k1 = F._weights_struct(c, torch.bfloat16, device=None, c_hidden=h, c_proj=h, **p)
+    w2, k2 = F._weights_struct(c, torch.bfloat16, device=None, c_hidden=h, c_proj=h, **p)
+    assert w1 is w2 and k1 == [] and k2 == [] and len(F._struct_cache) == 1
+    assert w1.w_out == p["w_out"].data_ptr() and w1.ln_out_bias == p["ln_out_b"].data_ptr()
+    # same memory seen as [h, c] instead of [c, h]: a different key, and the shape check fires
+    with pytest.raises(ValueError, match="to_out.weight"):
+        F._weights_struct(c, torch.bfloat16, device=None, c_hidden=h, c_proj=h, **{**p, "w_out": p["w_out"].view(h, c)})
+    # a transposed (non-contiguous) square weight is converted to a copy, which is returned for
+    # keeping alive and not remembered
+    w3, k3 = F._weights_struct(c, torch.bfloat16, device=None, c_hidden=h, c_proj=h, **{**p, "w_gate": p["w_gate"].t()})
+    assert len(k3) == 1 and w3.w_gate == k3[0].data_ptr() != p["w_gate"].data_ptr() and len(F._struct_cache) == 1
+    # fp32 Linear weights for a bf16 call: converted, not remembered
+    w4, k4 = F._weights_struct(c, torch.bfloat16, device=None, c_hidden=h, c_proj=h, **{**p, "w_left": p["w_left"].float()})
+    assert len(k4) == 1 and k4[0].dtype == torch.bfloat16 and len(F._struct_cache) == 1
+    # other expected widths with the same tensors: validated afresh and rejected
+    with pytest.raises(ValueError):
+        F._weights_struct(c, torch.bfloat16, device=None, c_hidden=c, c_proj=h, **p)
