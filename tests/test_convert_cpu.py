@@ -11,7 +11,23 @@ import torch.nn as nn
 from miniworld_engine_b200 import (BidirectionalTriangleMultiplicationB200, TriangleMultiplicationB200,
                                    from_reference, install)
 
-REFERENCE = "/root/reference/src"
+
+
+def _reference_src() -> str:
+    """``src`` directory of the reference project where this machine has one: the environment
+    variable MINIWORLD_REFERENCE, else the ``reference_path`` recorded in BASELINE.json."""
+    root = os.environ.get("MINIWORLD_REFERENCE")
+    if not root:
+        try:
+            import json
+            with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "BASELINE.json")) as f:
+                root = json.load(f).get("reference_path", "")
+        except (OSError, ValueError):
+            root = ""
+    return os.path.join(root, "src") if root else ""
+
+
+REFERENCE = _reference_src()
 
 
 class _LN(nn.Module):
