@@ -23,6 +23,7 @@
 #include "tm1_fold_sm100.cuh"
 #include "tm2_sm100.cuh"
 #include "tm2_fold_sm100.cuh"
+#include "wmma_kernels.cuh"
 
 using namespace trimul;
 
@@ -215,6 +216,33 @@ int run_plain_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, cons
     return launch_status();
 }
 
+// Warp-MMA kernels: bf16, c and h multiples of 16, weight matrices 32-byte aligned (fragment loads).
+bool wmma_ok(const trimul_desc* d, const void* const* mats, int n) {
+    if (d->dtype != TRIMUL_DTYPE_BF16 || (d->flags & TRIMUL_FLAG_PLAIN_KERNELS) != 0) return false;
+    if ((d->c % 16) != 0 || (d->c_hidden % 16) != 0) return false;
+    for (int i = 0; i < n; ++i)
+        if ((reinterpret_cast<uintptr_t>(mats[i]) & 31u) != 0) return false;
+    return true;
+}
+
+int run_wmma_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
+                 const trimul_planes* a, const trimul_planes* b, cudaStream_t st) {
+    PlainTm1Params p;
+    p.B = d->B; p.rows = d->rows; p.N = d->N; p.c = d->c; p.row0 = d->row0; p.h = d->c_hidden;
+    p.incoming = d->direction == TRIMUL_INCOMING;
+    p.mask_kind = mask ? d->mask_kind : 0;
+    p.mask = mask;
+    p.gamma = w->ln_in_weight; p.beta = w->ln_in_bias; p.eps = d->eps_in;
+    p.w_left = w->w_left; p.w_left_gate = w->w_left_gate; p.w_right = w->w_right; p.w_right_gate = w->w_right_gate;
+    p.a = view_of(*a); p.b = view_of(*b);
+    const int smem = wmma_tm1_smem(d->c);
+    if (!ensure_smem(wmma_tm1_kernel, wmma_tm1_smem(kPlainMaxC))) return TRIMUL_E_CUDA;   // opt in once, for the widest case
+    const int64_t along = p.incoming ? d->rows : d->N, other = p.incoming ? d->N : d->rows;
+    const int64_t grid = (int64_t)d->B * other * ((along + kWmPos - 1) / kWmPos);
+    wmma_tm1_kernel<<<(unsigned)grid, kWmThreads, smem, st>>>(static_cast<const __nv_bfloat16*>(z), p);
+    return launch_status();
+}
+
 // `n_dest` == 0: a and b are single plane sets.  `n_dest` > 0: a[k] and b[k], k < n_dest, are the
 // buffers that receive planes [k * P, (k + 1) * P), P = B * 128 / n_dest (identical geometry).
 int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
@@ -396,6 +424,24 @@ int run_plain_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri,
     return launch_status();
 }
 
+int run_wmma_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
+                 const void* residual, cudaStream_t st) {
+    PlainTm2Params p;
+    p.B = d->B; p.rows = d->rows; p.N = d->N; p.c = d->c; p.h = d->c_hidden;
+    p.gamma_in = w->ln_in_weight; p.beta_in = w->ln_in_bias;
+    p.gamma_out = w->ln_out_weight; p.beta_out = w->ln_out_bias;
+    p.eps_in = d->eps_in; p.eps_out = d->eps_out;
+    p.w_gate = w->w_gate; p.w_out = w->w_out;
+    p.tri = view_of(*tri);
+    const int smem = wmma_tm2_smem(d->c, d->c_hidden);
+    if (!ensure_smem(wmma_tm2_kernel, wmma_tm2_smem(kPlainMaxC, kPlainMaxC))) return TRIMUL_E_CUDA;
+    const int64_t grid = (int64_t)d->B * d->rows * ((d->N + kWmPos - 1) / kWmPos);
+    wmma_tm2_kernel<<<(unsigned)grid, kWmThreads, smem, st>>>(
+        static_cast<const __nv_bfloat16*>(z), static_cast<__nv_bfloat16*>(out),
+        static_cast<const __nv_bfloat16*>(residual), p);
+    return launch_status();
+}
+
 int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
                  const void* residual, cudaStream_t st, int32_t* status) {
     CUtensorMap tmZ, tmWg, tmWo, tmOut, tmRes, tmTri;
@@ -528,6 +574,8 @@ int trimul_b200_tm1(const trimul_desc* desc, const void* z, const uint8_t* mask,
                            ((reinterpret_cast<uintptr_t>(a->base) | reinterpret_cast<uintptr_t>(b->base)) & 127u) == 0;
     if (tensor_core_path(desc) && desc->c_hidden == 128 && chunks_ok)
         return run_fast_tm1(desc, z, mask, w, a, b, st, status);
+    const void* mats[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
+    if (wmma_ok(desc, mats, 4)) return run_wmma_tm1(desc, z, mask, w, a, b, st);
     return run_plain_tm1<__nv_bfloat16>(desc, z, mask, w, a, b, st);
 }
 
@@ -638,6 +686,8 @@ int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes*
         const bool folded_ok = (desc->flags & TRIMUL_FLAG_INPLACE_NORM_STAGE3) == 0 && (residual == nullptr || residual == z);
         if (!wide || folded_ok) return run_fast_tm2(desc, z, tri, w, out, residual, st, status);
     }
+    const void* mats[2] = {w->w_gate, w->w_out};
+    if (wmma_ok(desc, mats, 2)) return run_wmma_tm2(desc, z, tri, w, out, residual, st);
     return run_plain_tm2<__nv_bfloat16>(desc, z, tri, w, out, residual, st);
 }
 

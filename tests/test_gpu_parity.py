@@ -123,6 +123,47 @@ def test_cfg4_outgoing_bf16_b2_n512_dpair_sweep(c, dev):
     assert err <= TOL_BF16, f"c={c}: rel-RMS {err:.3e}"
 
 
+@pytest.mark.parametrize("outgoing", [True, False], ids=["outgoing", "incoming"])
+@pytest.mark.parametrize("c,B,N,mask_kind", [
+    (64, 2, 70, "tail7"), (256, 1, 65, "rand5"), (48, 1, 33, None), (32, 1, 130, "tail20"), (208, 1, 20, "tail3"),
+], ids=["c64", "c256", "c48", "c32", "c208"])
+def test_bf16_other_widths_take_the_warp_mma_kernels(dev, c, B, N, mask_kind, outgoing):
+    """bf16 with c != 128 (a multiple of 16): stages 1 and 3 run on the warp-MMA kernels.  Checked
+    against the oracle and, stage by stage on a row slab (rows < N, row0 > 0), against the scalar
+    CUDA-core kernels, which round at the same points."""
+    from miniworld_engine_b200 import stages as S
+    from tests._util import weights_dict
+    w = O.make_weights(c, 5, affine="random")
+    z = O.make_input(B, N, c, 6)
+    m = None if mask_kind is None else O.make_token_mask(B, N, mask_kind)
+    y = run_block(z, m, w, outgoing, torch.bfloat16, dev)
+    ref = oracle_out(z, m, w, outgoing, torch.bfloat16)
+    err = O.rel_rms(y.float(), ref.float())
+    assert err <= TOL_BF16, f"rel-RMS {err:.3e}"
+    y_plain = run_block(z, m, w, outgoing, torch.bfloat16, dev, plain_kernels=True)
+    assert O.rel_rms(y.float(), y_plain.float()) <= TOL_BF16
+    # stage 1 and stage 3 on a slab of rows
+    row0, rows = N // 3, N - N // 3 - 2
+    zs = z.bfloat16().to(dev)[:, row0:row0 + rows].contiguous()
+    md = None if m is None else m.to(dev)
+    wd = weights_dict(w, torch.bfloat16, dev)
+    pr, pc = (rows, N) if outgoing else (N, rows)
+    got, want = [], []
+    for plain, dst in ((False, got), (True, want)):
+        a = S.alloc_planes(B * c, pr, pc, torch.bfloat16, dev, fill=0)
+        b = S.alloc_planes(B * c, pr, pc, torch.bfloat16, dev, fill=0)
+        S.tm1(zs, md, wd, a, b, outgoing=outgoing, row0=row0, plain_kernels=plain)
+        dst += [S.planes_to_dense(a).float().cpu(), S.planes_to_dense(b).float().cpu()]
+    for g, wnt in zip(got, want):
+        assert O.rel_rms(g, wnt) <= 4e-3            # same rounding points, different summation order
+        assert torch.equal(g == 0, wnt == 0)        # the masked positions are exactly zero in both
+    tri = S.alloc_planes(B * c, rows, N, torch.bfloat16, dev)
+    tri.buf.copy_(torch.randn(tri.buf.shape, generator=torch.Generator().manual_seed(9)).bfloat16())
+    o1 = S.tm2(zs, tri, wd, residual=zs, row0=row0).float().cpu()
+    o2 = S.tm2(zs, tri, wd, residual=zs, row0=row0, plain_kernels=True).float().cpu()
+    assert O.rel_rms(o1 - zs.float().cpu(), o2 - zs.float().cpu()) <= 2e-2      # the update alone; both round the sum to bf16
+
+
 def test_pair_mask_and_token_mask_agree(dev):
     w, z = O.make_weights(128, 5, affine="random"), O.make_input(1, 96, 128, 6)
     m = O.make_token_mask(1, 96, "rand5", seed=9)
