@@ -18,7 +18,8 @@ the stage entry points:
   ``[d, 2h]`` projection (for ``h = 128`` the tri tile is consumed as two 128-channel halves).
 
 bf16 with ``d = h = 128`` takes the tensor-core kernels in every stage.  ``d_hidden != d_pair``
-(``h`` a multiple of 8, ``2h <= 256``) is served too: stage 1 then runs on the CUDA-core kernel,
+(``h`` a multiple of 8, ``2h <= 256``) is served too: stage 1 then runs on the warp-MMA kernel
+(widths that are multiples of 16; otherwise the CUDA-core kernel),
 the contraction stays on the tensor cores for bf16, and stage 3 does when ``d = 128`` and
 ``2h`` is 128 or 256.  fp32 takes the CUDA-core kernels throughout.
 

@@ -114,7 +114,13 @@ __global__ void __launch_bounds__(kWmThreads) wmma_tm1_kernel(const __nv_bfloat1
     const int o = bo % O, b = bo / O;
     const int npos = min(kWmPos, F - f0);
 
+    // element offsets of the 64 positions inside a plane, computed once: PlaneView::offset divides
+    // 64-bit integers, far too slow to repeat per channel
+    __shared__ long long ofs_a[kWmPos], ofs_b[kWmPos];
     if (threadIdx.x < kWmPos) {
+        const long long col = min(f0 + (int)threadIdx.x, F - 1);
+        ofs_a[threadIdx.x] = p.a.offset(0, o, col);
+        ofs_b[threadIdx.x] = p.b.offset(0, o, col);
         float k = 0.f;
         if (threadIdx.x < npos) {
             const int r = p.incoming ? f0 + threadIdx.x : o, s = p.incoming ? o : f0 + threadIdx.x;
@@ -173,8 +179,8 @@ __global__ void __launch_bounds__(kWmThreads) wmma_tm1_kernel(const __nv_bfloat1
                     const float left = scr[j * 16 + i] * sigmoid_ref(scr[256 + j * 16 + i]) * kq;
                     const float right = scr[512 + j * 16 + i] * sigmoid_ref(scr[768 + j * 16 + i]) * kq;
                     const long long plane = (long long)b * h + nf * 16 + j;
-                    static_cast<__nv_bfloat16*>(p.a.base)[p.a.offset(plane, o, f0 + q)] = __float2bfloat16_rn(left);
-                    static_cast<__nv_bfloat16*>(p.b.base)[p.b.offset(plane, o, f0 + q)] = __float2bfloat16_rn(right);
+                    static_cast<__nv_bfloat16*>(p.a.base)[plane * p.a.plane_stride + ofs_a[q]] = __float2bfloat16_rn(left);
+                    static_cast<__nv_bfloat16*>(p.b.base)[plane * p.b.plane_stride + ofs_b[q]] = __float2bfloat16_rn(right);
                 }
             }
             __syncwarp();
@@ -204,9 +210,11 @@ wmma_tm2_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__
     // raw tri tile, transposed into [position][channel]: consecutive threads walk the contiguous position axis
     {
         const int q = threadIdx.x & 63;
+        // the position's offset inside a plane once (PlaneView::offset divides 64-bit integers)
+        const __nv_bfloat16* src = static_cast<const __nv_bfloat16*>(p.tri.base) + p.tri.offset(0, r, min(s0 + q, p.N - 1));
+#pragma unroll 4
         for (int ch = threadIdx.x >> 6; ch < h; ch += 4)
-            tn[q * ldt + ch] = q < npos ? static_cast<const __nv_bfloat16*>(p.tri.base)[p.tri.offset((long long)b * h + ch, r, s0 + q)]
-                                        : __float2bfloat16_rn(0.f);
+            tn[q * ldt + ch] = q < npos ? src[((long long)b * h + ch) * p.tri.plane_stride] : __float2bfloat16_rn(0.f);
     }
     wmma_ln_tile([&](int q) { return z + (pos0 + q) * c; }, npos, c, ldx, p.gamma_in, p.beta_in, p.eps_in, xn);
     __syncthreads();

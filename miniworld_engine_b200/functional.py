@@ -163,7 +163,8 @@ def trimul_forward(
     The hidden width ``h`` is read off the weights: the four input projections are ``[h, c]``,
     ``ln_out_*`` have ``h`` entries and ``w_out`` is ``[c, h]`` (``whole_op.py:203-209``).  bf16 with
     ``c = h = 128`` runs on the tensor-core kernels; any other multiple of 8 up to 256 runs stage 1
-    (and, unless ``c = 128`` and ``h`` is 128 or 256, stage 3) on the CUDA-core kernels."""
+    (and, unless ``c = 128`` and ``h`` is 128 or 256, stage 3) on the warp-MMA kernels when both are
+    multiples of 16 and the activations bf16, else on the CUDA-core kernels."""
     if x.dim() != 4 or x.shape[1] != x.shape[2]:
         raise ValueError(f"x must be [B, N, N, c], got {tuple(x.shape)}")
     _require_cuda(x, "x")
