@@ -236,10 +236,11 @@ int run_wmma_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     p.w_left = w->w_left; p.w_left_gate = w->w_left_gate; p.w_right = w->w_right; p.w_right_gate = w->w_right_gate;
     p.a = view_of(*a); p.b = view_of(*b);
     const int smem = wmma_tm1_smem(d->c);
-    if (!ensure_smem(wmma_tm1_kernel, wmma_tm1_smem(kPlainMaxC))) return TRIMUL_E_CUDA;   // opt in once, for the widest case
+    auto kernel = d->c_hidden >= 128 ? wmma_tm1_kernel<4> : wmma_tm1_kernel<2>;
+    if (!ensure_smem(kernel, wmma_tm1_smem(kPlainMaxC))) return TRIMUL_E_CUDA;   // opt in once, for the widest case
     const int64_t along = p.incoming ? d->rows : d->N, other = p.incoming ? d->N : d->rows;
     const int64_t grid = (int64_t)d->B * other * ((along + kWmPos - 1) / kWmPos);
-    wmma_tm1_kernel<<<(unsigned)grid, kWmThreads, smem, st>>>(static_cast<const __nv_bfloat16*>(z), p);
+    kernel<<<(unsigned)grid, kWmThreads, smem, st>>>(static_cast<const __nv_bfloat16*>(z), p);
     return launch_status();
 }
 
@@ -434,9 +435,10 @@ int run_wmma_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     p.w_gate = w->w_gate; p.w_out = w->w_out;
     p.tri = view_of(*tri);
     const int smem = wmma_tm2_smem(d->c, d->c_hidden);
-    if (!ensure_smem(wmma_tm2_kernel, wmma_tm2_smem(kPlainMaxC, kPlainMaxC))) return TRIMUL_E_CUDA;
+    auto kernel = d->c >= 128 ? wmma_tm2_kernel<4> : wmma_tm2_kernel<2>;
+    if (!ensure_smem(kernel, wmma_tm2_smem(kPlainMaxC, kPlainMaxC))) return TRIMUL_E_CUDA;
     const int64_t grid = (int64_t)d->B * d->rows * ((d->N + kWmPos - 1) / kWmPos);
-    wmma_tm2_kernel<<<(unsigned)grid, kWmThreads, smem, st>>>(
+    kernel<<<(unsigned)grid, kWmThreads, smem, st>>>(
         static_cast<const __nv_bfloat16*>(z), static_cast<__nv_bfloat16*>(out),
         static_cast<const __nv_bfloat16*>(residual), p);
     return launch_status();

@@ -4,8 +4,8 @@
 // They keep the layouts and the bf16 rounding points of the other kernels (x_n, a, b, tri_n, out
 // rounded to bf16, fp32 accumulation and fp32 LayerNorm / gate arithmetic in between) and use the
 // warp-wide 16x16x16 MMA through nvcuda::wmma: one block owns 64 positions, normalises them into
-// shared memory once, and each warp multiplies a 32-position slice against the weight matrices,
-// whose 16x16 fragments it reads straight from global memory (they stay in L1/L2: at most
+// shared memory once, and each warp multiplies a 32- or 64-position slice against the weight
+// matrices, whose 16x16 fragments it reads straight from global memory (they stay in L2: at most
 // 4 x 256 x 256 bf16).  These are not tuned like the c = 128 kernels; they exist so that the other
 // widths of the reference's d_pair sweep do not fall back to the scalar CUDA-core kernels.
 #pragma once
@@ -98,7 +98,10 @@ using WmC = nvcuda::wmma::fragment<nvcuda::wmma::accumulator, 16, 16, 16, float>
 // elements (r, s).  Incoming: 64 consecutive rows r of one column s, plane elements (s, r) — in both
 // cases the 64 positions are contiguous along the plane's column axis.
 // grid: B * (outgoing ? rows : N) * ceil((outgoing ? N : rows) / 64); dynamic smem wmma_tm1_smem(c).
-__global__ void __launch_bounds__(kWmThreads) wmma_tm1_kernel(const __nv_bfloat16* __restrict__ z, PlainTm1Params p) {
+// kMT = 16-position tiles per warp: 2 (a warp owns 32 positions and every 4th 16-channel group) for
+// narrow outputs, 4 (all 64 positions, every 8th group) once there are at least 8 groups.
+template <int kMT>
+__global__ void __launch_bounds__(kWmThreads, 2) wmma_tm1_kernel(const __nv_bfloat16* __restrict__ z, PlainTm1Params p) {
     extern __shared__ __align__(128) unsigned char wm_smem[];
     const int c = p.c, h = p.h, ldx = c + 8;
     __nv_bfloat16* xn = reinterpret_cast<__nv_bfloat16*>(wm_smem);
@@ -141,56 +144,64 @@ __global__ void __launch_bounds__(kWmThreads) wmma_tm1_kernel(const __nv_bfloat1
         npos, c, ldx, p.gamma, p.beta, p.eps, xn);
     __syncthreads();
 
-    const __nv_bfloat16* W[4] = {static_cast<const __nv_bfloat16*>(p.w_left), static_cast<const __nv_bfloat16*>(p.w_left_gate),
-                                 static_cast<const __nv_bfloat16*>(p.w_right), static_cast<const __nv_bfloat16*>(p.w_right_gate)};
-    const int mp = warp & 1;                 // positions [32 mp, 32 mp + 32)
+    // Two passes, one gated projection each (left -> a, right -> b): a warp holds the value and the
+    // gate accumulators of kMT position tiles, so a weight fragment fetched from L2 serves 16 kMT
+    // positions.
+    constexpr int kClasses = 2 * kMT;                    // residue classes of the 16-channel groups: 8 warps / (4 / kMT) slices
+    const int mp = kMT == 2 ? (warp & 1) : 0;            // first position of the warp's slice / 32
+    const int cls = kMT == 2 ? (warp >> 1) : warp;
     float* scr = scr_all + warp * 4 * 256;
-    for (int nf = warp >> 1; nf < h / 16; nf += 4) {
-        WmC acc[2][4];
+    for (int pass = 0; pass < 2; ++pass) {
+        const __nv_bfloat16* Wv = static_cast<const __nv_bfloat16*>(pass ? p.w_right : p.w_left);
+        const __nv_bfloat16* Wg = static_cast<const __nv_bfloat16*>(pass ? p.w_right_gate : p.w_left_gate);
+        __nv_bfloat16* dst = static_cast<__nv_bfloat16*>(pass ? p.b.base : p.a.base);
+        const long long dst_plane = pass ? p.b.plane_stride : p.a.plane_stride;
+        const long long* ofs = pass ? ofs_b : ofs_a;
+        for (int nf = cls; nf < h / 16; nf += kClasses) {
+            WmC av[kMT], ag[kMT];
 #pragma unroll
-        for (int t = 0; t < 2; ++t)
-#pragma unroll
-            for (int m = 0; m < 4; ++m) nvcuda::wmma::fill_fragment(acc[t][m], 0.f);
-#pragma unroll 1
-        for (int k0 = 0; k0 < c; k0 += 16) {
-            WmA a0, a1;
-            nvcuda::wmma::load_matrix_sync(a0, xn + (mp * 32) * ldx + k0, ldx);
-            nvcuda::wmma::load_matrix_sync(a1, xn + (mp * 32 + 16) * ldx + k0, ldx);
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                WmB bf;
-                nvcuda::wmma::load_matrix_sync(bf, W[m] + (long long)nf * 16 * c + k0, c);
-                nvcuda::wmma::mma_sync(acc[0][m], a0, bf, acc[0][m]);
-                nvcuda::wmma::mma_sync(acc[1][m], a1, bf, acc[1][m]);
+            for (int t = 0; t < kMT; ++t) {
+                nvcuda::wmma::fill_fragment(av[t], 0.f);
+                nvcuda::wmma::fill_fragment(ag[t], 0.f);
             }
-        }
+#pragma unroll 2
+            for (int k0 = 0; k0 < c; k0 += 16) {
+                WmB bv, bg;
+                nvcuda::wmma::load_matrix_sync(bv, Wv + (long long)nf * 16 * c + k0, c);
+                nvcuda::wmma::load_matrix_sync(bg, Wg + (long long)nf * 16 * c + k0, c);
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
-#pragma unroll
-            for (int m = 0; m < 4; ++m)      // column-major: element (position i, channel j) at j * 16 + i
-                nvcuda::wmma::store_matrix_sync(scr + m * 256, acc[t][m], 16, nvcuda::wmma::mem_col_major);
-            __syncwarp();
-            const int i = lane & 15;
-            const int q = mp * 32 + t * 16 + i;
-            if (q < npos) {
-                const float kq = keep[q];
-                // plane element: outgoing (r, s) = (o, f0 + q); incoming (s, r) = (o, f0 + q)
-                for (int j = lane >> 4; j < 16; j += 2) {
-                    const float left = scr[j * 16 + i] * sigmoid_ref(scr[256 + j * 16 + i]) * kq;
-                    const float right = scr[512 + j * 16 + i] * sigmoid_ref(scr[768 + j * 16 + i]) * kq;
-                    const long long plane = (long long)b * h + nf * 16 + j;
-                    static_cast<__nv_bfloat16*>(p.a.base)[plane * p.a.plane_stride + ofs_a[q]] = __float2bfloat16_rn(left);
-                    static_cast<__nv_bfloat16*>(p.b.base)[plane * p.b.plane_stride + ofs_b[q]] = __float2bfloat16_rn(right);
+                for (int t = 0; t < kMT; ++t) {
+                    WmA a;
+                    nvcuda::wmma::load_matrix_sync(a, xn + (mp * 32 + t * 16) * ldx + k0, ldx);
+                    nvcuda::wmma::mma_sync(av[t], a, bv, av[t]);
+                    nvcuda::wmma::mma_sync(ag[t], a, bg, ag[t]);
                 }
             }
-            __syncwarp();
+#pragma unroll
+            for (int t = 0; t < kMT; ++t) {      // column-major: element (position i, channel j) at j * 16 + i
+                nvcuda::wmma::store_matrix_sync(scr, av[t], 16, nvcuda::wmma::mem_col_major);
+                nvcuda::wmma::store_matrix_sync(scr + 256, ag[t], 16, nvcuda::wmma::mem_col_major);
+                __syncwarp();
+                const int i = lane & 15;
+                const int q = mp * 32 + t * 16 + i;
+                if (q < npos) {
+                    const float kq = keep[q];
+                    // plane element: outgoing (r, s) = (o, f0 + q); incoming (s, r) = (o, f0 + q)
+                    for (int j = lane >> 4; j < 16; j += 2) {
+                        const float val = scr[j * 16 + i] * sigmoid_ref(scr[256 + j * 16 + i]) * kq;
+                        dst[((long long)b * h + nf * 16 + j) * dst_plane + ofs[q]] = __float2bfloat16_rn(val);
+                    }
+                }
+                __syncwarp();
+            }
         }
     }
 }
 
 // Stage 3.  A block owns 64 consecutive columns of one row of the slab.
-// grid: B * rows * ceil(N / 64); dynamic smem wmma_tm2_smem(c, h).
-__global__ void __launch_bounds__(kWmThreads)
+// grid: B * rows * ceil(N / 64); dynamic smem wmma_tm2_smem(c, h).  kMT as in stage 1.
+template <int kMT>
+__global__ void __launch_bounds__(kWmThreads, 2)
 wmma_tm2_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__ out,
                 const __nv_bfloat16* __restrict__ residual, PlainTm2Params p) {
     extern __shared__ __align__(128) unsigned char wm_smem[];
@@ -226,37 +237,41 @@ wmma_tm2_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__
 
     const __nv_bfloat16* Wg = static_cast<const __nv_bfloat16*>(p.w_gate);
     const __nv_bfloat16* Wo = static_cast<const __nv_bfloat16*>(p.w_out);
-    const int mp = warp & 1;
+    constexpr int kClasses = 2 * kMT;
+    const int mp = kMT == 2 ? (warp & 1) : 0;
+    const int cls = kMT == 2 ? (warp >> 1) : warp;
     float* scr = scr_all + warp * 4 * 256;
-    for (int nf = warp >> 1; nf < c / 16; nf += 4) {
-        WmC g[2], v[2];
+    for (int nf = cls; nf < c / 16; nf += kClasses) {
+        WmC g[kMT], v[kMT];
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {
+        for (int t = 0; t < kMT; ++t) {
             nvcuda::wmma::fill_fragment(g[t], 0.f);
             nvcuda::wmma::fill_fragment(v[t], 0.f);
         }
-#pragma unroll 4
+#pragma unroll 2
         for (int k0 = 0; k0 < c; k0 += 16) {
-            WmA a0, a1;
             WmB bf;
-            nvcuda::wmma::load_matrix_sync(a0, xn + (mp * 32) * ldx + k0, ldx);
-            nvcuda::wmma::load_matrix_sync(a1, xn + (mp * 32 + 16) * ldx + k0, ldx);
             nvcuda::wmma::load_matrix_sync(bf, Wg + (long long)nf * 16 * c + k0, c);
-            nvcuda::wmma::mma_sync(g[0], a0, bf, g[0]);
-            nvcuda::wmma::mma_sync(g[1], a1, bf, g[1]);
+#pragma unroll
+            for (int t = 0; t < kMT; ++t) {
+                WmA a;
+                nvcuda::wmma::load_matrix_sync(a, xn + (mp * 32 + t * 16) * ldx + k0, ldx);
+                nvcuda::wmma::mma_sync(g[t], a, bf, g[t]);
+            }
         }
-#pragma unroll 4
+#pragma unroll 2
         for (int k0 = 0; k0 < h; k0 += 16) {
-            WmA a0, a1;
             WmB bf;
-            nvcuda::wmma::load_matrix_sync(a0, tn + (mp * 32) * ldt + k0, ldt);
-            nvcuda::wmma::load_matrix_sync(a1, tn + (mp * 32 + 16) * ldt + k0, ldt);
             nvcuda::wmma::load_matrix_sync(bf, Wo + (long long)nf * 16 * h + k0, h);
-            nvcuda::wmma::mma_sync(v[0], a0, bf, v[0]);
-            nvcuda::wmma::mma_sync(v[1], a1, bf, v[1]);
+#pragma unroll
+            for (int t = 0; t < kMT; ++t) {
+                WmA a;
+                nvcuda::wmma::load_matrix_sync(a, tn + (mp * 32 + t * 16) * ldt + k0, ldt);
+                nvcuda::wmma::mma_sync(v[t], a, bf, v[t]);
+            }
         }
 #pragma unroll
-        for (int t = 0; t < 2; ++t) {        // row-major: element (position i, channel j) at i * 16 + j
+        for (int t = 0; t < kMT; ++t) {      // row-major: element (position i, channel j) at i * 16 + j
             nvcuda::wmma::store_matrix_sync(scr, g[t], 16, nvcuda::wmma::mem_row_major);
             nvcuda::wmma::store_matrix_sync(scr + 256, v[t], 16, nvcuda::wmma::mem_row_major);
             __syncwarp();
