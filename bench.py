@@ -27,6 +27,8 @@ Workloads
                            collective in the data path: independent pair tensors).
   n384_outgoing            BASELINE config 2.
   n768_incoming_pad77      BASELINE config 3.
+  n512_b2_outgoing_c64/c256, n384_outgoing_c256
+                           BASELINE config 4 (d_pair sweep) and the reference's published c=256 case.
   n2048_pair_sharded       BASELINE config 5: outgoing then incoming block at N=2048, output rows
                            sharded over the ranks (strong scaling, NCCL exchange per block).
 
@@ -52,6 +54,11 @@ WORKLOADS = {
     "n768_incoming_pad77": (1, 768, 128, False, "tail77"),
     "n1024_outgoing": (1, 1024, 128, True, "ones"),
     "n2048_outgoing": (1, 2048, 128, True, "rand5"),
+    # other channel widths (BASELINE config 4 and the reference's d_pair sweep): stages 1 and 3 run on
+    # the warp-MMA kernels there, the contraction on the same tcgen05 kernel
+    "n384_outgoing_c256": (1, 384, 256, True, "ones"),
+    "n512_b2_outgoing_c256": (2, 512, 256, True, "ones"),
+    "n512_b2_outgoing_c64": (2, 512, 64, True, "ones"),
 }
 # The bidirectional block (outgoing contraction on the first 128 hidden channels, incoming on the
 # second 128, one LayerNorm over all 256, residual added): single GPU, stage split by CUDA events.
@@ -72,9 +79,12 @@ UNIT = "TFLOP/s"
 # The reference publishes this metric on a B200 for its own sm_100 path, module forward (block +
 # residual add), bf16, B=1, c=128, measured by CUDA-graph replay: 0.5437 ms at N=768 = 427 TFLOP/s
 # with the FLOP count used here, 0.1596 ms at N=384, 0.9891 ms at N=1024
-# (benchmarks/modules/triangle_multiplication/results/b200/tables/inference_seq_len.csv:17,5,25).
-PUBLISHED_MS = {"n768_outgoing": 0.5437, "n384_outgoing": 0.1596, "n1024_outgoing": 0.9891}
-PUBLISHED_TFLOPS = {k: (2.0 * WORKLOADS[k][1] ** 3 * 128 + 12.0 * WORKLOADS[k][1] ** 2 * 128 ** 2) / (ms * 1e-3) / 1e12
+# (benchmarks/modules/triangle_multiplication/results/b200/tables/inference_seq_len.csv:17,5,25), and
+# 0.3072 ms at N=384 with c=256 (.../inference_d_pair.csv:9).
+PUBLISHED_MS = {"n768_outgoing": 0.5437, "n384_outgoing": 0.1596, "n1024_outgoing": 0.9891,
+                "n384_outgoing_c256": 0.3072}
+PUBLISHED_TFLOPS = {k: WORKLOADS[k][0] * (2.0 * WORKLOADS[k][1] ** 3 * WORKLOADS[k][2] +
+                                          12.0 * WORKLOADS[k][1] ** 2 * WORKLOADS[k][2] ** 2) / (ms * 1e-3) / 1e12
                     for k, ms in PUBLISHED_MS.items()}
 # DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
 # n768_outgoing workload, as multiples of S = B*N*N*c*2 bytes; other sizes are scaled by S
@@ -425,7 +435,8 @@ def run_b200(args):
         }
         for k, v in stage_info.items():
             v["frac"] = v["achieved"] / v["peak"]
-            v["traffic"] = NCU_TRAFFIC_PER_S[k] * S_bytes       # bytes per launch, from the ncu capture
+            # bytes per launch, from the ncu capture of the c = 128 kernels (none for the other widths)
+            v["traffic"] = NCU_TRAFFIC_PER_S[k] * S_bytes if c == 128 else None
         dom = max(stage_info, key=lambda k: stage_info[k]["ms"])
         roof = dict(stage_info[dom])
         roof.update(kernel=dom, peak_source=peaks["source"],
