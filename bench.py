@@ -337,7 +337,9 @@ def run_b200(args):
     # the same step (residual fused) captured once in a CUDA graph and replayed: no host work per
     # step, which is how the reference's published table was measured (cudagraph=manual)
     graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph):
+    # thread_local: another thread of this process (a collective library's watchdog) may touch the
+    # CUDA API while this thread captures
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
         y_graph = step_res()
     for _ in range(3):
         graph.replay()
