@@ -9,28 +9,39 @@ ONE JSON line:
 
 * ``value`` / ``metric``: whole-job TFLOP/s with inputs resident in HBM, algorithmic FLOPs
   ``B*(2*N^3*c + 12*N^2*c^2)`` per call, timed with CUDA events around exactly K steps
-  (barrier + synchronize on both sides, max over ranks);
+  (barrier + synchronize on both sides, max over ranks).  Nothing is recorded between the stage
+  launches of this region, so each stage is launched while its predecessor drains
+  (programmatic dependent launch), as in production use;
+* ``stages`` / ``roofline``: a second pass of K steps with CUDA events between the stage launches
+  (which serialises them): per-stage duration, achieved rate against the measured peak in
+  MEASURED_PEAKS.json; ``roofline`` is the slowest stage;
 * ``e2e``: the same metric through the public module call with HOST buffers: pinned
   host->device copy of z and the mask and device->host copy of the result inside the
   timed region, every step; uploads, blocks and downloads run on three streams with two
   buffers each way (a host working through a queue), the one-stream form is reported beside it;
-* ``roofline``: the dominant kernel's achieved rate (CUDA events between the stage
-  launches of the timed region) against the measured peak in MEASURED_PEAKS.json;
+* ``parity_rel_rms``: relative RMS distance of the benchmarked output from the CPU oracle on
+  the same seeded inputs (tolerance 1e-2 in bf16);
+* ``comparators``: ``torch.bmm`` (cuBLAS) on the very operand planes the contraction reads, timed
+  the same way — the kernel the reference's contraction lands on;
 * ``cpu_baseline``: the CPU oracle (a port of the reference's reference.py) timed on this
   box's host cores on a bounded sample (rank 0, N=1 only);
-* ``clocks``: SM clock and throttle reasons sampled through NVML during the timed region.
+* ``clocks``: SM clock and throttle reasons sampled through NVML while all timed legs run.
 
 Workloads
   n768_outgoing (default)  bf16, B=1, N=768, c=128, all-ones token mask: the configuration
                            the headline metric is quoted on.  With --gpus N > 1 every rank
                            runs its own block on its own pair tensor (weak scaling, no
-                           collective in the data path: independent pair tensors).
+                           collective in the data path: independent pair tensors), and the line
+                           carries a ``sharded_n2048`` record beside it: BASELINE config 5 with the
+                           output rows sharded over the N ranks (strong scaling), its speed-up over
+                           one GPU measured in the same run and a bit-for-bit comparison of every
+                           rank's slab with the unsharded result.
   n384_outgoing            BASELINE config 2.
   n768_incoming_pad77      BASELINE config 3.
   n512_b2_outgoing_c64/c256, n384_outgoing_c256
                            BASELINE config 4 (d_pair sweep) and the reference's published c=256 case.
   n2048_pair_sharded       BASELINE config 5: outgoing then incoming block at N=2048, output rows
-                           sharded over the ranks (strong scaling, NCCL exchange per block).
+                           sharded over the ranks (strong scaling, one exchange per block).
 
 ``--impl reference`` times the CPU oracle on the host cores instead (rank 0 only).
 """
@@ -96,6 +107,15 @@ def block_flops(B, N, c):
     return float(B) * (2.0 * N ** 3 * c + 12.0 * N ** 2 * c ** 2)
 
 
+def workload_config(name, B, N, c, direction, mask_kind):
+    """The ``config`` object of a workload: identical in both arms (b200 and reference)."""
+    S_mb = B * N * N * c * 2 / 1e6
+    return {"workload": name, "B": B, "N": N, "c": c, "direction": direction, "mask": mask_kind,
+            "l2": ("working set 5 x %.0f MB per call exceeds the 126 MB L2; no flush" % S_mb if 5 * S_mb > 126 else
+                   "working set 5 x %.0f MB per call fits the 126 MB L2: stages chain through L2, as in the "
+                   "reference's own measurement; no flush" % S_mb)}
+
+
 def measured_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -110,7 +130,7 @@ class ClockSampler:
     """SM clock and throttle reasons sampled through NVML (read-only queries) from a
     background thread while the timed region runs."""
 
-    def __init__(self, gpu_index: int, period_s: float = 0.002):
+    def __init__(self, gpu_index: int, period_s: float = 0.001):
         import threading
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -185,16 +205,16 @@ def cpu_oracle_rate(B, N, c, outgoing, mask_kind, budget_s=25.0, max_calls=3):
     t0 = time.perf_counter()
     O.trimul_forward(z, m, w, outgoing)                      # warm-up (thread pools, allocator)
     warm = time.perf_counter() - t0
-    best, calls = float("inf"), 0
+    best, calls, y = float("inf"), 0, None
     while calls < max_calls and (calls == 0 or (time.perf_counter() - t0) + best < budget_s):
         t1 = time.perf_counter()
-        O.trimul_forward(z, m, w, outgoing)
+        y = O.trimul_forward(z, m, w, outgoing)
         best = min(best, time.perf_counter() - t1)
         calls += 1
     return {"value": block_flops(B, N, c) / best / 1e12, "unit": UNIT, "cores": cores, "kind": "port",
             "seconds_per_call": best,
             "sample": f"{calls} full block call(s) of the same workload (bf16 oracle, best of {calls}, "
-                      f"warm-up {warm:.2f}s)"}
+                      f"warm-up {warm:.2f}s)"}, y
 
 
 def run_reference(args):
@@ -235,9 +255,9 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "calls_per_s": args.steps / dt, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic (seeded randn, all on the host)",
-        "config": {"workload": args.workload, "B": B, "N": N, "c": c,
-                   "direction": "outgoing then incoming" if pair else ("outgoing" if outgoing else "incoming"),
-                   "mask": mask_kind},
+        "config": workload_config(args.workload, B, N, c,
+                                  "outgoing then incoming" if pair else ("outgoing" if outgoing else "incoming"),
+                                  mask_kind),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"{args.steps} full block calls per run (each step = one call of the workload)"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -281,9 +301,9 @@ def run_b200(args):
     b = S.alloc_planes(planes, N, N, torch.bfloat16, dev)
     tri = S.alloc_planes(planes, N, N, torch.bfloat16, dev)
 
-    def step(ev=None):
+    def step(ev=None, residual=None):
         """One block call = the three stage launches of trimul_b200_forward, with optional
-        events between them (the events cost nothing measurable)."""
+        events between them."""
         if ev is not None:
             ev[0].record()
         S.tm1(z, m, wd, a, b, outgoing=outgoing)
@@ -292,7 +312,7 @@ def run_b200(args):
         S.contract(a, b, tri)
         if ev is not None:
             ev[2].record()
-        out = S.tm2(z, tri, wd)
+        out = S.tm2(z, tri, wd, residual=residual)
         if ev is not None:
             ev[3].record()
         return out
@@ -302,37 +322,40 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
+    def timed(fn, n):
+        """n calls of fn between two events; nothing recorded in between."""
+        barrier()
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(n):
+            fn()
+        t1.record()
+        barrier()
+        return t0.elapsed_time(t1)
+
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
     sampler = ClockSampler(local_rank) if rank == 0 else None
+    # the timed region: exactly K steps, stages launched back to back
+    total_ms = timed(step, args.steps)
+    # the same K steps again with events between the stages (per-stage durations for the roofline)
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     barrier()
     for k in range(args.steps):
         step(evs[k])
     barrier()
-    clocks = sampler.stop() if sampler else None
-    total_ms = evs[0][0].elapsed_time(evs[-1][3])
+    staged_ms = evs[0][0].elapsed_time(evs[-1][3]) / args.steps
     stage_ms = [sum(e[i].elapsed_time(e[i + 1]) for e in evs) / args.steps for i in range(3)]
     st = read_status(dev)
     if st[0] != 0:
         raise SystemExit(f"bench.py: device status {st}: a bounded wait expired, timing is invalid")
 
     # the same step with the residual fused into the output stage (what the reference MODULE returns)
-    def step_res():
-        S.tm1(z, m, wd, a, b, outgoing=outgoing)
-        S.contract(a, b, tri)
-        return S.tm2(z, tri, wd, residual=z)
+    step_res = lambda: step(residual=z)
     for _ in range(3):
         step_res()
-    barrier()
-    r0, r1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    r0.record()
-    for _ in range(args.steps):
-        step_res()
-    r1.record()
-    barrier()
-    res_ms = r0.elapsed_time(r1) / args.steps
+    res_ms = timed(step_res, args.steps) / args.steps
 
     # the same step (residual fused) captured once in a CUDA graph and replayed: no host work per
     # step, which is how the reference's published table was measured (cudagraph=manual)
@@ -343,17 +366,36 @@ def run_b200(args):
         y_graph = step_res()
     for _ in range(3):
         graph.replay()
-    barrier()
-    g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    g0.record()
-    for _ in range(args.steps):
-        graph.replay()
-    g1.record()
-    barrier()
-    graph_ms = g0.elapsed_time(g1) / args.steps
+    graph_ms = timed(graph.replay, args.steps) / args.steps
     if not torch.equal(y_graph, step_res()):
         raise SystemExit("bench.py: the CUDA-graph replay and the eager step disagree")
     del graph, y_graph
+
+    # comparator: cuBLAS (torch.bmm) on the very planes the contraction reads — the kernel the
+    # reference's contraction lands on (module.py:439-442); same events, same warm-up
+    comparators = None
+    if a.pitch == N and rank == 0:
+        a3 = a.buf[: planes * a.plane_stride].view(planes, N, N)
+        b3 = b.buf[: planes * b.plane_stride].view(planes, N, N)
+        t3 = torch.empty(planes, N, N, dtype=torch.bfloat16, device=dev)
+        bmm = lambda: torch.bmm(a3, b3.transpose(1, 2), out=t3)
+        for _ in range(3):
+            bmm()
+        torch.cuda.synchronize(dev)
+        c0, c1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        c0.record()
+        for _ in range(args.steps):
+            bmm()
+        c1.record()
+        torch.cuda.synchronize(dev)
+        bmm_ms = c0.elapsed_time(c1) / args.steps
+        S.contract(a, b, tri)
+        own = S.planes_to_dense(tri)
+        comparators = {"cublas_bmm_ms": bmm_ms, "cublas_bmm_tflops": 2.0 * B * N ** 3 * c / (bmm_ms * 1e-3) / 1e12,
+                       "contract_ms": stage_ms[1],
+                       "contract_vs_cublas_rel_rms": float((own.float() - t3.float()).norm() / t3.float().norm()),
+                       "what": "torch.bmm(a, b^T) over the same B*c operand planes, device-timed back to back"}
+        del t3, own
 
     # end to end through the public module call, host buffers in and out.  Every step copies its
     # input from pinned host memory and its result back to pinned host memory; as a host that
@@ -416,10 +458,19 @@ def run_b200(args):
     if not torch.equal(out_host[0], out_host[1]):
         raise SystemExit("bench.py: the two end-to-end result buffers differ")
 
-    t = torch.tensor([total_ms, e2e_ms, res_ms, graph_ms] + stage_ms, device=dev, dtype=torch.float64)
+    clocks = sampler.stop() if sampler else None
+    t = torch.tensor([total_ms, e2e_ms, res_ms, graph_ms, staged_ms] + stage_ms, device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms, res_ms, graph_ms, *stage_ms = [float(v) for v in t.cpu()]
+    total_ms, e2e_ms, res_ms, graph_ms, staged_ms, *stage_ms = [float(v) for v in t.cpu()]
+
+    # BASELINE config 5 beside the replica line: rows sharded over the ranks, checked bit for bit
+    sharded = None
+    if world > 1:
+        del a, b, tri
+        torch.cuda.empty_cache()
+        sharded = measure_sharded_pair("n2048_pair_sharded", "auto", max(5, min(args.steps, 10)), 3, dev, rank, world,
+                                       check=True, one_gpu=True)
 
     if rank == 0:
         peaks = measured_peaks()
@@ -431,10 +482,11 @@ def run_b200(args):
                     "unit": "GB/s", "peak": peaks["hbm_gbs"]},
             "contract": {"ms": stage_ms[1], "bound": "tensor",
                          "achieved": 2.0 * B * N ** 3 * c / (stage_ms[1] * 1e-3) / 1e12, "unit": "TFLOP/s",
-                         "peak": peaks["bf16_tflops_sustained"]},
+                         "peak": peaks["bf16_tflops"], "frac_of_sustained": None},
             "tm2": {"ms": stage_ms[2], "bound": "hbm", "achieved": 3 * S_bytes / (stage_ms[2] * 1e-3) / 1e9,
                     "unit": "GB/s", "peak": peaks["hbm_gbs"]},
         }
+        stage_info["contract"]["frac_of_sustained"] = stage_info["contract"]["achieved"] / peaks["bf16_tflops_sustained"]
         for k, v in stage_info.items():
             v["frac"] = v["achieved"] / v["peak"]
             # bytes per launch, from the ncu capture of the c = 128 kernels (none for the other widths)
@@ -443,7 +495,10 @@ def run_b200(args):
         roof = dict(stage_info[dom])
         roof.update(kernel=dom, peak_source=peaks["source"],
                     algorithmic=(3 * S_bytes if roof["bound"] == "hbm" else 2.0 * B * N ** 3 * c),
-                    algorithmic_unit="bytes" if roof["bound"] == "hbm" else "flop")
+                    algorithmic_unit="bytes" if roof["bound"] == "hbm" else "flop",
+                    how="stage durations from the pass with CUDA events between the stage launches "
+                        f"({staged_ms:.4f} ms per step against {ms_per_step:.4f} ms without the events)")
+        config = workload_config(args.workload, B, N, c, "outgoing" if outgoing else "incoming", mask_kind)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "calls_per_s": world * 1e3 / ms_per_step,
@@ -455,55 +510,67 @@ def run_b200(args):
             "with_residual": {"ms_per_step": res_ms, "value": flops * world / (res_ms * 1e-3) / 1e12, "unit": UNIT},
             "cuda_graph_replay": {"ms_per_step": graph_ms, "value": flops * world / (graph_ms * 1e-3) / 1e12,
                                   "unit": UNIT, "what": "the with_residual step captured once and replayed"},
+            "staged_ms_per_step": staged_ms,
             "dtype": "bf16",
             "data": "synthetic (seeded randn pair tensor and weights, all-ones LayerNorm gamma)",
             "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
-            "config": {"workload": args.workload, "B": B, "N": N, "c": c,
-                       "direction": "outgoing" if outgoing else "incoming", "mask": mask_kind,
-                       "parallelism": "one block per GPU, no collective" if world > 1 else "single GPU",
-                       "l2": "working set 5 x %.0f MB per call exceeds the 126 MB L2; no flush" % (S_bytes / 1e6)},
+            "config": config,
+            "parallelism": "one block per GPU, no collective" if world > 1 else "single GPU",
             "gpu_launches": 3 * args.steps,
             "e2e": {"value": flops * world / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "ms_per_step": e2e_ms,
                     "serial_ms_per_step": e2e_serial_ms,
                     "how": "pinned host buffers, upload / block / download on three streams, two buffers each way",
                     "h2d_bytes_per_step": z_host.numel() * 2 + m_host.numel(),
                     "d2h_bytes_per_step": out_host[0].numel() * 2},
-            "roofline": roof, "stages": stage_info, "clocks": clocks,
+            "roofline": roof, "stages": stage_info, "comparators": comparators, "clocks": clocks,
         }
-        if world == 1 and not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_oracle_rate(B, N, c, outgoing, mask_kind)
+        if sharded is not None:
+            line["sharded_n2048"] = sharded
+        if not args.no_cpu_baseline:
+            # the oracle call also gives the reference output for this very input: parity of the
+            # benchmarked kernels (rank 0's pair tensor is seed 1, the oracle's)
+            base, y_ref = cpu_oracle_rate(B, N, c, outgoing, mask_kind, budget_s=25.0 if world == 1 else 5.0,
+                                          max_calls=3 if world == 1 else 1)
+            if world == 1:
+                line["cpu_baseline"] = base
+            y_dev = step().float().cpu()
+            line["parity_rel_rms"] = O.rel_rms(y_dev, y_ref.float())
+            line["parity_tolerance"] = 1e-2
+            if not line["parity_rel_rms"] <= 1e-2:
+                raise SystemExit(f"bench.py: parity against the oracle failed: rel-RMS {line['parity_rel_rms']:.3e}")
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-def run_sharded_pair(args):
-    """Outgoing block followed by an incoming block on its output, rows sharded over the ranks
-    with one NCCL exchange per block (all-gather b; incoming also all-to-all a)."""
+def measure_sharded_pair(workload, shard_mode, steps, warmup, dev, rank, world, *, check=True, one_gpu=False):
+    """Outgoing block followed by an incoming block on its output (independent weight sets, seeds 0
+    and 3), rows sharded over the ranks; the process group must already exist when world > 1.
+
+    ``shard_mode``: "rows" (NCCL all-gather of b, all-to-all of a for the incoming block),
+    "channels" (three NCCL all-to-alls per block), "peer" (no collective: the producing kernels store
+    into the consumer GPU's memory, two bounded flag barriers per block) or "auto" (peer where its
+    kernels exist for the problem, else channels).  ``check``: every rank also computes the unsharded
+    pair on its own GPU and compares its slab with it, bit for bit.  ``one_gpu``: that unsharded pair
+    is timed on rank 0 and the speed-up over it reported.  Returns the record on rank 0, None elsewhere."""
     import torch
     import torch.distributed as dist
     from oracle import trimul_oracle as O
-    from miniworld_engine_b200 import read_status, stages as S
+    from miniworld_engine_b200 import read_status, stages as S, trimul_forward
     from miniworld_engine_b200.sharded import ChannelShardPlan, PeerShardContext, ShardPlan, exchange
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py: no CUDA device; the b200 arm has no CPU path (use --impl reference)")
-    torch.cuda.set_device(local_rank)
-    dev = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    B, N, c, mask_kind = PAIR_WORKLOADS[args.workload]
+    B, N, c, mask_kind = PAIR_WORKLOADS[workload]
+    if shard_mode == "auto":
+        shard_mode = "peer" if (world > 1 and PeerShardContext.supported(B, N, c, torch.bfloat16, world)) else "channels"
     R = N // world
     g = torch.Generator().manual_seed(1)
-    z_slab = None
+    slabs = []
     for r in range(world):      # the same seeded tensor on every rank, generated slab by slab
-        blk = torch.randn(B, R, N, c, generator=g)
+        blk = torch.randn(B, R, N, c, generator=g).to(torch.bfloat16)
+        if r == rank or check:
+            slabs.append(blk.to(dev))
         if r == rank:
-            z_slab = blk.to(torch.bfloat16).to(dev)
-    del blk
+            z_slab = slabs[-1]
     m = O.make_token_mask(B, N, mask_kind).to(dev)
 
     def wdict(seed):
@@ -514,13 +581,11 @@ def run_sharded_pair(args):
                     ln_out_b=w.ln_out_bias.to(dev), w_gate=w.to_gate.to(dev), w_out=w.to_out.to(dev))
 
     w_out, w_in = wdict(0), wdict(3)
-    peer = args.shard_mode == "peer"
-    channels = args.shard_mode == "channels" or peer
+    peer = shard_mode == "peer"
+    channels = shard_mode == "channels" or peer
     Plan = ChannelShardPlan if channels else ShardPlan
     plans = {True: Plan(B, N, c, world, rank, True), False: Plan(B, N, c, world, rank, False)}
     if peer:
-        if world == 1:
-            dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1, device_id=dev)
         ctx = PeerShardContext(B, N, c, torch.bfloat16, dev)
         bufs = {k: {"a_recv": ctx._local["a"], "b_recv": ctx._local["b"], "tri_send": ctx._local["tri"],
                     "tri_recv": ctx._local["tri"]} for k in plans}
@@ -571,15 +636,15 @@ def run_sharded_pair(args):
         a_send, a_recv, b_full, tri_buf = bufs[outgoing]
         a_w, b_w = p.tm1_outputs(a_send, b_full)
         S.tm1(x, m, wd, a_w, b_w, outgoing=outgoing, row0=p.row0)
-        ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+        mark(ev)
         exchange(p, a_send, a_recv, b_full)
-        ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+        mark(ev)
         a_r, b_r = p.contract_operands(a_recv, b_full)
         tri = p.tri_spec(tri_buf)
         S.contract(a_r, b_r, tri)
-        ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+        mark(ev)
         y = S.tm2(x, tri, wd, row0=p.row0)
-        ev.append(torch.cuda.Event(enable_timing=True)); ev[-1].record()
+        mark(ev)
         return y
 
     def step():
@@ -594,53 +659,134 @@ def run_sharded_pair(args):
             dist.barrier()
         torch.cuda.synchronize(dev)
 
-    for _ in range(max(args.warmup, 3)):
+    for _ in range(max(warmup, 3)):
         step()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    sampler = ClockSampler(dev.index) if rank == 0 else None
     barrier()
-    all_ev = [step()[0] for _ in range(args.steps)]
+    all_ev = [step()[0] for _ in range(steps)]
     barrier()
     clocks = sampler.stop() if sampler else None
     total_ms = all_ev[0][0].elapsed_time(all_ev[-1][-1])
     names = (["tm1+scatter", "barrier+contract+scatter", "barrier", "tm2"] if peer else
              ["tm1", "a2a_in+contract", "a2a_out", "tm2"] if channels else ["tm1", "exchange", "contract", "tm2"])
-    stage_ms = [sum(e[i].elapsed_time(e[i + 1]) + e[i + 4].elapsed_time(e[i + 5]) for e in all_ev) / args.steps
+    stage_ms = [sum(e[i].elapsed_time(e[i + 1]) + e[i + 4].elapsed_time(e[i + 5]) for e in all_ev) / steps
                 for i in range(4)]
     if read_status(dev)[0] != 0:
         raise SystemExit(f"bench.py: device status {read_status(dev)}: timing is invalid")
-    t = torch.tensor([total_ms] + stage_ms, device=dev, dtype=torch.float64)
+
+    # every rank: the unsharded pair on its own GPU (same kernels through the public functional op)
+    parity, one_gpu_ms = None, None
+    if check:
+        y_slab = step()[1]
+        z_full = torch.cat(slabs, dim=1)
+        del slabs
+
+        def kw(wd):
+            return dict(ln_in_weight=wd["ln_in_w"], ln_in_bias=wd["ln_in_b"], w_left=wd["w_left"],
+                        w_left_gate=wd["w_left_gate"], w_right=wd["w_right"], w_right_gate=wd["w_right_gate"],
+                        ln_out_weight=wd["ln_out_w"], ln_out_bias=wd["ln_out_b"], w_gate=wd["w_gate"], w_out=wd["w_out"])
+
+        def whole():
+            y1 = trimul_forward(z_full, m, outgoing=True, **kw(w_out))
+            return trimul_forward(y1, m, outgoing=False, **kw(w_in))
+
+        y_full = whole()
+        mine = y_full[:, rank * R:(rank + 1) * R]
+        bit = bool(torch.equal(y_slab, mine))
+        rel = float((y_slab.float() - mine.float()).norm() / mine.float().norm())
+        del y_full, mine
+        if one_gpu:
+            torch.cuda.synchronize(dev)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(3):
+                whole()
+            e1.record()
+            torch.cuda.synchronize(dev)
+            one_gpu_ms = e0.elapsed_time(e1) / 3
+        flags = torch.tensor([1.0 if bit else 0.0, -rel], device=dev, dtype=torch.float64)
+        if world > 1:
+            dist.all_reduce(flags, op=dist.ReduceOp.MIN)
+        parity = {"bit_identical": bool(flags[0].item() == 1.0), "rel_rms_vs_unsharded": float(-flags[1].item()),
+                  "what": "every rank's output slab against the unsharded pair of blocks computed on the same GPU"}
+        if read_status(dev)[0] != 0:
+            raise SystemExit(f"bench.py: device status {read_status(dev)} after the unsharded check")
+        if not parity["rel_rms_vs_unsharded"] <= 1e-2:
+            raise SystemExit(f"bench.py: sharded result differs from the unsharded one: {parity}")
+
+    t = torch.tensor([total_ms] + stage_ms + [one_gpu_ms if (one_gpu_ms is not None and rank == 0) else 0.0],
+                     device=dev, dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, *stage_ms = [float(v) for v in t.cpu()]
+    total_ms, *stage_ms, one_gpu_ms = [float(v) for v in t.cpu()]
+    if rank != 0:
+        return None
+    peaks = measured_peaks()
+    flops = 2.0 * block_flops(B, N, c)
+    ms = total_ms / steps
+    gathered = (world - 1) * R * N * c * 2 * B          # bytes each rank receives per all-gather
+    a2a = (world - 1) * R * R * c * 2 * B               # and in the incoming all-to-all
+    if channels:                                        # three exchanges of (world-1)/world slabs
+        gathered, a2a = 3 * (world - 1) * R * N * (c // world) * 2 * B, 0
+    rec = {
+        "workload": workload, "ms_per_step": ms, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT,
+        "calls_per_s": 2e3 / ms, "steps": steps, "scaling": "strong", "shard_mode": shard_mode,
+        "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["bf16_tflops"],
+        "parallelism": (f"rows sharded over {world} GPU(s), contraction sharded over channel planes, "
+                        "exchanges done by the kernels' own stores into peer memory, two bounded flag barriers per block")
+        if peer else (f"rows sharded over {world} GPU(s), contraction sharded over channel planes, "
+                      "three all-to-alls per block") if channels else
+        (f"output rows sharded over {world} GPU(s), all-gather of b per block, "
+         "all-to-all of a for the incoming block"),
+        "nvlink_bytes_received_per_rank_per_step": 2 * gathered + a2a,
+        "stages": {n: {"ms": v} for n, v in zip(names, stage_ms)},
+        "gpu_launches": (10 if peer else 6) * steps,
+        "clocks": clocks,
+    }
+    if parity is not None:
+        rec["sharded_parity"] = parity
+    if one_gpu and one_gpu_ms > 0:
+        rec["one_gpu_ms_per_step"] = one_gpu_ms
+        rec["speedup_over_one_gpu"] = one_gpu_ms / ms
+    return rec
+
+
+def run_sharded_pair(args):
+    """BASELINE config 5 as the line's own workload (``--workload n2048_pair_sharded``)."""
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the b200 arm has no CPU path (use --impl reference)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    elif args.shard_mode == "peer":
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1, device_id=dev)
+    rec = measure_sharded_pair(args.workload, args.shard_mode, args.steps, args.warmup, dev, rank, world,
+                               check=not args.no_check, one_gpu=world > 1)
     if rank == 0:
-        peaks = measured_peaks()
-        flops = 2.0 * block_flops(B, N, c)
-        ms = total_ms / args.steps
-        gathered = (world - 1) * R * N * c * 2 * B          # bytes each rank receives per all-gather
-        a2a = (world - 1) * R * R * c * 2 * B               # and in the incoming all-to-all
-        if channels:                                        # three all-to-alls of (world-1)/world slabs
-            gathered, a2a = 3 * (world - 1) * R * N * (c // world) * 2 * B, 0
+        B, N, c, mask_kind = PAIR_WORKLOADS[args.workload]
         line = {
-            "metric": METRIC, "value": flops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms,
-            "calls_per_s": 2e3 / ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic (seeded randn pair tensor and weights)",
-            "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / world / peaks["bf16_tflops"],
-            "config": {"workload": args.workload, "B": B, "N": N, "c": c, "direction": "outgoing then incoming",
-                       "mask": mask_kind, "parallelism": (f"rows sharded over {world} GPU(s), contraction sharded over channel planes, "
-                                       "exchanges done by the kernels' own TMA stores into peer memory, two barriers per block")
-                       if peer else (f"rows sharded over {world} GPU(s), contraction sharded over channel planes, "
-                                       "three all-to-alls per block") if channels else
-                       (f"output rows sharded over {world} GPU(s), all-gather of b per block, "
-                        "all-to-all of a for the incoming block"),
-                       "nvlink_bytes_received_per_rank_per_step": 2 * gathered + a2a},
-            "gpu_launches": 6 * args.steps,
-            "stages": {n: {"ms": v} for n, v in zip(names, stage_ms)},
-            "clocks": clocks,
+            "metric": METRIC, "value": rec["value"], "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": rec["ms_per_step"], "calls_per_s": rec["calls_per_s"],
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (seeded randn pair tensor and weights)",
+            "frac_of_bf16_peak": rec["frac_of_bf16_peak"],
+            "config": workload_config(args.workload, B, N, c, "outgoing then incoming", mask_kind),
+            "parallelism": rec["parallelism"],
         }
+        for k in ("shard_mode", "nvlink_bytes_received_per_rank_per_step", "gpu_launches", "stages", "clocks",
+                  "sharded_parity", "one_gpu_ms_per_step", "speedup_over_one_gpu"):
+            if k in rec:
+                line[k] = rec[k]
         print(json.dumps(line), flush=True)
-    if world > 1 or peer:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 
@@ -732,10 +878,9 @@ def run_bidirectional(args):
         "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic (seeded randn pair tensor and weights, all-ones LayerNorm gamma)",
         "frac_of_bf16_peak": flops / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
-        "config": {"workload": args.workload, "B": B, "N": N, "c": d, "c_hidden": 2 * h,
-                   "direction": "bidirectional (outgoing + incoming halves), residual added", "mask": mask_kind,
-                   "parallelism": "single GPU",
-                   "l2": "working set exceeds the 126 MB L2 for N >= 512; no flush"},
+        "config": dict(workload_config(args.workload, B, N, d, "bidirectional (outgoing + incoming halves), residual added",
+                                       mask_kind), c_hidden=2 * h),
+        "parallelism": "single GPU",
         "gpu_launches": 4 * args.steps,
         "roofline": dict(stages[dom], kernel=dom, peak_source=peaks["source"], traffic=None),
         "stages": stages, "clocks": clocks,
@@ -751,8 +896,10 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="n768_outgoing", choices=sorted(WORKLOADS) + sorted(PAIR_WORKLOADS) + sorted(BIDIR_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--shard-mode", default="rows", choices=["rows", "channels", "peer"],
+    ap.add_argument("--shard-mode", default="auto", choices=["auto", "rows", "channels", "peer"],
                     help="exchange pattern of the *_pair_sharded workloads")
+    ap.add_argument("--no-check", action="store_true",
+                    help="*_pair_sharded: skip the comparison with the unsharded result")
     args = ap.parse_args()
     if args.impl == "reference":
         args.steps = 3 if args.steps is None else args.steps

@@ -40,7 +40,7 @@
 extern "C" {
 #endif
 
-#define TRIMUL_B200_ABI_VERSION 1
+#define TRIMUL_B200_ABI_VERSION 2
 
 /* error codes */
 #define TRIMUL_OK                 0
@@ -69,17 +69,20 @@ extern "C" {
                                          (cross-checking aid; same layouts, same rounding points)   */
 #define TRIMUL_FLAG_SINGLE_CTA_CONTRACT 2u /* contraction on lone CTAs (128x256 tiles) instead of CTA
                                          pairs (256x256 tiles, cta_group::2); cross-checking aid    */
-#define TRIMUL_FLAG_PAIR_STAGE1 4u    /* stage 1 on CTA pairs (each CTA holds one side's weights and
-                                         normalises half of every tile); same results, currently
-                                         slower than the default lone-CTA kernel                     */
-#define TRIMUL_FLAG_FOLDED_STAGE1 8u   /* stage 1 with the input LayerNorm folded into the projection
-                                         weights (held in tensor memory) and applied per position
-                                         in the epilogue; rounds W*gamma instead of LN(x) to bf16;
-                                         currently slower than the default kernel                   */
+#define TRIMUL_FLAG_SMEM_STORE_STAGE1 4u /* stage 1 in its transposed form (D[channel][position], 16
+                                         narrower UMMAs per side, results staged in shared memory
+                                         and TMA-stored) instead of the default kernel (8 UMMAs of
+                                         full width per side, thread = position, direct global
+                                         stores); cross-checking aid, slower                        */
 #define TRIMUL_FLAG_INPLACE_NORM_STAGE3 16u /* stage 3 with both LayerNorms applied in place in shared
                                          memory before the projections (rounds LN(x) to bf16 like the
                                          reference) instead of the default kernel, which folds them
                                          into the weights; cross-checking aid, slower               */
+#define TRIMUL_FLAG_SERIAL_LAUNCH 32u  /* launch the tensor-core stages without programmatic dependent
+                                         launch.  By default a stage may be scheduled while its
+                                         predecessor in the stream drains and waits on the device
+                                         (griddepcontrol.wait) before it touches global memory; the
+                                         results are the same either way                            */
 
 /*
  * Problem description.  `rows`/`row0` select a horizontal slab of z for the row-sharded
@@ -110,6 +113,16 @@ typedef struct trimul_desc {
     uint32_t flags;          /* TRIMUL_FLAG_*                                                       */
     int32_t  rows;           /* z rows in this call (N for the unsharded block)                     */
     int32_t  row0;           /* global index of the first of them                                   */
+    const void* drop_scale;  /* optional (NULL = none): the reference module's row-broadcast dropout
+                                scale, a DEVICE pointer to [B, 1, N, c] values of the activation
+                                dtype, 16-byte aligned (module.py:332-337).  The last stage multiplies
+                                the block output by it before the residual is added, as the
+                                reference's gate kernel does (kernels/trimul_inproj/triton/
+                                gate_elem.py:41-78).  Not available together with a residual that is
+                                a different tensor from z on the tensor-core path
+                                (TRIMUL_E_UNSUPPORTED).  Callers built against the descriptor
+                                without this field pass the shorter struct_bytes and are served
+                                as before                                                            */
 } trimul_desc;
 
 /* Parameters, named as in reference.py:51-59.  Linear weights have the activation dtype;
@@ -214,7 +227,7 @@ int trimul_b200_contract(int32_t dtype, uint32_t flags, int32_t planes,
  * access); all destinations of one call share one geometry and only differ in `base`.
  * The calls order nothing between GPUs: the caller puts a cross-GPU barrier between a scattering
  * stage and the stage that consumes what other GPUs scattered.  1 <= n_dest <= 8.  Only the
- * tensor-core kernels scatter: bf16, c = 128, P a multiple of 8 that divides or is a multiple of
+ * tensor-core kernels scatter: bf16, c = 128, P a multiple of 16 that divides or is a multiple of
  * 128, R a multiple of 128; anything else returns TRIMUL_E_UNSUPPORTED and the caller falls back
  * to the plain stages plus a collective.
  */
@@ -224,6 +237,29 @@ int trimul_b200_tm1_scatter(const trimul_desc* desc, const void* z, const uint8_
 int trimul_b200_contract_scatter(int32_t dtype, uint32_t flags, int32_t planes,
                                  const trimul_planes* a, const trimul_planes* b, int32_t n_dest,
                                  const trimul_planes* tri_dest, void* stream, int32_t* status);
+
+/*
+ * Barrier over the `world` GPUs of one node for the scattering stages above, enqueued on `stream`.
+ * (No counterpart in the reference, which has no multi-GPU code.)  peer_flags[r], r < world, is
+ * the DEVICE address — valid on this GPU, i.e. peer-mapped for r != rank — of rank r's flag array:
+ * `world` int32 words, zero before the first barrier.  `epoch` numbers the barriers 1, 2, 3, ...
+ * and must be the same on every rank for the same barrier.  The kernel stores `epoch` into word
+ * [rank] of every rank's array (release, system scope) and waits until every word of its own array
+ * has reached `epoch` (acquire).  The wait is bounded by `timeout_us`: when it runs out the kernel
+ * writes {TRIMUL_E_DEVICE_TIMEOUT, 9, missing rank, epoch} to `status` and returns, so the caller —
+ * who reads the status words after synchronising — learns that a peer never arrived instead of
+ * hanging.  Plain peer loads and stores; no multicast.
+ */
+int trimul_b200_peer_barrier(int32_t rank, int32_t world, int32_t* const* peer_flags, uint32_t epoch,
+                             uint32_t timeout_us, void* stream, int32_t* status);
+
+/*
+ * Self-test of the bounded device-side waits.  (No counterpart in the reference.)  Launches one
+ * small kernel that waits, with a limit of `timeout_us`, on a barrier nothing will ever complete:
+ * the wait gives up, the kernel writes {TRIMUL_E_DEVICE_TIMEOUT, 10, 0, 1077} to `status` and returns
+ * normally; the context stays usable.  `status` must be non-NULL and zeroed.
+ */
+int trimul_b200_selftest_expiring_wait(uint32_t timeout_us, void* stream, int32_t* status);
 
 /*
  * Stage 3: LayerNorm_out over the channels of tri, the output projection, the output gate

@@ -12,7 +12,7 @@ import os
 PKG_DIR = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(PKG_DIR, "libtrimul_b200.so")
 
-ABI_VERSION = 1
+ABI_VERSION = 2
 
 OK = 0
 E_INVALID, E_UNSUPPORTED, E_WORKSPACE, E_CUDA, E_DEVICE_TIMEOUT = -1, -2, -3, -4, -5
@@ -23,9 +23,9 @@ OUTGOING, INCOMING = 0, 1
 MASK_NONE, MASK_TOKEN, MASK_PAIR = 0, 1, 2
 FLAG_PLAIN_KERNELS = 1
 FLAG_SINGLE_CTA_CONTRACT = 2
-FLAG_PAIR_STAGE1 = 4
-FLAG_FOLDED_STAGE1 = 8
+FLAG_SMEM_STORE_STAGE1 = 4
 FLAG_INPLACE_NORM_STAGE3 = 16
+FLAG_SERIAL_LAUNCH = 32
 
 EXPORTED_SYMBOLS = (
     "trimul_b200_abi_version",
@@ -40,6 +40,8 @@ EXPORTED_SYMBOLS = (
     "trimul_b200_bidir_workspace_bytes",
     "trimul_b200_forward_bidir",
     "trimul_b200_contract_scatter",
+    "trimul_b200_peer_barrier",
+    "trimul_b200_selftest_expiring_wait",
 )
 
 
@@ -51,6 +53,7 @@ class Desc(C.Structure):
         ("eps_in", C.c_float), ("eps_out", C.c_float),
         ("flags", C.c_uint32),
         ("rows", C.c_int32), ("row0", C.c_int32),
+        ("drop_scale", C.c_void_p),
     ]
 
 
@@ -111,6 +114,11 @@ def load():
     lib.trimul_b200_forward_static.restype = C.c_int
     lib.trimul_b200_forward_static.argtypes = [PD, C.c_void_p, C.c_void_p, PW, C.c_void_p, C.c_void_p,
                                                C.c_void_p, C.c_void_p]
+    lib.trimul_b200_peer_barrier.restype = C.c_int
+    lib.trimul_b200_peer_barrier.argtypes = [C.c_int32, C.c_int32, C.POINTER(C.c_void_p), C.c_uint32, C.c_uint32,
+                                             C.c_void_p, C.c_void_p]
+    lib.trimul_b200_selftest_expiring_wait.restype = C.c_int
+    lib.trimul_b200_selftest_expiring_wait.argtypes = [C.c_uint32, C.c_void_p, C.c_void_p]
     if lib.trimul_b200_abi_version() != ABI_VERSION:
         raise TrimulLibraryError(
             f"ABI mismatch: library {lib.trimul_b200_abi_version()}, binding {ABI_VERSION}; rebuild the library")
@@ -138,6 +146,7 @@ def check(code: int, what: str) -> None:
 
 
 def make_desc(B, N, c, *, dtype, direction, mask_kind=MASK_NONE, eps_in=1e-5, eps_out=1e-5,
-              flags=0, rows=None, row0=0, c_hidden=None) -> Desc:
+              flags=0, rows=None, row0=0, c_hidden=None, drop_scale=None) -> Desc:
+    """``drop_scale`` is a device address (``tensor.data_ptr()``) or None."""
     return Desc(C.sizeof(Desc), B, N, c, c if c_hidden is None else c_hidden, dtype, direction, mask_kind,
-                eps_in, eps_out, flags, N if rows is None else rows, row0)
+                eps_in, eps_out, flags, N if rows is None else rows, row0, drop_scale)

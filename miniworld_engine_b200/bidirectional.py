@@ -35,14 +35,14 @@ import torch
 import torch.nn as nn
 
 from . import _lib
-from .functional import _dtype_code, _mask_bytes, _pinned_weights, _require_cuda, _status_words, _workspace
-from .module import PinnedLayerNormParams
+from .functional import (_dtype_code, _mask_bytes, _pinned_weights, _require_cuda, _require_no_grad,
+                         _status_words, _workspace)
+from .module import PinnedLayerNormParams, _lecun_trunc_normal_
 
 __all__ = ["bidir_trimul_forward", "bidirectional_triangle_multiplicative_update_b200",
            "BidirectionalTriangleMultiplicationB200"]
 
 
-@torch.no_grad()
 def bidir_trimul_forward(
     x: torch.Tensor,
     mask: torch.Tensor | None,
@@ -72,6 +72,8 @@ def bidir_trimul_forward(
         raise ValueError(f"w_out must be [{d}, {h2}] and w_gate [{d}, {d}]")
     if mask is not None and tuple(mask.shape) != (B, N):
         raise ValueError(f"mask must be [B, N], got {tuple(mask.shape)}")
+    _require_no_grad("bidir_trimul_forward", x, ln_in_weight, ln_in_bias, w_left, w_left_gate, w_right, w_right_gate,
+                     ln_out_weight, ln_out_bias, w_gate, w_out)
     _require_cuda(x, "x")
     x = x.detach().contiguous()
     mask_kind, mask_u8 = _lib.MASK_NONE, None
@@ -150,7 +152,11 @@ class BidirectionalTriangleMultiplicationB200(nn.Module):
         self.ln_out = PinnedLayerNormParams(d2)
         self.to_gate = nn.Linear(d_pair, d_pair, bias=False)
         self.to_out = nn.Linear(d2, d_pair, bias=False)
-        with torch.no_grad():      # the reference zero-initialises the gates and to_out (bidirectional.py:78-84)
+        with torch.no_grad():
+            # the reference's "default" (LeCun truncated normal) init for the two projections and zeros
+            # for the gates and to_out (bidirectional.py:77-84)
+            _lecun_trunc_normal_(self.to_left.weight)
+            _lecun_trunc_normal_(self.to_right.weight)
             for lin in (self.to_left_gate, self.to_right_gate, self.to_gate, self.to_out):
                 lin.weight.zero_()
 

@@ -2,7 +2,7 @@
 
 The reference picks a backend through ``ImplementationType`` in the module constructors
 (``src/miniworld_engine/modules/triangle_multiplication/module.py:94-131``); a patched checkout
-adds a member for this backend.  Where the reference cannot be patched,
+adds a member for this backend (the patch ships under ``integration/``).  Where the reference cannot be patched,
 ``install`` does the equivalent on a model that has already been built: every
 ``TriangleMultiplication`` / ``BidirectionalTriangleMultiplication`` submodule is replaced by
 ``TriangleMultiplicationB200`` / ``BidirectionalTriangleMultiplicationB200`` holding the same

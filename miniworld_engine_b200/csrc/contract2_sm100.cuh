@@ -84,6 +84,9 @@ contract2_sm100_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_con
     cluster_sync_all();          // both CTAs' barriers are initialised before anyone signals the peer
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done without touching global memory: now wait for the producer of a and b
+    griddep_wait();
+    griddep_launch_dependents();
 
     // pair tiles: 256 rows x 256 columns of one plane
     const int tiles_m = (p.rows_a + 255) / 256;

@@ -185,6 +185,7 @@ struct PlainTm2Params {
     float eps_in, eps_out;
     const void *w_gate, *w_out;
     PlaneView tri;
+    const void* drop_scale;   // [B, 1, N, c] row-broadcast multiplier of the block output, or null
 };
 
 // grid: B * rows * ceil(N / kPlainPos); block kPlainThreads
@@ -228,6 +229,8 @@ plain_tm2_kernel(const T* __restrict__ z, T* __restrict__ out, const T* __restri
         }
         for (int q = 0; q < npos; ++q) {
             float y = sigmoid_ref(g[q]) * v[q];
+            if (p.drop_scale != nullptr)   // applied to the rounded block output, as out * scale would
+                y = round_t<T>(y) * load_f<T>((const T*)p.drop_scale + ((long long)b * p.N + s0 + q) * c + o);
             if (residual != nullptr) y = round_t<T>(y) + load_f<T>(residual + (pos0 + q) * c + o);
             out[(pos0 + q) * c + o] = store_t<T>(y);
         }

@@ -115,12 +115,22 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint64_t* bar, uint32_t parity
     return done;
 }
 
-// Time budget of one wait.  After a short spin each poll sleeps, and every 64th poll compares
-// the global nanosecond timer with the moment the slow path was entered.  One second is far
-// beyond any legitimate wait in these kernels and short enough that a protocol bug returns
-// control to the host with the context intact.
-constexpr uint32_t kWaitSpin = 4096u;
-constexpr uint64_t kWaitNs   = 1000ull * 1000ull * 1000ull;
+// Time budget of one wait.  A polling thread costs issue slots that the working warps of the same
+// scheduler need (the suspend hint does not park it for long): after a handful of immediate
+// polls each further poll is preceded by a short sleep, and every 64th poll compares the global
+// nanosecond timer with the moment the slow path was entered.  One second is far beyond any
+// legitimate wait in these kernels and short enough that a protocol bug returns control to the
+// host with the context intact.  For the same reason a group of warps never polls with more
+// than one thread (group_wait below).
+#ifndef TRIMUL_HOT_POLLS
+#define TRIMUL_HOT_POLLS 8
+#endif
+#ifndef TRIMUL_POLL_SLEEP_NS
+#define TRIMUL_POLL_SLEEP_NS 32
+#endif
+constexpr uint32_t kHotPolls = TRIMUL_HOT_POLLS;
+constexpr uint32_t kPollSleepNs = TRIMUL_POLL_SLEEP_NS;
+constexpr uint64_t kWaitNs = 1000ull * 1000ull * 1000ull;
 
 __device__ __forceinline__ uint64_t global_timer_ns() {
     uint64_t t;
@@ -134,20 +144,19 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // kOutOfLine = true keeps the polling loop out of line.  Kernels that wait in dozens of places
 // and have large epilogues can outgrow the SM's instruction cache when the loop is inlined
 // everywhere (instruction-cache hit rates of 60-90 % and the instruction-fetch path near its
-// peak were measured); for them the call is cheaper than the misses.  Kernels whose code fits
-// keep the inlined loop, which measured 5-10 % faster there.
+// peak were measured); for them the call is cheaper than the misses.
 __device__ __forceinline__ bool mbar_wait_loop(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                               int32_t* status, int stage, int detail) {
+                                               int32_t* status, int stage, int detail, uint64_t limit_ns = kWaitNs) {
     uint64_t t0 = 0;
     for (uint32_t it = 0;; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
-        if (it >= kWaitSpin) {
-            __nanosleep(64);
+        if (it >= kHotPolls) {
+            __nanosleep(kPollSleepNs);
             if ((it & 63u) == 0u) {
                 if (*abort_flag != 0) return false;
                 const uint64_t now = global_timer_ns();
                 if (t0 == 0) t0 = now;
-                else if (now - t0 > kWaitNs) break;
+                else if (now - t0 > limit_ns) break;
             }
         }
     }
@@ -156,17 +165,17 @@ __device__ __forceinline__ bool mbar_wait_loop(uint64_t* bar, uint32_t parity, v
     return false;
 }
 __device__ __noinline__ bool mbar_wait_slow(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                            int32_t* status, int stage, int detail) {
-    return mbar_wait_loop(bar, parity, abort_flag, status, stage, detail);
+                                            int32_t* status, int stage, int detail, uint64_t limit_ns) {
+    return mbar_wait_loop(bar, parity, abort_flag, status, stage, detail, limit_ns);
 }
 template <bool kOutOfLine = false>
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int32_t* status, int stage, int detail) {
+                                          int32_t* status, int stage, int detail, uint64_t limit_ns = kWaitNs) {
     if (kOutOfLine) {
         if (mbar_try_wait(bar, parity)) return true;
-        return mbar_wait_slow(bar, parity, abort_flag, status, stage, detail);
+        return mbar_wait_slow(bar, parity, abort_flag, status, stage, detail, limit_ns);
     }
-    return mbar_wait_loop(bar, parity, abort_flag, status, stage, detail);
+    return mbar_wait_loop(bar, parity, abort_flag, status, stage, detail, limit_ns);
 }
 
 // Collective AND over the `nthreads` threads that share named barrier `id`: every one of them
@@ -191,9 +200,10 @@ __device__ __forceinline__ bool named_barrier_all(int id, int nthreads, bool ok)
 // poller's verdict and its view of memory to every thread of the group.
 template <bool kOutOfLine = false>
 __device__ __forceinline__ bool group_wait(uint64_t* bar, uint32_t parity, bool poller, int bar_id, int nthreads,
-                                           volatile int* abort_flag, int32_t* status, int stage, int detail) {
+                                           volatile int* abort_flag, int32_t* status, int stage, int detail,
+                                           uint64_t limit_ns = kWaitNs) {
     bool ok = true;
-    if (poller) ok = mbar_wait<kOutOfLine>(bar, parity, abort_flag, status, stage, detail);
+    if (poller) ok = mbar_wait<kOutOfLine>(bar, parity, abort_flag, status, stage, detail, limit_ns);
     return named_barrier_all(bar_id, nthreads, ok);
 }
 
@@ -344,6 +354,46 @@ __device__ __forceinline__ void umma_bf16_ss(uint32_t tmem_d, uint64_t desc_a, u
         : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]^T: the A operand is read from tensor memory, 128 lanes (rows) x 16
+// bf16 per UMMA stored two per 32-bit column (8 columns per K step of 16).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                             uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// registers -> TMEM: thread t of the warp writes 16 consecutive 32-bit columns of lane
+// (warp_id % 4) * 32 + t
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------
+// Programmatic dependent launch.  A kernel launched with the programmatic-stream-serialization
+// attribute may start while the kernel before it in the stream is still running; nothing the
+// predecessor wrote may be read (and nothing it reads may be overwritten) before
+// griddep_wait() returns, which happens once the predecessor has completed and its memory
+// operations are visible.  Without the launch attribute both instructions are no-ops.
+// griddep_launch_dependents() lets the NEXT kernel in the stream be scheduled as soon as every
+// CTA of this grid has executed it (its CTAs then take over SMs as this grid's CTAs retire).
+// ---------------------------------------------------------------------------------------
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------------------
 // TMEM -> registers: 32 lanes x 32 consecutive fp32 columns; thread t of the warp gets lane
 // (warp_id % 4) * 32 + t.  The address carries the lane in bits [16,32) and the column in [0,16).
@@ -486,6 +536,11 @@ __device__ __forceinline__ void f2_unpack(f32x2 v, float& lo, float& hi) {
 __device__ __forceinline__ f32x2 f2_fma(f32x2 a, f32x2 b, f32x2 c) {
     f32x2 r;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ f32x2 f2_mul(f32x2 a, f32x2 b) {
+    f32x2 r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
     return r;
 }
 __device__ __forceinline__ f32x2 f2_add(f32x2 a, f32x2 b) {
@@ -656,6 +711,65 @@ __device__ __forceinline__ void ln_row_inplace(uint8_t* tile, int sub_bytes, int
             if (zero_row) o = make_uint4(0u, 0u, 0u, 0u);
             *p = o;
         }
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// LayerNorm of 4 * kIters consecutive rows (first row `row0`, a multiple of 8) of a
+// [128 rows][128 channels] tile by ONE WARP, in place, same tile layout as above.  Eight lanes
+// share a row: lane l works on row row0 + 4 i + (l >> 3) in iteration i and owns 16-byte chunk
+// l & 7 of both sub-tiles, i.e. channels [8 j, 8 j + 8) and [64 + 8 j, 64 + 8 j + 8), j = l & 7.
+// Every value is read from shared memory ONCE and stays in registers between the statistics and
+// the normalisation; gamma and beta of the lane's 16 channels live in registers (`gb`: gamma
+// pairs [0,8), beta pairs [8,16)), so no affine vector is fetched per row; the row sums are
+// combined by a three-step butterfly over the eight lanes.  A quarter warp reads or writes one
+// whole 128-byte swizzled row segment: conflict-free.  Bit i of `zero_bits` set -> the lane's
+// row of iteration i is a masked position and is written as zeros.
+// ---------------------------------------------------------------------------------------
+template <int kIters>
+__device__ __forceinline__ void ln_rows_warp(uint8_t* tile, int sub_bytes, int row0, int lane, const f32x2 (&gb)[16],
+                                             float eps, uint32_t zero_bits) {
+    const int rr = lane >> 3;
+    const uint32_t j = (uint32_t)lane & 7u;
+#pragma unroll 2
+    for (int i = 0; i < kIters; ++i) {
+        const int r = row0 + 4 * i + rr;
+        const uint32_t off = (uint32_t)r * 128u + ((j ^ ((uint32_t)r & 7u)) << 4);
+        uint4* p0 = reinterpret_cast<uint4*>(tile + off);
+        uint4* p1 = reinterpret_cast<uint4*>(tile + sub_bytes + off);
+        const uint4 v0 = *p0, v1 = *p1;
+        // common shift of the row: its channel 0 (held by the lane with j == 0)
+        const float shift = bf16_lo(__shfl_sync(0xffffffffu, v0.x, lane & 24));
+        const f32x2 ns = f2_pack(-shift, -shift);
+        f32x2 d[8];
+        d[0] = f2_add(f2_from_bf16x2(v0.x), ns); d[1] = f2_add(f2_from_bf16x2(v0.y), ns);
+        d[2] = f2_add(f2_from_bf16x2(v0.z), ns); d[3] = f2_add(f2_from_bf16x2(v0.w), ns);
+        d[4] = f2_add(f2_from_bf16x2(v1.x), ns); d[5] = f2_add(f2_from_bf16x2(v1.y), ns);
+        d[6] = f2_add(f2_from_bf16x2(v1.z), ns); d[7] = f2_add(f2_from_bf16x2(v1.w), ns);
+        const f32x2 sa = f2_add(f2_add(d[0], d[1]), f2_add(d[2], d[3]));
+        const f32x2 sb = f2_add(f2_add(d[4], d[5]), f2_add(d[6], d[7]));
+        const f32x2 qa = f2_fma(d[0], d[0], f2_fma(d[1], d[1], f2_fma(d[2], d[2], f2_fma(d[3], d[3], 0ull))));
+        const f32x2 qb = f2_fma(d[4], d[4], f2_fma(d[5], d[5], f2_fma(d[6], d[6], f2_fma(d[7], d[7], 0ull))));
+        float t1 = f2_hsum(f2_add(sa, sb)), t2 = f2_hsum(f2_add(qa, qb));
+#pragma unroll
+        for (int o = 4; o >= 1; o >>= 1) {
+            t1 += __shfl_xor_sync(0xffffffffu, t1, o);
+            t2 += __shfl_xor_sync(0xffffffffu, t2, o);
+        }
+        const float m1 = t1 * (1.0f / 128.0f);
+        const float var = fmaxf(fmaf(-m1, m1, t2 * (1.0f / 128.0f)), 0.f);
+        const float rstd = rsqrtf(var + eps);
+        const float nm = -m1 * rstd;                       // y = d * rstd + nm
+        const f32x2 r2 = f2_pack(rstd, rstd), n2 = f2_pack(nm, nm);
+        uint32_t o[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = f2_to_bf16x2(f2_fma(f2_fma(d[k], r2, n2), gb[k], gb[8 + k]));
+        if ((zero_bits >> i) & 1u) {
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = 0u;
+        }
+        *p0 = make_uint4(o[0], o[1], o[2], o[3]);
+        *p1 = make_uint4(o[4], o[5], o[6], o[7]);
     }
 }
 

@@ -1,0 +1,343 @@
+// Stage 1 of the block in its TRANSPOSED form (the previous default), kept as a cross-check
+// (TRIMUL_FLAG_SMEM_STORE_STAGE1): D^T[channel][position] = W[channel][:] . x_n[position][:], the
+// weights are the UMMA A operand, a TMEM lane is an output channel, so an epilogue thread owns a
+// run of consecutive positions of one channel, which it writes to a swizzled staging box that is
+// TMA-stored into the channel-major destination.  16 UMMAs of 128 x 128 x 16 per side and tile and a
+// two-deep z ring (the staging boxes and per-row LayerNorm constants take the rest of the shared
+// memory).  Same arithmetic and rounding points as tm1_sm100.cuh; the LayerNorm sums a row in a
+// different order, so the two agree to the last bf16 bit of a few elements, not bit for bit.
+//
+// Persistent kernel, one CTA per SM, 576 threads, 128-position tiles:
+//   warp 0        TMA producer: the four weight matrices once, then z tiles into a 2-stage ring
+//   warp 1        UMMA issuer: per tile, left pair (proj, gate) then right pair, 128x128x16 each,
+//                 into four 128-column TMEM accumulators
+//   warps 2..9    LayerNorm: two groups of four warps on alternate tiles, one thread per position
+//   warps 10..13  epilogue of the left side, warps 14..17 of the right side
+#pragma once
+
+#include "tm1_sm100.cuh"
+
+namespace trimul {
+
+constexpr int kS1Threads = 576;
+constexpr int kS1LnThreads = 256;      // warps 2..9
+constexpr int kS1EpiThreads = 128;     // per side
+constexpr int kS1WBytes = 8 * kT1SubTile;         // 4 matrices x 2 K halves
+constexpr int kS1XStages = 2;
+constexpr int kS1StagingBytes = 2 * kT1SubTile;   // one [128 channels][64 positions] store box per side
+constexpr int kS1OffX = kS1WBytes;
+constexpr int kS1OffStaging = kS1OffX + kS1XStages * kT1XBytes;
+constexpr int kS1OffAffine = kS1OffStaging + kS1StagingBytes;      // gamma[128], beta[128] fp32
+constexpr int kS1OffBars = kS1OffAffine + 2 * kT1C * 4;
+constexpr int kS1SmemBytes = kS1OffBars + 192;
+constexpr int kS1LnBarrier = 2;
+constexpr int kS1EpiBarrier = 3;       // 3: left side, 4: right side
+constexpr int kS1LnBarrier2 = 5;       // second LayerNorm group
+
+template <bool kScatter>
+__global__ void __launch_bounds__(kS1Threads, 1)
+tm1_staged_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWl,
+                 const __grid_constant__ CUtensorMap tmWlg, const __grid_constant__ CUtensorMap tmWr,
+                 const __grid_constant__ CUtensorMap tmWrg, const __grid_constant__ CUtensorMap tmA,
+                 const __grid_constant__ CUtensorMap tmB, const Tm1Params p,
+                 const __grid_constant__ ScatterMaps scA, const __grid_constant__ ScatterMaps scB) {
+    extern __shared__ __align__(1024) uint8_t smem[];
+    if ((smem_u32(smem) & 1023u) != 0u) {
+        if (threadIdx.x == 0) report_timeout(p.status, kStageIdTm1, 900);
+        return;
+    }
+    uint8_t* sW = smem;
+    uint8_t* sX = smem + kS1OffX;
+    uint8_t* sOut = smem + kS1OffStaging;
+    float* sGamma = reinterpret_cast<float*>(smem + kS1OffAffine);
+    float* sBeta = sGamma + kT1C;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kS1OffBars);
+    uint64_t* w_full = bars;            // weights landed
+    uint64_t* x_full = bars + 1;        // [2] z tile landed
+    uint64_t* xn_ready = bars + 3;      // [2] tile normalised (256 arrivals)
+    uint64_t* x_empty = bars + 5;       // [2] UMMAs that read the tile retired
+    uint64_t* acc_full = bars + 7;      // [2] side's accumulators complete
+    uint64_t* acc_empty = bars + 9;     // [2] side's accumulators drained (4 arrivals)
+    uint64_t* w_ready = bars + 11;      // weights halved (512 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 12);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    if (threadIdx.x == 0) {
+        mbar_init(w_full, 1);
+        mbar_init(w_ready, kS1LnThreads + 2 * kS1EpiThreads);
+        for (int s = 0; s < 2; ++s) {
+            mbar_init(&x_full[s], 1);
+            mbar_init(&xn_ready[s], kS1LnThreads / 2);
+            mbar_init(&x_empty[s], 1);
+            mbar_init(&acc_full[s], 1);
+            mbar_init(&acc_empty[s], 4);
+        }
+        *abort_flag = 0;
+        fence_mbarrier_init();
+        tma_prefetch_desc(&tmZ);
+        tma_prefetch_desc(&tmA);
+        tma_prefetch_desc(&tmB);
+    }
+    if (threadIdx.x >= 64 && threadIdx.x < 64 + kT1C) {
+        sGamma[threadIdx.x - 64] = p.gamma[threadIdx.x - 64];
+        sBeta[threadIdx.x - 64] = p.beta[threadIdx.x - 64];
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, 512);
+        tmem_relinquish();
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp >= 2) {
+        // every worker thread: halve its share of the weights once they have landed
+        if (mbar_wait(w_full, 0, abort_flag, p.status, kStageIdTm1, 150)) {
+            halve_bf16_smem(sW, kS1WBytes, threadIdx.x - 64, kS1LnThreads + 2 * kS1EpiThreads);
+            fence_proxy_async_smem();
+        }
+        mbar_arrive(w_ready);
+    }
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(w_full, kS1WBytes);
+            const CUtensorMap* wm[4] = {&tmWl, &tmWlg, &tmWr, &tmWrg};
+            for (int m = 0; m < 4; ++m)
+                for (int kh = 0; kh < 2; ++kh)
+                    tma_load_2d(sW + (m * 2 + kh) * kT1SubTile, wm[m], w_full, kh * 64, 0);
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (it >> 1) & 1u;
+                if (!mbar_wait(&x_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm1, 100 + s)) break;
+                const int t0 = (tile % p.tiles_per_fixed) * kT1P;
+                const int bf = tile / p.tiles_per_fixed;
+                const int f = bf % p.n_fixed;
+                const int b = bf / p.n_fixed;
+                mbar_arrive_expect_tx(&x_full[s], kT1XBytes);
+                uint8_t* dst = sX + s * kT1XBytes;
+                // z viewed as (channel, column, row, batch); outgoing box = 128 columns of row f,
+                // incoming box = 128 rows of column f
+                const int col = p.incoming ? f : t0;
+                const int row = p.incoming ? t0 : f;
+                tma_load_4d(dst, &tmZ, &x_full[s], 0, col, row, b);
+                tma_load_4d(dst + kT1SubTile, &tmZ, &x_full[s], 64, col, row, b);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(128, kT1P);
+            bool ok = mbar_wait(w_ready, 0, abort_flag, p.status, kStageIdTm1, 200);
+            tcgen05_fence_after();
+            uint32_t it = 0;
+            for (int tile = blockIdx.x; ok && tile < p.total_tiles; tile += gridDim.x, ++it) {
+                const int s = it & 1;
+                const uint32_t ph = (it >> 1) & 1u;
+                if (!mbar_wait(&xn_ready[s], ph, abort_flag, p.status, kStageIdTm1, 210 + s)) break;
+                tcgen05_fence_after();
+                const uint32_t xs = smem_u32(sX + s * kT1XBytes);
+                for (int side = 0; side < 2; ++side) {
+                    if (!mbar_wait(&acc_empty[side], (it & 1u) ^ 1u, abort_flag, p.status, kStageIdTm1,
+                                   220 + side)) {
+                        ok = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint32_t d_p = tmem_base + side * 256;
+                    const uint32_t d_g = d_p + 128;
+                    const uint32_t wp = smem_u32(sW + (side * 4) * kT1SubTile);       // proj: 2 K halves
+                    const uint32_t wg = smem_u32(sW + (side * 4 + 2) * kT1SubTile);   // gate: 2 K halves
+#pragma unroll
+                    for (int kk = 0; kk < kT1C / 16; ++kk) {
+                        const uint32_t sub = (kk >> 2) * kT1SubTile;
+                        const uint64_t kofs = (kk & 3) * kDescKStep;
+                        const uint64_t db = umma_smem_desc_sw128(xs + sub) + kofs;
+                        umma_bf16_ss(d_p, umma_smem_desc_sw128(wp + sub) + kofs, db, idesc, kk != 0);
+                        umma_bf16_ss(d_g, umma_smem_desc_sw128(wg + sub) + kofs, db, idesc, kk != 0);
+                    }
+                    umma_commit(&acc_full[side]);
+                }
+                if (!ok) break;
+                umma_commit(&x_empty[s]);   // both sides' UMMAs have read the tile when this fires
+            }
+        }
+        __syncwarp();
+    } else if (warp < 10) {
+        // ------------------------------------------------------------------ LayerNorm (+ mask)
+        // two groups of four warps; group g takes the tiles with (local tile index & 1) == g, which
+        // are the ones in stage g; one thread per position
+        const int g = (warp - 2) >> 2;
+        const int pos = threadIdx.x - 64 - g * 128;    // 0..127, row of the tile
+        const int bar_id = g == 0 ? kS1LnBarrier : kS1LnBarrier2;
+        uint32_t it = g;
+        for (int tile = blockIdx.x + g * gridDim.x; tile < p.total_tiles; tile += 2 * gridDim.x, it += 2) {
+            const uint32_t ph = (it >> 1) & 1u;
+            // pair-mask value of this position (independent of the tile data: do it first)
+            bool keep = true;
+            if (p.mask_kind != 0) {
+                const int t0 = (tile % p.tiles_per_fixed) * kT1P;
+                const int bf = tile / p.tiles_per_fixed;
+                const int f = bf % p.n_fixed;
+                const int b = bf / p.n_fixed;
+                const int run = t0 + pos;
+                keep = false;
+                if (run < p.n_run) {
+                    const int zr = p.row0 + (p.incoming ? run : f);   // global z row
+                    const int zc = p.incoming ? f : run;              // z column
+                    if (p.mask_kind == 1)
+                        keep = (p.mask[(size_t)b * p.N + zr] != 0) && (p.mask[(size_t)b * p.N + zc] != 0);
+                    else
+                        keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
+                }
+            }
+            if (!group_wait(&x_full[g], ph, pos == 0, bar_id, 128, abort_flag, p.status, kStageIdTm1, 300 + g)) break;
+#ifdef TRIMUL_S1_WARP_LN
+            {
+                // experiment: the warp-cooperative LayerNorm of tm1_sm100.cuh inside this kernel
+                const int wg = (warp - 2) & 3, rr = lane >> 3, j = lane & 7;
+                f32x2 gb[16];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    gb[k] = f2_pack(sGamma[8 * j + 2 * k], sGamma[8 * j + 2 * k + 1]);
+                    gb[4 + k] = f2_pack(sGamma[64 + 8 * j + 2 * k], sGamma[64 + 8 * j + 2 * k + 1]);
+                    gb[8 + k] = f2_pack(sBeta[8 * j + 2 * k], sBeta[8 * j + 2 * k + 1]);
+                    gb[12 + k] = f2_pack(sBeta[64 + 8 * j + 2 * k], sBeta[64 + 8 * j + 2 * k + 1]);
+                }
+                uint32_t zero_bits = 0u;
+                if (p.mask_kind != 0) {
+                    const int t0 = (tile % p.tiles_per_fixed) * kT1P;
+                    const int bf = tile / p.tiles_per_fixed;
+                    const int f = bf % p.n_fixed;
+                    const int b = bf / p.n_fixed;
+                    for (int i = 0; i < 8; ++i) {
+                        const int run = t0 + 32 * wg + 4 * i + rr;
+                        bool kp = false;
+                        if (run < p.n_run) {
+                            const int zr = p.row0 + (p.incoming ? run : f);
+                            const int zc = p.incoming ? f : run;
+                            if (p.mask_kind == 1)
+                                kp = (p.mask[(size_t)b * p.N + zr] != 0) && (p.mask[(size_t)b * p.N + zc] != 0);
+                            else
+                                kp = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
+                        }
+                        if (!kp) zero_bits |= 1u << i;
+                    }
+                }
+                ln_rows_warp<8>(sX + g * kT1XBytes, kT1SubTile, 32 * wg, lane, gb, p.eps, zero_bits);
+            }
+#else
+            ln_row_inplace(sX + g * kT1XBytes, kT1SubTile, pos, sGamma, sBeta, p.eps, !keep);
+#endif
+            fence_proxy_async_smem();   // normalised tile -> visible to the UMMA (async proxy)
+            mbar_arrive(&xn_ready[g]);
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue, one side per group
+        const int side = (warp - 10) >> 2;
+        const int q = warp & 3;
+        const int ch = q * 32 + lane;                 // output channel == TMEM lane
+        const bool leader = ((warp - 10) & 3) == 0 && lane == 0;
+        const int bar_id = kS1EpiBarrier + side;
+        uint8_t* stg = sOut + side * kT1SubTile;
+        const CUtensorMap* om = side == 0 ? &tmA : &tmB;
+        const ScatterMaps* sm = side == 0 ? &scA : &scB;
+        const int rc = side == 0 ? p.a_row_chunk : p.b_row_chunk;
+        const int cc = side == 0 ? p.a_col_chunk : p.b_col_chunk;
+        const uint32_t t_p = tmem_base + side * 256 + ((uint32_t)(q * 32) << 16);
+        uint32_t it = 0;
+        for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
+            const int t0 = (tile % p.tiles_per_fixed) * kT1P;
+            const int bf = tile / p.tiles_per_fixed;
+            const int f = bf % p.n_fixed;
+            const int b = bf / p.n_fixed;
+            if (!group_wait(&acc_full[side], it & 1u, leader, bar_id, kS1EpiThreads, abort_flag, p.status,
+                            kStageIdTm1, 400 + side))
+                break;
+            tcgen05_fence_after();
+            // 16 positions at a time; the TMEM loads of the next 16 are in flight while the current
+            // 16 are gated, rounded and written to the staging box (64 positions per TMA store)
+            auto emit16 = [&](int c16, const uint32_t (&rp)[16], const uint32_t (&rg)[16]) {
+#pragma unroll
+                for (int k = 0; k < 2; ++k) {
+                    uint32_t o[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int i0 = k * 8 + 2 * e;
+                        o[e] = gate2_bf16(__uint_as_float(rp[i0]), __uint_as_float(rg[i0]),
+                                          __uint_as_float(rp[i0 + 1]), __uint_as_float(rg[i0 + 1]));
+                    }
+                    const int chunk = ((c16 & 3) * 2 + k) ^ (ch & 7);
+                    *reinterpret_cast<uint4*>(stg + ch * 128 + (chunk << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+                }
+            };
+            uint32_t rpA[16], rgA[16], rpB[16], rgB[16];
+            tmem_ld_32x16(t_p, rpA);
+            tmem_ld_32x16(t_p + 128, rgA);
+#pragma unroll 1
+            for (int half = 0; half < 2; ++half) {
+                if (leader) tma_store_wait_read<0>();      // the previous store has read the staging box
+                named_barrier_sync(bar_id, kS1EpiThreads);
+#pragma unroll 1
+                for (int cp = 0; cp < 2; ++cp) {
+                    const int c16 = half * 4 + cp * 2;
+                    tmem_ld_wait();
+                    tmem_ld_32x16(t_p + (c16 + 1) * 16, rpB);
+                    tmem_ld_32x16(t_p + 128 + (c16 + 1) * 16, rgB);
+                    emit16(c16, rpA, rgA);
+                    tmem_ld_wait();
+                    if (c16 + 2 < 8) {
+                        tmem_ld_32x16(t_p + (c16 + 2) * 16, rpA);
+                        tmem_ld_32x16(t_p + 128 + (c16 + 2) * 16, rgA);
+                    } else {
+                        // every TMEM read of this side's accumulators has completed: hand them back early
+                        tcgen05_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(&acc_empty[side]);
+                    }
+                    emit16(c16 + 1, rpB, rgB);
+                }
+                fence_proxy_async_smem();
+                named_barrier_sync(bar_id, kS1EpiThreads);
+                if (leader) {
+                    const int col0 = t0 + half * 64;
+                    if (col0 < p.n_run) {
+                        if (kScatter) {
+                            const int seg = p.planes_per_dest < kT1C ? p.planes_per_dest : kT1C;
+                            for (int k0 = 0; k0 < kT1C; k0 += seg) {
+                                const int plane = b * kT1C + k0;
+                                const int d = plane / p.planes_per_dest;
+                                tma_store_4d(&sm->map[d], stg + k0 * 128, col0 % cc, f % rc,
+                                             plane - d * p.planes_per_dest, col0 / cc + f / rc);
+                            }
+                        } else {
+                            tma_store_4d(om, stg, col0 % cc, f % rc, b * kT1C, col0 / cc + f / rc);
+                        }
+                        tma_store_commit();
+                    }
+                }
+            }
+        }
+        if (leader) tma_store_wait_all<0>();
+        __syncwarp();
+    }
+
+    if (*abort_flag != 0) {
+        for (int i = 0; i < 256; ++i) __nanosleep(1000);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+}  // namespace trimul

@@ -70,6 +70,8 @@ constexpr int kG2EpiBarrier = 4;        // 4: channels 0..63, 5: channels 64..12
 struct Tm2FoldParams {
     Tm2Params base;
     int residual_is_z;    // add the z tile to the result (the block's `pair + update` form)
+    const __nv_bfloat16* drop_scale;   // [B, 1, N, 128] row-broadcast multiplier of the block output
+                                       // (module.py:332-337), applied before the residual; or null
 };
 
 template <bool kResidualIsZ, int kKH>
@@ -140,6 +142,9 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
     __syncthreads();
     tcgen05_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // set-up done without touching global memory: now wait for the producer of tri (and of z)
+    griddep_wait();
+    griddep_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
@@ -320,6 +325,13 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             const f32x2 rout = f2_pack(st.z, st.z), tout = f2_pack(st.w, st.w);
             const uint32_t t_g = tmem_base + s * 256 + grp * 64 + lane_bits;     // gate; proj 128 columns on
             uint8_t* tile_row = sZ + zs * kT2XBytes + grp * kT2SubTile + row * 128;
+            // this position's 64 drop-scale values (it is column j0 + row of z row r, any r)
+            const __nv_bfloat16* ds_row = nullptr;
+            if (fp.drop_scale != nullptr) {
+                const int j0 = (tile % p.tiles_per_row) * kT2P;
+                const int b = (tile / p.tiles_per_row) / p.rows;
+                if (j0 + row < p.N) ds_row = fp.drop_scale + ((size_t)b * p.N + j0 + row) * kT2C + grp * 64;
+            }
             // 8 output channels (one 16-byte chunk) at a time; the TMEM loads of the next 8 are in
             // flight while the current 8 get their statistics, are gated, rounded and written over the
             // z tile.  The loop stays rolled to keep the code small.
@@ -329,6 +341,11 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 if (kResidualIsZ) {
                     const uint4 rv = *dst;
                     res[0] = rv.x; res[1] = rv.y; res[2] = rv.z; res[3] = rv.w;
+                }
+                uint32_t dsw[4] = {0u, 0u, 0u, 0u};
+                if (ds_row != nullptr) {
+                    const uint4 dv = __ldg(reinterpret_cast<const uint4*>(ds_row + c8 * 8));
+                    dsw[0] = dv.x; dsw[1] = dv.y; dsw[2] = dv.z; dsw[3] = dv.w;
                 }
                 uint32_t o[4];
 #pragma unroll
@@ -341,6 +358,8 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                     float g0, g1;
                     f2_unpack(hg, g0, g1);
                     o[k] = f2_to_bf16x2(f2_fma(ho, f2_pack(tanh_fast(g0), tanh_fast(g1)), ho));
+                    if (ds_row != nullptr)   // the scale multiplies the rounded block output, like `out * scale`
+                        o[k] = f2_to_bf16x2(f2_mul(f2_from_bf16x2(o[k]), f2_from_bf16x2(dsw[k])));
                     if (kResidualIsZ)   // the reference rounds the block output to bf16 before `out + pair`
                         o[k] = f2_to_bf16x2(f2_add(f2_from_bf16x2(o[k]), f2_from_bf16x2(res[k])));
                 }

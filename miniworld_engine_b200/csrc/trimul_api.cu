@@ -9,18 +9,21 @@
 #include "../../include/trimul_b200.h"
 
 #include <atomic>
+#include <cstddef>
+#include <cstring>
 #include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 
 #include <mutex>
+#include <utility>
 
 #include "contract_sm100.cuh"
 #include "contract2_sm100.cuh"
+#include "peer_barrier.cuh"
 #include "plain_kernels.cuh"
 #include "tm1_sm100.cuh"
-#include "tm1_pair_sm100.cuh"
-#include "tm1_fold_sm100.cuh"
+#include "tm1_staged_sm100.cuh"
 #include "tm2_sm100.cuh"
 #include "tm2_fold_sm100.cuh"
 #include "wmma_kernels.cuh"
@@ -134,8 +137,18 @@ inline int64_t round_up(int64_t v, int64_t m) { return (v + m - 1) / m * m; }
 // ---------------------------------------------------------------------------------------
 // validation
 // ---------------------------------------------------------------------------------------
+// The descriptor grew by one trailing field (drop_scale); a caller built against the shorter
+// form passes its own size in struct_bytes and simply has no such field.
+constexpr uint32_t kDescBytesV1 = (uint32_t)offsetof(trimul_desc, drop_scale);
+
+inline const void* desc_drop_scale(const trimul_desc* d) {
+    return d->struct_bytes >= sizeof(trimul_desc) ? d->drop_scale : nullptr;
+}
+
 int check_desc(const trimul_desc* d) {
-    if (d == nullptr || d->struct_bytes != sizeof(trimul_desc)) return TRIMUL_E_INVALID;
+    if (d == nullptr || (d->struct_bytes != sizeof(trimul_desc) && d->struct_bytes != kDescBytesV1))
+        return TRIMUL_E_INVALID;
+    if (desc_drop_scale(d) != nullptr && (reinterpret_cast<uintptr_t>(d->drop_scale) & 15u) != 0) return TRIMUL_E_INVALID;
     if (d->B <= 0 || d->N <= 0 || d->c <= 0 || d->rows <= 0 || d->row0 < 0) return TRIMUL_E_INVALID;
     if (d->row0 + d->rows > d->N) return TRIMUL_E_INVALID;
     if (d->dtype != TRIMUL_DTYPE_BF16 && d->dtype != TRIMUL_DTYPE_FP32) return TRIMUL_E_INVALID;
@@ -197,6 +210,28 @@ bool tensor_core_path(const trimul_desc* d) {
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? TRIMUL_OK : TRIMUL_E_CUDA; }
 
+// Launch of a tensor-core stage kernel.  `overlap` asks for programmatic dependent launch: the
+// kernel may be scheduled while its predecessor in the stream is still draining, runs its set-up
+// (barriers, tensor memory, descriptor prefetch) and then blocks in griddepcontrol.wait until the
+// predecessor has completed, so launch latency and set-up disappear from the critical path.  Every
+// kernel launched this way executes that wait before it touches global memory.
+template <typename... KArgs, typename... Args>
+int launch_stage(void (*kernel)(KArgs...), int grid, int block, int smem, cudaStream_t st, bool overlap,
+                 Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid, 1, 1);
+    cfg.blockDim = dim3((unsigned)block, 1, 1);
+    cfg.dynamicSmemBytes = (size_t)smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = overlap ? 1u : 0u;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...) == cudaSuccess ? TRIMUL_OK : TRIMUL_E_CUDA;
+}
+inline bool overlap_launches(uint32_t flags) { return (flags & TRIMUL_FLAG_SERIAL_LAUNCH) == 0; }
+
 // ---------------------------------------------------------------------------------------
 // stage 1
 // ---------------------------------------------------------------------------------------
@@ -249,14 +284,12 @@ int run_wmma_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
 int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
                  const trimul_planes* a, const trimul_planes* b, cudaStream_t st, int32_t* status, int n_dest = 0) {
     const bool inc = d->direction == TRIMUL_INCOMING;
-    const bool pair = (d->flags & TRIMUL_FLAG_PAIR_STAGE1) != 0 && sm_count() >= 2;
-    const uint32_t zpos = pair ? 64 : 128;       // positions one CTA loads per tile
-    CUtensorMap tmZ, tmW[4], tmA, tmB;
+    CUtensorMap tmZ, tmW[4];
     {
         const uint64_t dims[4] = {128, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
         const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
-        const uint32_t box_out[4] = {64, zpos, 1, 1};
-        const uint32_t box_in[4] = {64, 1, zpos, 1};
+        const uint32_t box_out[4] = {64, 128, 1, 1};
+        const uint32_t box_in[4] = {64, 1, 128, 1};
         if (!encode_bf16(&tmZ, z, 4, dims, strides, inc ? box_in : box_out, 128)) return TRIMUL_E_CUDA;
     }
     const void* ws[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
@@ -267,22 +300,7 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
         if (!encode_bf16(&tmW[m], ws[m], 2, dims, strides, box, 128)) return TRIMUL_E_CUDA;
     }
     const int planes = d->B * 128;
-    ScatterMaps scA{}, scB{};
     const int planes_per_dest = n_dest > 0 ? planes / n_dest : planes;
-    if (n_dest > 0) {
-        // stores of a and b: 64 positions x one destination's share of the 128 planes per box
-        const uint32_t seg = planes_per_dest < 128 ? planes_per_dest : 128;
-        for (int k = 0; k < n_dest; ++k) {
-            if (!encode_planes(&scA.map[k], a[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
-            if (!encode_planes(&scB.map[k], b[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
-        }
-        tmA = scA.map[0];
-        tmB = scB.map[0];
-    } else {
-        // stores of a and b: 64 positions x 128 planes per box
-        if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
-        if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
-    }
 
     Tm1Params p;
     p.B = d->B; p.c = 128;
@@ -301,37 +319,38 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
     p.planes_per_dest = planes_per_dest;
     p.status = status;
+    const trimul_planes* sides[2] = {a, b};
+    for (int sd = 0; sd < 2; ++sd) {
+        Tm1Dest& dd = p.dest[sd];
+        for (int k = 0; k < 8; ++k)
+            dd.base[k] = static_cast<__nv_bfloat16*>(k < (n_dest > 0 ? n_dest : 1) ? sides[sd][k].base : nullptr);
+        dd.plane_stride = sides[sd]->plane_stride;
+        dd.chunk_stride = sides[sd]->chunk_stride;
+        dd.pitch = (int)sides[sd]->pitch;
+        dd.row_chunk = eff_chunk(sides[sd]->row_chunk, sides[sd]->rows);
+        dd.col_chunk = eff_chunk(sides[sd]->col_chunk, sides[sd]->cols);
+    }
+    const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+    const bool overlap = overlap_launches(d->flags);
+    if ((d->flags & TRIMUL_FLAG_SMEM_STORE_STAGE1) != 0 && n_dest == 0) {
+        // cross-check variant: transposed projections, results staged in shared memory and TMA-stored
+        CUtensorMap tmA, tmB;
+        if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+        if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+        ScatterMaps scA{}, scB{};
+        if (!ensure_smem(tm1_staged_sm100_kernel<false>, kS1SmemBytes)) return TRIMUL_E_CUDA;
+        tm1_staged_sm100_kernel<false><<<grid, kS1Threads, kS1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA,
+                                                                             tmB, p, scA, scB);
+        return launch_status();
+    }
     if (n_dest > 0) {
         if (!ensure_smem(tm1_sm100_kernel<true>, kT1SmemBytes)) return TRIMUL_E_CUDA;
-        const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-        tm1_sm100_kernel<true><<<grid, kT1Threads, kT1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p,
-                                                                     scA, scB);
-        return launch_status();
-    }
-    if ((d->flags & TRIMUL_FLAG_FOLDED_STAGE1) != 0) {
-        // LayerNorm folded into the weights, which live in tensor memory
-        Tm1FoldParams fp;
-        fp.base = p;
-        for (int m = 0; m < 4; ++m) fp.w[m] = static_cast<const __nv_bfloat16*>(ws[m]);
-        if (!ensure_smem(tm1_fold_sm100_kernel, kF1SmemBytes)) return TRIMUL_E_CUDA;
-        const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-        tm1_fold_sm100_kernel<<<grid, kF1Threads, kF1SmemBytes, st>>>(tmZ, tmA, tmB, fp);
-        return launch_status();
-    }
-    if (pair) {
-        // CTA pairs: one cluster of two CTAs per 128-position tile
-        if (!ensure_smem(tm1_pair_sm100_kernel, kP1SmemBytes)) return TRIMUL_E_CUDA;
-        const int max_clusters = sm_count() / 2;
-        const int clusters = p.total_tiles < max_clusters ? p.total_tiles : max_clusters;
-        tm1_pair_sm100_kernel<<<2 * clusters, kP1Threads, kP1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3],
-                                                                             tmA, tmB, p);
-        return launch_status();
+        return launch_stage(tm1_sm100_kernel<true>, grid, kT1Threads, kT1SmemBytes, st, overlap, tmZ, tmW[0], tmW[1],
+                            tmW[2], tmW[3], p);
     }
     if (!ensure_smem(tm1_sm100_kernel<false>, kT1SmemBytes)) return TRIMUL_E_CUDA;
-    const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
-    tm1_sm100_kernel<false><<<grid, kT1Threads, kT1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p,
-                                                                  scA, scB);
-    return launch_status();
+    return launch_stage(tm1_sm100_kernel<false>, grid, kT1Threads, kT1SmemBytes, st, overlap, tmZ, tmW[0], tmW[1],
+                        tmW[2], tmW[3], p);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -349,8 +368,10 @@ bool fast_contract_ok(const trimul_planes* a, const trimul_planes* b, const trim
     // a chunk boundary must not cut through a tile (a CTA's half tile for the pair kernel) or a K slice
     if (a->row_chunk < a->rows && (a->row_chunk % kCtBM)) return false;
     if (b->row_chunk < b->rows && (b->row_chunk % (pair ? 128 : kCtBN))) return false;
-    if (a->col_chunk < a->cols && (a->col_chunk % kCtBK)) return false;
-    if (b->col_chunk < b->cols && (b->col_chunk % kCtBK)) return false;
+    // K chunks: whole K slices per chunk, and the last chunk full (the tensor map gives every chunk
+    // the extent col_chunk, so a ragged last chunk would read its padding instead of zeros)
+    if (a->col_chunk < a->cols && ((a->col_chunk % kCtBK) || (a->cols % a->col_chunk))) return false;
+    if (b->col_chunk < b->cols && ((b->col_chunk % kCtBK) || (b->cols % b->col_chunk))) return false;
     if (t->row_chunk < t->rows && (t->row_chunk % kCtBM)) return false;
     if (t->col_chunk < t->cols && (t->col_chunk % 64)) return false;
     if ((reinterpret_cast<uintptr_t>(a->base) | reinterpret_cast<uintptr_t>(b->base) |
@@ -362,7 +383,7 @@ bool fast_contract_ok(const trimul_planes* a, const trimul_planes* b, const trim
 // `n_dest` == 0: t is one plane set.  `n_dest` > 0 (pair kernel only): t[k], k < n_dest, receives
 // output rows [k * R, (k + 1) * R), R = rows_a / n_dest (identical geometry, R a multiple of 128).
 int run_fast_contract(int planes, const trimul_planes* a, const trimul_planes* b, const trimul_planes* t,
-                      cudaStream_t st, int32_t* status, bool pair, int n_dest = 0) {
+                      cudaStream_t st, int32_t* status, bool pair, uint32_t flags, int n_dest = 0) {
     CUtensorMap tmA, tmB, tmD;
     ScatterMaps sc{};
     if (!encode_planes(&tmA, *a, planes, kCtBK, kCtBM, 1)) return TRIMUL_E_CUDA;
@@ -388,14 +409,15 @@ int run_fast_contract(int planes, const trimul_planes* a, const trimul_planes* b
         if (pair_tiles > 0x3fffffff) return TRIMUL_E_UNSUPPORTED;
         const int max_clusters = sm_count() / 2;
         const int clusters = pair_tiles < max_clusters ? (int)pair_tiles : max_clusters;
+        const bool overlap = overlap_launches(flags);
         if (n_dest > 0) {
             if (!ensure_smem(contract2_sm100_kernel<true>, kC2SmemBytes)) return TRIMUL_E_CUDA;
-            contract2_sm100_kernel<true><<<2 * clusters, kCtThreads, kC2SmemBytes, st>>>(tmA, tmB, tmD, p, sc);
-        } else {
-            if (!ensure_smem(contract2_sm100_kernel<false>, kC2SmemBytes)) return TRIMUL_E_CUDA;
-            contract2_sm100_kernel<false><<<2 * clusters, kCtThreads, kC2SmemBytes, st>>>(tmA, tmB, tmD, p, sc);
+            return launch_stage(contract2_sm100_kernel<true>, 2 * clusters, kCtThreads, kC2SmemBytes, st, overlap, tmA,
+                                tmB, tmD, p, sc);
         }
-        return launch_status();
+        if (!ensure_smem(contract2_sm100_kernel<false>, kC2SmemBytes)) return TRIMUL_E_CUDA;
+        return launch_stage(contract2_sm100_kernel<false>, 2 * clusters, kCtThreads, kC2SmemBytes, st, overlap, tmA,
+                            tmB, tmD, p, sc);
     }
     if (n_dest > 0) return TRIMUL_E_UNSUPPORTED;
     const int64_t total = (int64_t)planes * p.tiles_m * p.tiles_n;
@@ -419,6 +441,7 @@ int run_plain_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri,
     p.eps_in = d->eps_in; p.eps_out = d->eps_out;
     p.w_gate = w->w_gate; p.w_out = w->w_out;
     p.tri = view_of(*tri);
+    p.drop_scale = desc_drop_scale(d);
     const int64_t grid = (int64_t)d->B * d->rows * ((d->N + kPlainPos - 1) / kPlainPos);
     plain_tm2_kernel<T><<<(unsigned)grid, kPlainThreads, 0, st>>>(static_cast<const T*>(z), static_cast<T*>(out),
                                                                    static_cast<const T*>(residual), p);
@@ -434,6 +457,7 @@ int run_wmma_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     p.eps_in = d->eps_in; p.eps_out = d->eps_out;
     p.w_gate = w->w_gate; p.w_out = w->w_out;
     p.tri = view_of(*tri);
+    p.drop_scale = desc_drop_scale(d);
     const int smem = wmma_tm2_smem(d->c, d->c_hidden);
     auto kernel = d->c >= 128 ? wmma_tm2_kernel<4> : wmma_tm2_kernel<2>;
     if (!ensure_smem(kernel, wmma_tm2_smem(kPlainMaxC, kPlainMaxC))) return TRIMUL_E_CUDA;
@@ -480,11 +504,12 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
         Tm2FoldParams fp;
         fp.base = p;
         fp.residual_is_z = residual != nullptr;
+        fp.drop_scale = static_cast<const __nv_bfloat16*>(desc_drop_scale(d));
 #define TRIMUL_LAUNCH_TM2_FOLD(RES, KH)                                                                          \
     do {                                                                                                          \
         if (!ensure_smem(tm2_fold_sm100_kernel<RES, KH>, G2Layout<KH>::kSmemBytes)) return TRIMUL_E_CUDA;          \
-        tm2_fold_sm100_kernel<RES, KH><<<grid, kG2Threads, G2Layout<KH>::kSmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, \
-                                                                                          tmTri, fp);             \
+        return launch_stage(tm2_fold_sm100_kernel<RES, KH>, grid, kG2Threads, G2Layout<KH>::kSmemBytes, st,        \
+                            overlap_launches(d->flags), tmZ, tmWg, tmWo, tmOut, tmTri, fp);                       \
     } while (0)
         if (kh == 2) {
             if (residual != nullptr) TRIMUL_LAUNCH_TM2_FOLD(true, 2);
@@ -494,9 +519,9 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
             else TRIMUL_LAUNCH_TM2_FOLD(false, 1);
         }
 #undef TRIMUL_LAUNCH_TM2_FOLD
-        return launch_status();
     }
     if (kh != 1) return TRIMUL_E_UNSUPPORTED;      // the in-place variant below is 128 hidden channels only
+    if (desc_drop_scale(d) != nullptr) return TRIMUL_E_UNSUPPORTED;   // ... and has no drop-scale operand
     if (!ensure_smem(tm2_sm100_kernel, kT2SmemBytes)) return TRIMUL_E_CUDA;
     tm2_sm100_kernel<<<grid, kT2Threads, kT2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmRes, tmTri, p);
     return launch_status();
@@ -595,8 +620,9 @@ int trimul_b200_contract(int32_t dtype, uint32_t flags, int32_t planes, const tr
     if (dtype == TRIMUL_DTYPE_FP32) return run_plain_contract<float>(planes, a, b, tri, st);
     if ((flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0) {
         const bool pair = (flags & TRIMUL_FLAG_SINGLE_CTA_CONTRACT) == 0 && sm_count() >= 2;
-        if (fast_contract_ok(a, b, tri, pair)) return run_fast_contract(planes, a, b, tri, st, status, pair);
-        if (pair && fast_contract_ok(a, b, tri, false)) return run_fast_contract(planes, a, b, tri, st, status, false);
+        if (fast_contract_ok(a, b, tri, pair)) return run_fast_contract(planes, a, b, tri, st, status, pair, flags);
+        if (pair && fast_contract_ok(a, b, tri, false))
+            return run_fast_contract(planes, a, b, tri, st, status, false, flags);
     }
     return run_plain_contract<__nv_bfloat16>(planes, a, b, tri, st);
 }
@@ -634,9 +660,9 @@ int trimul_b200_tm1_scatter(const trimul_desc* desc, const void* z, const uint8_
             return TRIMUL_E_INVALID;
     }
     if (!same_geometry(a_dest, n_dest) || !same_geometry(b_dest, n_dest)) return TRIMUL_E_INVALID;
-    // tensor-core kernel only: a destination's share must be whole 8-plane groups of a 128-plane tile
+    // tensor-core kernel only: a destination's share must be whole 16-plane groups of a 128-plane tile
     if (!tensor_core_path(desc) || desc->c_hidden != 128) return TRIMUL_E_UNSUPPORTED;
-    if (per % 8 != 0 || !(128 % per == 0 || per % 128 == 0)) return TRIMUL_E_UNSUPPORTED;
+    if (per % 16 != 0 || !(128 % per == 0 || per % 128 == 0)) return TRIMUL_E_UNSUPPORTED;
     if ((a_dest->col_chunk < a_dest->cols && a_dest->col_chunk % 64) ||
         (b_dest->col_chunk < b_dest->cols && b_dest->col_chunk % 64))
         return TRIMUL_E_UNSUPPORTED;
@@ -646,7 +672,6 @@ int trimul_b200_tm1_scatter(const trimul_desc* desc, const void* z, const uint8_
 int trimul_b200_contract_scatter(int32_t dtype, uint32_t flags, int32_t planes, const trimul_planes* a,
                                  const trimul_planes* b, int32_t n_dest, const trimul_planes* tri_dest, void* stream,
                                  int32_t* status) {
-    (void)flags;
     if (a == nullptr || b == nullptr || tri_dest == nullptr) return TRIMUL_E_INVALID;
     if (planes <= 0 || planes > 65535) return TRIMUL_E_INVALID;
     if (dtype != TRIMUL_DTYPE_BF16 && dtype != TRIMUL_DTYPE_FP32) return TRIMUL_E_INVALID;
@@ -667,7 +692,7 @@ int trimul_b200_contract_scatter(int32_t dtype, uint32_t flags, int32_t planes, 
     trimul_planes shape = tri_dest[0];        // operand checks of the tile geometry use the full extent
     shape.rows = a->rows; shape.row_chunk = a->rows;
     if (!fast_contract_ok(a, b, &shape, true)) return TRIMUL_E_UNSUPPORTED;
-    return run_fast_contract(planes, a, b, tri_dest, static_cast<cudaStream_t>(stream), status, true, n_dest);
+    return run_fast_contract(planes, a, b, tri_dest, static_cast<cudaStream_t>(stream), status, true, flags, n_dest);
 }
 
 int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes* tri, const trimul_weights* w,
@@ -713,6 +738,10 @@ int trimul_b200_forward(const trimul_desc* desc, const void* z, const uint8_t* m
     if (z == nullptr || out == nullptr || out == z || !aligned16(z) || !aligned16(out)) return TRIMUL_E_INVALID;
     if (residual != nullptr && (!aligned16(residual) || residual == out)) return TRIMUL_E_INVALID;
     if (desc->mask_kind != TRIMUL_MASK_NONE && mask == nullptr) return TRIMUL_E_INVALID;
+    // the one combination the tensor-core last stage has no kernel for (see trimul_desc.drop_scale)
+    if (desc_drop_scale(desc) != nullptr && residual != nullptr && residual != z && tensor_core_path(desc) &&
+        desc->c_hidden == 128)
+        return TRIMUL_E_UNSUPPORTED;
     if ((rc = trimul_b200_tm1(desc, z, mask, w, &a, &b, stream, status)) != TRIMUL_OK) return rc;
     if ((rc = trimul_b200_contract(desc->dtype, desc->flags, desc->B * desc->c_hidden, &a, &b, &t, stream, status)) !=
         TRIMUL_OK)
@@ -747,7 +776,8 @@ int trimul_b200_forward_bidir(const trimul_desc* desc, const void* z, const uint
     const int64_t set_bytes = (int64_t)(need / 3);
     uint8_t* base = static_cast<uint8_t*>(workspace);
     // stage 1: per batch element and direction, with that direction's rows of the [2h, c] weights
-    trimul_desc d1 = *desc;
+    trimul_desc d1 = {};
+    memcpy(&d1, desc, desc->struct_bytes < sizeof(trimul_desc) ? desc->struct_bytes : sizeof(trimul_desc));
     d1.B = 1;
     d1.c_hidden = (int32_t)h;
     for (int bi = 0; bi < desc->B; ++bi) {
@@ -778,6 +808,27 @@ int trimul_b200_forward_bidir(const trimul_desc* desc, const void* z, const uint
         TRIMUL_OK)
         return rc;
     return trimul_b200_tm2(desc, z, &t, w, out, add_residual ? z : nullptr, stream, status);
+}
+
+int trimul_b200_peer_barrier(int32_t rank, int32_t world, int32_t* const* peer_flags, uint32_t epoch,
+                             uint32_t timeout_us, void* stream, int32_t* status) {
+    if (world < 1 || world > kMaxDest || rank < 0 || rank >= world || peer_flags == nullptr || epoch == 0 ||
+        timeout_us == 0)
+        return TRIMUL_E_INVALID;
+    PeerFlags pf{};
+    for (int r = 0; r < world; ++r) {
+        if (peer_flags[r] == nullptr || (reinterpret_cast<uintptr_t>(peer_flags[r]) & 3u) != 0) return TRIMUL_E_INVALID;
+        pf.flags[r] = peer_flags[r];
+    }
+    peer_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(pf, rank, world, epoch,
+                                                                        (uint64_t)timeout_us * 1000ull, status);
+    return launch_status();
+}
+
+int trimul_b200_selftest_expiring_wait(uint32_t timeout_us, void* stream, int32_t* status) {
+    if (timeout_us == 0 || status == nullptr) return TRIMUL_E_INVALID;
+    expire_wait_kernel<<<1, 128, 0, static_cast<cudaStream_t>(stream)>>>((uint64_t)timeout_us * 1000ull, status);
+    return launch_status();
 }
 
 // ---------------------------------------------------------------------------------------

@@ -281,6 +281,9 @@ wmma_tm2_kernel(const __nv_bfloat16* __restrict__ z, __nv_bfloat16* __restrict__
                 if (q < npos) {
                     float y = sigmoid_ref(scr[i * 16 + j]) * scr[256 + i * 16 + j];
                     const long long e = (pos0 + q) * c + nf * 16 + j;
+                    if (p.drop_scale != nullptr)
+                        y = __bfloat162float(__float2bfloat16_rn(y)) *
+                            __bfloat162float(static_cast<const __nv_bfloat16*>(p.drop_scale)[((long long)b * p.N + s0 + q) * c + nf * 16 + j]);
                     if (residual != nullptr) y = __bfloat162float(__float2bfloat16_rn(y)) + __bfloat162float(residual[e]);
                     out[e] = __float2bfloat16_rn(y);
                 }

@@ -42,6 +42,17 @@ def _require_cuda(t: torch.Tensor, name: str) -> None:
             f"{name} must live on a CUDA device: trimul_b200 has no CPU path (got device {t.device})")
 
 
+def _require_no_grad(what: str, *tensors) -> None:
+    """The kernels have no backward.  The reference's functional op is autograd-transparent
+    (``kernels/trimul_inproj/whole_op.py:170-190``) and its module routes grad-enabled calls to an
+    autograd-capable path (``module.py:229-233``), so a caller that expects gradients must not be
+    handed a silently detached result: raise instead."""
+    if torch.is_grad_enabled() and any(isinstance(t, torch.Tensor) and t.requires_grad for t in tensors):
+        raise NotImplementedError(
+            f"{what} is forward-only (no backward kernels): call it under torch.no_grad(), or with "
+            "inputs and parameters that do not require grad")
+
+
 def _mask_bytes(mask: torch.Tensor) -> torch.Tensor:
     """Mask as one byte per element, without a kernel launch when it already is bool/uint8."""
     if mask.dtype == torch.bool:
@@ -153,12 +164,18 @@ def trimul_forward(
     residual: torch.Tensor | None = None,
     plain_kernels: bool = False,
     inplace_norm: bool = False,
+    serial_launch: bool = False,
+    drop_scale: torch.Tensor | None = None,
 ) -> torch.Tensor:
     """One block call on the current CUDA stream.  ``mask`` is a ``[B,N]`` token mask, a
     ``[B,N,N]`` pair mask or None; ``residual`` (same shape/dtype as ``x``) is added to the
     result when given.  Passing ``x`` itself as the residual (the block's ``pair + update`` form)
     costs nothing extra: the last stage adds the tile it already holds.  ``plain_kernels`` and
-    ``inplace_norm`` select cross-checking variants of the kernels (see the flags in the C header).
+    ``inplace_norm`` select cross-checking variants of the kernels, ``serial_launch`` turns
+    programmatic dependent launch of the stages off (see the flags in the C header).
+    ``drop_scale`` is the reference module's row-broadcast dropout scale ``[B, 1, N, c]``
+    (``module.py:332-337``): the block output is multiplied by it before the residual is added
+    (``kernels/trimul_inproj/triton/gate_elem.py:41-78``).
 
     The hidden width ``h`` is read off the weights: the four input projections are ``[h, c]``,
     ``ln_out_*`` have ``h`` entries and ``w_out`` is ``[c, h]`` (``whole_op.py:203-209``).  bf16 with
@@ -167,6 +184,8 @@ def trimul_forward(
     multiples of 16 and the activations bf16, else on the CUDA-core kernels."""
     if x.dim() != 4 or x.shape[1] != x.shape[2]:
         raise ValueError(f"x must be [B, N, N, c], got {tuple(x.shape)}")
+    _require_no_grad("trimul_forward", x, residual, ln_in_weight, ln_in_bias, w_left, w_left_gate, w_right,
+                     w_right_gate, ln_out_weight, ln_out_bias, w_gate, w_out)
     _require_cuda(x, "x")
     B, N, _, c = x.shape
     code = _dtype_code(x)
@@ -189,12 +208,20 @@ def trimul_forward(
             raise ValueError("residual must match x in shape and dtype")
         _require_cuda(residual, "residual")
         residual = residual.detach().contiguous()
+    if drop_scale is not None:
+        if tuple(drop_scale.shape) != (B, 1, N, c) or drop_scale.dtype != x.dtype:
+            raise ValueError(f"drop_scale must be [B, 1, N, c] = {(B, 1, N, c)} of dtype {x.dtype}, got "
+                             f"{tuple(drop_scale.shape)} {drop_scale.dtype}")
+        _require_cuda(drop_scale, "drop_scale")
+        drop_scale = drop_scale.detach().contiguous()
 
     lib = _lib.load()
     desc = _lib.make_desc(B, N, c, c_hidden=h, dtype=code, direction=_lib.OUTGOING if outgoing else _lib.INCOMING,
                           mask_kind=mask_kind, eps_in=eps_in, eps_out=eps_out,
                           flags=(_lib.FLAG_PLAIN_KERNELS if plain_kernels else 0) |
-                          (_lib.FLAG_INPLACE_NORM_STAGE3 if inplace_norm else 0))
+                          (_lib.FLAG_INPLACE_NORM_STAGE3 if inplace_norm else 0) |
+                          (_lib.FLAG_SERIAL_LAUNCH if serial_launch else 0),
+                          drop_scale=drop_scale.data_ptr() if drop_scale is not None else None)
     w, keep = _weights_struct(c, x.dtype, ln_in_weight, ln_in_bias, w_left, w_left_gate, w_right, w_right_gate,
                               ln_out_weight, ln_out_bias, w_gate, w_out, x.device, c_hidden=h, c_proj=h)
     nbytes = C.c_size_t()

@@ -100,8 +100,10 @@ class TriangleMultiplicationB200(nn.Module):
 
     @torch.no_grad()
     def block(self, pair: torch.Tensor, mask: torch.Tensor | None = None, *,
-              residual: torch.Tensor | None = None, plain_kernels: bool = False) -> torch.Tensor:
-        """The block output as ``reference.py:62-83`` defines it (no residual unless given)."""
+              residual: torch.Tensor | None = None, plain_kernels: bool = False,
+              drop_scale: torch.Tensor | None = None) -> torch.Tensor:
+        """The block output as ``reference.py:62-83`` defines it (no residual unless given;
+        ``drop_scale`` ``[B, 1, L, D]`` multiplies it before the residual is added)."""
         return F_b200.trimul_forward(
             pair, mask, outgoing=self.outgoing,
             ln_in_weight=self.ln_pair.weight, ln_in_bias=self.ln_pair.bias,
@@ -110,7 +112,7 @@ class TriangleMultiplicationB200(nn.Module):
             ln_out_weight=self.ln_out.weight, ln_out_bias=self.ln_out.bias,
             w_gate=self.to_gate.weight, w_out=self.to_out.weight,
             eps_in=self.ln_pair.eps, eps_out=self.ln_out.eps,
-            residual=residual, plain_kernels=plain_kernels)
+            residual=residual, plain_kernels=plain_kernels, drop_scale=drop_scale)
 
     def forward(self, pair: torch.Tensor, mask: torch.Tensor | None = None,
                 dropout_p: float | None = None) -> torch.Tensor:
@@ -125,5 +127,7 @@ class TriangleMultiplicationB200(nn.Module):
             # row-broadcast dropout scale [B,1,L,D] = (rand > p) / (1 - p), module.py:332-337
             b, _, l2, d = pair.shape
             keep = torch.rand(b, 1, l2, d, device=pair.device, dtype=pair.dtype) > dropout_p
-            return self.block(pair, mask) * (keep.to(pair.dtype) / (1.0 - dropout_p)) + pair
+            # scale and residual are applied in the last stage's epilogue, like the reference's gate
+            # kernel does (kernels/trimul_inproj/triton/gate_elem.py:41-78)
+            return self.block(pair, mask, residual=pair, drop_scale=keep.to(pair.dtype) / (1.0 - dropout_p))
         return self.block(pair, mask, residual=pair)

@@ -20,10 +20,13 @@ over the full N x N x N, and returns the rows of ``tri`` to their owners (all-to
 a rank receives ``3 (world-1)/world`` of one operand instead of ``(world-1)`` operand slabs.
 
 ``PeerShardContext`` runs the channel-sharded pattern WITHOUT collectives in the data path: the
-three exchanges are the TMA stores of the producing kernels themselves, aimed at the consumer
+three exchanges are the stores of the producing kernels themselves, aimed at the consumer
 rank's memory (peer access over NVLink through symmetric-memory buffers), so the transfer of a
 tile overlaps the computation of the next one and nothing is copied twice.  Only two stream-ordered
-cross-GPU barriers per block remain.
+cross-GPU barriers per block remain; they are this library's own flag exchange with a bounded
+wait (``trimul_b200_peer_barrier``): a rank that stopped between steps makes its peers' barrier
+give up after ``barrier_timeout_us`` and report through the status words (``read_status``), which
+callers of ``PeerShardContext.forward`` should poll between steps.
 
 No k-sum is split across ranks in any pattern, so the result equals the single-GPU result.  The reference has
 no distributed code at all; its single-GPU module is the behaviour to match.
@@ -36,10 +39,14 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import ctypes as C
+
 import torch
 import torch.distributed as dist
 
+from . import _lib
 from . import stages as S
+from .functional import _status_words
 
 __all__ = ["ShardPlan", "ChannelShardPlan", "PeerShardContext", "peer_dest_specs", "exchange",
            "trimul_forward_sharded"]
@@ -269,7 +276,7 @@ class PeerShardContext:
     def supported(B: int, N: int, c: int, dtype: torch.dtype, world: int) -> bool:
         """Whether the scattering kernels exist for this problem on ``world`` ranks: bf16, c = 128
         (tensor-core kernels), at most 8 ranks, a rank's share of the ``B*c`` planes a multiple of
-        8 that divides or is a multiple of 128, and ``N/world`` rows per rank a multiple of 128.
+        16 that divides or is a multiple of 128, and ``N/world`` rows per rank a multiple of 128.
         Otherwise use ``trimul_forward_sharded(mode="channels")``, which does the same exchanges
         with NCCL all-to-alls."""
         if dtype != torch.bfloat16 or c != 128 or not 1 <= world <= 8:
@@ -277,9 +284,10 @@ class PeerShardContext:
         if N % world or (B * c) % world:
             return False
         per, rows = B * c // world, N // world
-        return per % 8 == 0 and (128 % per == 0 or per % 128 == 0) and rows % 128 == 0
+        return per % 16 == 0 and (128 % per == 0 or per % 128 == 0) and rows % 128 == 0
 
-    def __init__(self, B: int, N: int, c: int, dtype: torch.dtype, device, group=None):
+    def __init__(self, B: int, N: int, c: int, dtype: torch.dtype, device, group=None,
+                 barrier_timeout_us: int = 1_000_000):
         import os
         os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")   # plain peer stores only
         import torch.distributed._symmetric_memory as symm_mem
@@ -302,10 +310,30 @@ class PeerShardContext:
             self._peer[name] = [t if d == self.rank else h.get_buffer(d, (n,), dtype) for d in range(self.world)]
         self._dest = {o: peer_dest_specs(self._plans[o], lambda d: self._peer["a"][d], lambda d: self._peer["b"][d],
                                          lambda d: self._peer["tri"][d]) for o in (True, False)}
+        # flag words of the barrier: one array of `world` int32 per rank, writable by every rank
+        self.barrier_timeout_us = int(barrier_timeout_us)
+        self._epoch = 0
+        self._flags = symm_mem.empty(self.world, dtype=torch.int32, device=self.device)
+        self._flags.zero_()
+        fh = symm_mem.rendezvous(self._flags, self.group)
+        self._handles["flags"] = fh
+        self._flag_views = [self._flags if d == self.rank else fh.get_buffer(d, (self.world,), torch.int32)
+                            for d in range(self.world)]
+        self._flag_ptrs = (C.c_void_p * self.world)(*[t.data_ptr() for t in self._flag_views])
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)          # every rank's flags are zero before anyone signals
 
     def barrier(self) -> None:
-        """Stream-ordered barrier over the ranks of the group (device-side signal exchange)."""
-        self._handles["a"].barrier(channel=0)
+        """Stream-ordered barrier over the ranks of the group: the library's flag exchange with a
+        bounded wait.  When a peer never arrives the wait expires after ``barrier_timeout_us`` and
+        the status words say so (``read_status``); nothing hangs."""
+        self._epoch += 1
+        st = _status_words(self.device)
+        with torch.cuda.device(self.device):
+            rc = _lib.load().trimul_b200_peer_barrier(
+                self.rank, self.world, self._flag_ptrs, self._epoch, self.barrier_timeout_us,
+                torch.cuda.current_stream(self.device).cuda_stream, st.data_ptr())
+        _lib.check(rc, "trimul_b200_peer_barrier")
 
     @torch.no_grad()
     def forward(self, z_slab: torch.Tensor, mask, weights: dict, *, outgoing: bool, eps_in: float = 1e-5,

@@ -97,16 +97,16 @@ def dense_to_planes(spec: PlaneSpec, dense: torch.Tensor) -> None:
         spec.buf[: P * spec.plane_stride].view(P, spec.rows, spec.pitch)[..., :spec.cols].copy_(dense)
 
 
-def _desc(x, N, outgoing, mask_kind, eps_in, eps_out, plain, row0, pair_stage1=False, folded_stage1=False,
-          inplace_norm=False, c_hidden=None):
+def _desc(x, N, outgoing, mask_kind, eps_in, eps_out, plain, row0, smem_store=False, inplace_norm=False,
+          c_hidden=None, serial_launch=False):
     B, rows, _, c = x.shape
     return _lib.make_desc(B, N, c, c_hidden=c_hidden, dtype=_dtype_code(x),
                           direction=_lib.OUTGOING if outgoing else _lib.INCOMING, mask_kind=mask_kind,
                           eps_in=eps_in, eps_out=eps_out,
                           flags=(_lib.FLAG_PLAIN_KERNELS if plain else 0) |
-                          (_lib.FLAG_PAIR_STAGE1 if pair_stage1 else 0) |
-                          (_lib.FLAG_FOLDED_STAGE1 if folded_stage1 else 0) |
-                          (_lib.FLAG_INPLACE_NORM_STAGE3 if inplace_norm else 0),
+                          (_lib.FLAG_SMEM_STORE_STAGE1 if smem_store else 0) |
+                          (_lib.FLAG_INPLACE_NORM_STAGE3 if inplace_norm else 0) |
+                          (_lib.FLAG_SERIAL_LAUNCH if serial_launch else 0),
                           rows=rows, row0=row0)
 
 
@@ -123,14 +123,17 @@ def _mask_arg(mask, B, N):
 
 
 def tm1(z_slab: torch.Tensor, mask, weights: dict, a: PlaneSpec, b: PlaneSpec, *, outgoing: bool,
-        row0: int = 0, eps: float = 1e-5, plain_kernels: bool = False, pair_stage1: bool = False,
-        folded_stage1: bool = False) -> None:
-    """Stage 1 on a ``[B, rows, N, c]`` slab of z (rows ``row0 .. row0+rows`` of the grid)."""
+        row0: int = 0, eps: float = 1e-5, plain_kernels: bool = False, smem_store: bool = False,
+        serial_launch: bool = False) -> None:
+    """Stage 1 on a ``[B, rows, N, c]`` slab of z (rows ``row0 .. row0+rows`` of the grid).
+    ``smem_store`` selects the cross-checking variant of the tensor-core kernel;
+    ``serial_launch`` (on every stage) turns programmatic dependent launch off."""
     _require_cuda(z_slab, "z")
     B, rows, N, c = z_slab.shape
     kind, mask_u8 = _mask_arg(mask, B, N)
     hp = int(weights["w_left"].shape[0])      # operand planes per batch element (d_hidden)
-    d = _desc(z_slab, N, outgoing, kind, eps, eps, plain_kernels, row0, pair_stage1, folded_stage1, c_hidden=hp)
+    d = _desc(z_slab, N, outgoing, kind, eps, eps, plain_kernels, row0, smem_store, c_hidden=hp,
+              serial_launch=serial_launch)
     w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, c_proj=hp,
                               c_hidden=int(weights["w_out"].shape[1]), **weights)
     st = _status_words(z_slab.device)
@@ -145,7 +148,7 @@ def tm1(z_slab: torch.Tensor, mask, weights: dict, a: PlaneSpec, b: PlaneSpec, *
 
 
 def contract(a: PlaneSpec, b: PlaneSpec, tri: PlaneSpec, *, plain_kernels: bool = False,
-             single_cta: bool = False) -> None:
+             single_cta: bool = False, serial_launch: bool = False) -> None:
     """Stage 2: ``tri[p] = a[p] @ b[p]^T`` for every plane."""
     dev = a.buf.device
     code = _lib.DTYPE_BF16 if a.buf.dtype == torch.bfloat16 else _lib.DTYPE_FP32
@@ -153,7 +156,8 @@ def contract(a: PlaneSpec, b: PlaneSpec, tri: PlaneSpec, *, plain_kernels: bool 
     with torch.cuda.device(dev):
         rc = _lib.load().trimul_b200_contract(
             code, (_lib.FLAG_PLAIN_KERNELS if plain_kernels else 0) |
-            (_lib.FLAG_SINGLE_CTA_CONTRACT if single_cta else 0), a.planes,
+            (_lib.FLAG_SINGLE_CTA_CONTRACT if single_cta else 0) |
+            (_lib.FLAG_SERIAL_LAUNCH if serial_launch else 0), a.planes,
             C.byref(a.struct()), C.byref(b.struct()), C.byref(tri.struct()),
             torch.cuda.current_stream(dev).cuda_stream, st.data_ptr())
     _lib.check(rc, "trimul_b200_contract")
@@ -206,15 +210,15 @@ def contract_scatter(a: PlaneSpec, b: PlaneSpec, tri_dest) -> None:
 
 def tm2(z_slab: torch.Tensor, tri: PlaneSpec, weights: dict, *, residual=None, row0: int = 0,
         eps_in: float = 1e-5, eps_out: float = 1e-5, plain_kernels: bool = False,
-        inplace_norm: bool = False) -> torch.Tensor:
+        inplace_norm: bool = False, serial_launch: bool = False) -> torch.Tensor:
     """Stage 3 on a ``[B, rows, N, c]`` slab; returns the matching output slab.  The hidden width
     is read off ``weights["w_out"]`` (``[c, c_hidden]``): ``c``, or ``2c`` for the bidirectional
     block, whose ``tri`` holds ``B * 2c`` planes (per batch: outgoing planes, then incoming)."""
     _require_cuda(z_slab, "z")
     B, rows, N, c = z_slab.shape
     h = int(weights["w_out"].shape[1])
-    d = _desc(z_slab, N, True, _lib.MASK_NONE, eps_in, eps_out, plain_kernels, row0, False, False, inplace_norm,
-              c_hidden=h)
+    d = _desc(z_slab, N, True, _lib.MASK_NONE, eps_in, eps_out, plain_kernels, row0, False, inplace_norm,
+              c_hidden=h, serial_launch=serial_launch)
     w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, c_hidden=h,
                               c_proj=int(weights["w_left"].shape[0]), **weights)
     out = torch.empty_like(z_slab)

@@ -35,8 +35,9 @@ Arithmetic notes that matter for parity:
 * The token mask becomes a pair mask ``m[i] & m[k]`` that multiplies the gated
   left/right operands only.  The output gate sees the *unmasked* normalised
   input (``reference.py:72-75,83``).
-* No residual is added (``reference.py:83``); the reference's kernel-backed
-  module adds ``pair`` afterwards, which callers do separately.
+* No residual is added by the block itself (``reference.py:83``); the reference's
+  kernel-backed module adds ``pair`` afterwards, after the optional row-broadcast
+  dropout scale (``module.py:208-222``): ``trimul_module_forward`` restates that.
 """
 
 from __future__ import annotations
@@ -234,6 +235,25 @@ def trimul_forward(
 ) -> torch.Tensor:
     """Module-form block output (no residual), ``reference.py:62-83``."""
     return trimul_stages(z, token_mask, w, outgoing)["out"]
+
+
+@torch.no_grad()
+def trimul_module_forward(
+    z: torch.Tensor,
+    token_mask: torch.Tensor | None,
+    w: TrimulWeights,
+    outgoing: bool = True,
+    drop_scale: torch.Tensor | None = None,
+) -> torch.Tensor:
+    """What the reference MODULE returns: ``pair + drop_row(trimul(pair))``
+    (``src/miniworld_engine/modules/triangle_multiplication/module.py:208-222``): the block output,
+    times the row-broadcast dropout scale ``[B, 1, N, c]`` when one is live (training,
+    ``module.py:332-337``), plus the input.  Each step rounds to the activation dtype as eager
+    PyTorch does."""
+    out = trimul_stages(z, token_mask, w, outgoing)["out"]
+    if drop_scale is not None:
+        out = out * drop_scale
+    return out + z
 
 
 @torch.no_grad()

@@ -7,7 +7,9 @@ Run where the reference tree is available (it cannot travel to a GPU box):
 It imports the reference's ``TriangleMultiplicationReference``,
 ``triangle_multiplicative_update_pytorch``
 (``src/miniworld_engine/modules/triangle_multiplication/reference.py:32-122``) and
-``BidirectionalTriangleMultiplication`` (``.../bidirectional.py:93-156``, eager branch) unmodified,
+``BidirectionalTriangleMultiplication`` (``.../bidirectional.py:93-156``, eager branch) and the
+``TriangleMultiplication`` module in training mode with row-broadcast dropout
+(``.../module.py:208-222,332-337``, PyTorch backend) unmodified,
 runs them on CPU on the seeded inputs produced by ``oracle/trimul_oracle.py``'s
 generators, and writes one ``.npz`` per case: the inputs actually fed (so a
 change in a random generator cannot silently move the fixture) and the
@@ -53,6 +55,35 @@ BIDIR_CASES = [
     ("bidir_bf16_n14_d128_h64_rand5_aff", "bf16", 1, 14, 128, "rand5", "random", 48, 49, 64),
     ("bidir_bf16_n12_d64_h128_tail2_aff", "bf16", 1, 12, 64, "tail2", "random", 50, 51, 128),
 ]
+
+
+# the MODULE in training mode with row-broadcast dropout (module.py:208-222,332-337), generic PyTorch
+# backend: name, dtype, B, N, c, direction, mask kind, affine, weight seed, input seed, p_drop, rng seed
+DROPOUT_CASES = [
+    ("drop_out_fp32_n12_c32_tail3_aff_p25", "fp32", 2, 12, 32, "outgoing", "tail3", "random", 60, 61, 0.25, 7),
+    ("drop_in_bf16_n16_c128_rand5_aff_p15", "bf16", 1, 16, 128, "incoming", "rand5", "random", 62, 63, 0.15, 8),
+    ("drop_out_bf16_n14_c64_nomask_p50", "bf16", 2, 14, 64, "outgoing", "none", "unit", 64, 65, 0.5, 9),
+]
+
+
+def run_dropout_reference(case):
+    from miniworld_engine.modules.triangle_multiplication.module import TriangleMultiplication
+    name, dt, B, N, c, direction, mkind, affine, wseed, zseed, p_drop, rseed = case
+    dtype = torch.float32 if dt == "fp32" else torch.bfloat16
+    w = O.make_weights(c, wseed, affine=affine)
+    z = O.make_input(B, N, c, zseed)
+    mask = None if mkind == "none" else O.make_token_mask(B, N, mkind, seed=zseed + 100)
+    with torch.no_grad():
+        m = TriangleMultiplication(c, outgoing=(direction == "outgoing"), implementation="pytorch", p_drop=p_drop)
+        m.load_state_dict(w.state_dict())
+        m = m.to(dtype).train()
+        zd = z.to(dtype)
+        torch.manual_seed(rseed)
+        y = m(zd, mask)
+        # the scale is the first (and only) draw of the forward pass: the same seed reproduces it
+        torch.manual_seed(rseed)
+        ds = m._make_drop_row_scale(zd, p_drop)
+    return z, mask, w, ds, y
 
 
 def run_bidir_reference(case):
@@ -130,6 +161,18 @@ def main():
         path = os.path.join(HERE, name + ".npz")
         np.savez_compressed(path, **arrays)
         print(f"{name}: out shape {tuple(y.shape)} dtype {y.dtype} -> {os.path.getsize(path)} B")
+    for case in DROPOUT_CASES:
+        name = case[0]
+        z, mask, w, ds, y = run_dropout_reference(case)
+        arrays = {"z": z.numpy(), "out": y.float().numpy(), "drop_scale": ds.float().numpy()}
+        if mask is not None:
+            arrays["mask"] = mask.numpy()
+        for k, v in w.state_dict().items():
+            arrays["w:" + k] = v.numpy()
+        path = os.path.join(HERE, name + ".npz")
+        np.savez_compressed(path, **arrays)
+        print(f"{name}: out shape {tuple(y.shape)} dtype {y.dtype}, kept {float((ds != 0).float().mean()):.2f} -> "
+              f"{os.path.getsize(path)} B")
     for case in BIDIR_CASES:
         name = case[0]
         z, mask, w, y = run_bidir_reference(case)

@@ -34,7 +34,7 @@ def test_header_symbols_are_exported(lib):
 
 def test_struct_layouts_match_header(lib):
     from miniworld_engine_b200 import _lib
-    assert C.sizeof(_lib.Desc) == 13 * 4
+    assert C.sizeof(_lib.Desc) == 64 and _lib.Desc.drop_scale.offset == 56     # 13 x 4 bytes, padding, one pointer
     assert C.sizeof(_lib.Weights) == 10 * 8
     assert C.sizeof(_lib.Planes) == 8 * 8
     assert lib.trimul_b200_abi_version() == _lib.ABI_VERSION
@@ -162,3 +162,55 @@ def test_parameter_struct_cache_is_keyed_by_what_the_struct_depends_on(monkeypat
     # other expected widths with the same tensors: validated afresh and rejected
     with pytest.raises(ValueError):
         F._weights_struct(c, torch.bfloat16, device=None, c_hidden=c, c_proj=h, **p)
+
+
+def test_functional_ops_refuse_to_detach_silently():
+    """The functional entry points are forward-only: with grad enabled and an input or a parameter
+    that requires grad they raise (the reference's op is autograd-transparent,
+    kernels/trimul_inproj/whole_op.py:170-190), before any device check."""
+    import torch
+    from miniworld_engine_b200 import triangle_multiplicative_update_b200
+    from miniworld_engine_b200.bidirectional import bidirectional_triangle_multiplicative_update_b200
+    d = 16
+    x = torch.zeros(1, 4, 4, d, requires_grad=True)
+    v, m, m2 = torch.zeros(d), torch.zeros(d, d), torch.zeros(2 * d, d)
+    with pytest.raises(NotImplementedError, match="forward-only"):
+        triangle_multiplicative_update_b200(x, "outgoing", None, v, v, m2, m2, v, v, m, m)
+    w = torch.zeros(2 * d, d, requires_grad=True)
+    with pytest.raises(NotImplementedError, match="forward-only"):
+        triangle_multiplicative_update_b200(x.detach(), "incoming", None, v, v, w, m2, v, v, m, m)
+    v2, mo = torch.zeros(2 * d), torch.zeros(d, 2 * d)
+    with pytest.raises(NotImplementedError, match="forward-only"):
+        bidirectional_triangle_multiplicative_update_b200(
+            x, None, norm_in_weight=v, norm_in_bias=v, to_left_weight=m2, to_left_gate_weight=m2,
+            to_right_weight=m2, to_right_gate_weight=m2, norm_out_weight=v2, norm_out_bias=v2,
+            to_out_weight=mo, to_gate_weight=m)
+    # without grad the same calls get as far as the device check
+    with torch.no_grad(), pytest.raises(RuntimeError, match="no CPU path"):
+        triangle_multiplicative_update_b200(x, "outgoing", None, v, v, m2, m2, v, v, m, m)
+
+
+def test_descriptor_without_the_trailing_field_is_still_accepted(lib):
+    """A caller built against the shorter descriptor (no drop_scale) passes its own struct_bytes."""
+    from miniworld_engine_b200 import _lib
+    d = _lib.make_desc(1, 16, 128, dtype=_lib.DTYPE_BF16, direction=_lib.OUTGOING)
+    n_new, n_old = C.c_size_t(), C.c_size_t()
+    assert lib.trimul_b200_workspace_bytes(C.byref(d), C.byref(n_new), None, None, None) == _lib.OK
+    d.struct_bytes = 56
+    d.drop_scale = 0xdead0                      # must be ignored: the short form has no such field
+    assert lib.trimul_b200_workspace_bytes(C.byref(d), C.byref(n_old), None, None, None) == _lib.OK
+    assert n_old.value == n_new.value
+    d.struct_bytes = 60
+    assert lib.trimul_b200_workspace_bytes(C.byref(d), C.byref(n_old), None, None, None) == _lib.E_INVALID
+
+
+def test_barrier_and_selftest_argument_checks(lib):
+    from miniworld_engine_b200 import _lib
+    ptrs = (C.c_void_p * 2)(0x1000, 0x2000)
+    assert lib.trimul_b200_peer_barrier(0, 9, ptrs, 1, 1000, None, None) == _lib.E_INVALID     # world > 8
+    assert lib.trimul_b200_peer_barrier(2, 2, ptrs, 1, 1000, None, None) == _lib.E_INVALID     # rank outside
+    assert lib.trimul_b200_peer_barrier(0, 2, ptrs, 0, 1000, None, None) == _lib.E_INVALID     # epoch 0
+    assert lib.trimul_b200_peer_barrier(0, 2, ptrs, 1, 0, None, None) == _lib.E_INVALID        # no limit
+    bad = (C.c_void_p * 2)(0x1000, None)
+    assert lib.trimul_b200_peer_barrier(0, 2, bad, 1, 1000, None, None) == _lib.E_INVALID      # null flag array
+    assert lib.trimul_b200_selftest_expiring_wait(1000, None, None) == _lib.E_INVALID          # status required

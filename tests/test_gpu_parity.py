@@ -14,7 +14,7 @@ import torch
 
 from oracle import trimul_oracle as O
 from tests._util import forward_kwargs, oracle_out
-from tests.test_oracle_golden import FILES, load_case
+from tests.test_oracle_golden import FILES, load_case, load_drop_scale
 
 pytestmark = pytest.mark.gpu
 
@@ -62,6 +62,14 @@ def test_golden_fixture(path, dev):
         y = run_block(z, mask, w, direction == "outgoing", dtype, dev)
     elif form == "bidir":
         y = run_bidir(z, mask, w, dtype, dev)
+    elif form == "dropout":
+        # what the reference module returns in training mode: block * scale + pair, in one call
+        zd = z.to(dtype).to(dev)
+        ds = load_drop_scale(path, dtype).to(dev)
+        from miniworld_engine_b200 import read_status, trimul_forward
+        y = trimul_forward(zd, None if mask is None else mask.to(dev), outgoing=(direction == "outgoing"),
+                           **forward_kwargs(w, dtype, dev), residual=zd, drop_scale=ds).cpu()
+        assert read_status(dev)[0] == 0
     else:
         from miniworld_engine_b200 import triangle_multiplicative_update_b200 as f
         wd = w.to(dtype)
@@ -260,9 +268,9 @@ def test_module_state_dict_roundtrip_and_forward(dev):
 
 def test_alternative_kernels_agree(dev):
     """The lone-CTA contraction is another schedule of the same arithmetic as the CTA-pair one
-    (same accumulation order per output element): bit-identical.  The CTA-pair stage 1 sums the
-    LayerNorm statistics in a different order, so it may differ from the default in the last
-    bf16 bit of a few elements."""
+    (same accumulation order per output element): bit-identical.  The stage 1 that keeps its
+    weights in shared memory sums the LayerNorm statistics in a different order from the default
+    one (weights in tensor memory), so the two may differ in the last bf16 bit of a few elements."""
     from miniworld_engine_b200 import read_status, stages as S
     from tests._util import weights_dict
     w = O.make_weights(128, 0, affine="random")
@@ -272,25 +280,19 @@ def test_alternative_kernels_agree(dev):
     m = O.make_token_mask(2, N, "tail9").to(dev)
     for outgoing in (True, False):
         res = []
-        for pair in (False, True):
+        for smem_store in (False, True):
             a = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
             b = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
-            S.tm1(z, m, wd, a, b, outgoing=outgoing, pair_stage1=pair)
+            S.tm1(z, m, wd, a, b, outgoing=outgoing, smem_store=smem_store)
             res.append((S.planes_to_dense(a).clone(), S.planes_to_dense(b).clone(), a, b))
         assert O.rel_rms(res[1][0].float().cpu(), res[0][0].float().cpu()) <= 1e-3
         assert O.rel_rms(res[1][1].float().cpu(), res[0][1].float().cpu()) <= 1e-3
+        assert torch.equal(res[1][0] == 0, res[0][0] == 0)      # masked positions: exact zeros in both
         t1 = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
         t2 = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
         S.contract(res[0][2], res[0][3], t1)
         S.contract(res[0][2], res[0][3], t2, single_cta=True)
         assert torch.equal(S.planes_to_dense(t1), S.planes_to_dense(t2))
-        # stage 1 with the LayerNorm folded into weights held in tensor memory: rounds W*gamma
-        # instead of LN(x) to bf16, so it agrees with the default to bf16 noise, not bit for bit
-        a = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
-        b = S.alloc_planes(256, N, N, torch.bfloat16, dev, fill=float("nan"))
-        S.tm1(z, m, wd, a, b, outgoing=outgoing, folded_stage1=True)
-        assert O.rel_rms(S.planes_to_dense(a).float().cpu(), res[0][0].float().cpu()) <= 5e-3
-        assert O.rel_rms(S.planes_to_dense(b).float().cpu(), res[0][1].float().cpu()) <= 5e-3
         # stage 3: default (both LayerNorms folded into the weights) against the in-place variant,
         # with and without the residual
         for residual in (None, z):
@@ -543,3 +545,80 @@ def test_full_size_token_permutation_equivariance(dev):
         yp = run_block(zp.float(), m[:, p], w, outgoing, torch.bfloat16, dev)
         err = O.rel_rms(yp.float(), y[:, p][:, :, p].float())
         assert err <= 3e-3, f"outgoing={outgoing}: rel-RMS {err:.3e}"
+
+
+def test_headline_n768_outgoing_vs_oracle(dev):
+    """The benchmark's headline workload itself (bf16, B=1, N=768, c=128, outgoing, all-ones token
+    mask) against the CPU oracle on the same seeded inputs."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    w, z, m = O.make_weights(128, 0), O.make_input(1, 768, 128, 1), O.make_token_mask(1, 768, "ones")
+    y = run_block(z, m, w, True, torch.bfloat16, dev)
+    ref = oracle_out(z, m, w, True, torch.bfloat16)
+    err = O.rel_rms(y.float(), ref.float())
+    assert err <= TOL_BF16, f"rel-RMS {err:.3e}"
+
+
+def test_config5_n2048_outgoing_then_incoming_vs_oracle(dev):
+    """BASELINE config 5 on one GPU: an outgoing block followed by an incoming block on its output
+    (independent weight sets, seeds 0 and 3), N=2048, random 5 % token padding, against two CPU-oracle
+    block calls.  The second block is compared on the SAME input (the first block's GPU output), so the
+    check is per block and errors do not compound."""
+    torch.set_num_threads(os.cpu_count() or 1)
+    N = 2048
+    w1, w2 = O.make_weights(128, 0), O.make_weights(128, 3)
+    z, m = O.make_input(1, N, 128, 1), O.make_token_mask(1, N, "rand5")
+    y1 = run_block(z, m, w1, True, torch.bfloat16, dev)
+    ref1 = oracle_out(z, m, w1, True, torch.bfloat16)
+    e1 = O.rel_rms(y1.float(), ref1.float())
+    assert e1 <= TOL_BF16, f"outgoing block: rel-RMS {e1:.3e}"
+    del ref1
+    y2 = run_block(y1.float(), m, w2, False, torch.bfloat16, dev)
+    ref2 = O.trimul_forward(y1, m, w2.to(torch.bfloat16), False)
+    e2 = O.rel_rms(y2.float(), ref2.float())
+    assert e2 <= TOL_BF16, f"incoming block: rel-RMS {e2:.3e}"
+    # padded output rows of the second block: LayerNorm_out of an all-zero contraction gives beta = 0
+    pad = ~m[0]
+    assert float(y2[0, pad].abs().max()) == 0.0 and float(y2[0, :, pad].abs().max()) == 0.0
+
+
+def test_fused_dropout_scale_equals_the_unfused_composition(dev):
+    """`block * scale + pair` fused into the last stage's epilogue gives bit for bit what the three
+    separate operations give (same rounding points), on the tensor-core path and on the others."""
+    from miniworld_engine_b200 import read_status, trimul_forward
+    for c, N, dtype in ((128, 200, torch.bfloat16), (64, 40, torch.bfloat16), (32, 24, torch.float32)):
+        w = O.make_weights(c, 5, affine="random")
+        z = O.make_input(2, N, c, 6).to(dtype).to(dev)
+        m = O.make_token_mask(2, N, "tail9").to(dev)
+        g = torch.Generator().manual_seed(7)
+        ds = ((torch.rand(2, 1, N, c, generator=g) > 0.3).float() / 0.7).to(dtype).to(dev)
+        kw = forward_kwargs(w, dtype, dev)
+        fused = trimul_forward(z, m, outgoing=True, **kw, residual=z, drop_scale=ds)
+        plain = trimul_forward(z, m, outgoing=True, **kw)
+        assert torch.equal(fused, plain * ds + z), (c, N, dtype)
+        only_scale = trimul_forward(z, m, outgoing=True, **kw, drop_scale=ds)
+        assert torch.equal(only_scale, plain * ds), (c, N, dtype)
+    assert read_status(dev)[0] == 0
+
+
+def test_contraction_refuses_a_ragged_last_k_chunk_on_the_tensor_cores(dev):
+    """K-chunked operands (what an all-to-all leaves behind) whose last chunk is not full: the
+    tensor-core kernel would read the chunk's padding, so the call must take the CUDA-core kernel,
+    which bounds every index.  The padding is poisoned with NaN to prove nothing reads it."""
+    from miniworld_engine_b200 import stages as S
+    P, R, K, chunk = 8, 128, 192, 128
+    g = torch.Generator().manual_seed(3)
+    a_d = torch.randn(P, R, K, generator=g).bfloat16().to(dev)
+    b_d = torch.randn(P, R, K, generator=g).bfloat16().to(dev)
+    a = S.alloc_planes(P, R, K, torch.bfloat16, dev, fill=float("nan"), col_chunk=chunk)
+    b = S.alloc_planes(P, R, K, torch.bfloat16, dev, fill=float("nan"), col_chunk=chunk)
+    # the test helper scatters whole chunks only: fill chunk 0 fully, chunk 1 with the remaining 64 columns
+    for spec, dense in ((a, a_d), (b, b_d)):
+        v = spec.buf[: 2 * spec.chunk_stride].view(2, P, R, spec.pitch)
+        v[0, :, :, :chunk] = dense[..., :chunk]
+        v[1, :, :, : K - chunk] = dense[..., chunk:]
+    t = S.alloc_planes(P, R, R, torch.bfloat16, dev, fill=float("nan"))
+    S.contract(a, b, t)
+    got = S.planes_to_dense(t).float()
+    ref = torch.einsum("pik,pjk->pij", a_d.float(), b_d.float())
+    assert not torch.isnan(got).any()
+    assert O.rel_rms(got.cpu(), ref.cpu()) <= 5e-3

@@ -1,6 +1,7 @@
 """The CPU oracle restates the reference exactly: check it against the golden
 fixtures that ``tests/golden/make_golden.py`` produced by running the reference's
-own ``reference.py`` (module and functional forms) and its bidirectional module."""
+own ``reference.py`` (module and functional forms), its bidirectional module and its
+``TriangleMultiplication`` module in training mode with row-broadcast dropout."""
 
 import glob
 import os
@@ -41,8 +42,16 @@ def load_case(path):
         mask = torch.from_numpy(d["mask"]) if "mask" in d.files else None
     dtype = torch.bfloat16 if "bf16" in name else torch.float32
     direction = "incoming" if ("in_" in name.split("fp32")[0].split("bf16")[0]) else "outgoing"
-    form = "functional" if name.startswith("func") else "bidir" if name.startswith("bidir") else "module"
+    form = ("functional" if name.startswith("func") else "bidir" if name.startswith("bidir") else
+            "dropout" if name.startswith("drop") else "module")
+    if form == "dropout":
+        direction = "incoming" if name.startswith("drop_in") else "outgoing"
     return name, z, mask, w, torch.from_numpy(d["out"]), dtype, direction, form
+
+
+def load_drop_scale(path, dtype):
+    """The row-broadcast dropout scale [B, 1, N, c] the reference module drew for a dropout fixture."""
+    return torch.from_numpy(np.load(path)["drop_scale"]).to(dtype)
 
 
 def test_fixture_set_is_complete():
@@ -51,6 +60,7 @@ def test_fixture_set_is_complete():
     assert len(names) >= 15
     assert sum(n.startswith("bidir") for n in names) >= 6
     assert sum("_h" in n for n in names) >= 3      # d_hidden != d_pair
+    assert sum(n.startswith("drop") for n in names) >= 3   # module in training mode, dropout scale live
 
 
 @pytest.mark.parametrize("path", FILES, ids=[os.path.basename(f)[:-4] for f in FILES])
@@ -62,6 +72,10 @@ def test_oracle_matches_reference_output(path):
         y = O.trimul_forward(z.to(dtype), mask, wd, outgoing=(direction == "outgoing"))
     elif form == "bidir":
         y = O.bidir_forward(z.to(dtype), mask, wd)
+    elif form == "dropout":
+        ds = load_drop_scale(path, dtype)
+        assert tuple(ds.shape) == (z.shape[0], 1, z.shape[2], z.shape[3]) and 0.0 < float((ds == 0).float().mean()) < 1.0
+        y = O.trimul_module_forward(z.to(dtype), mask, wd, outgoing=(direction == "outgoing"), drop_scale=ds)
     else:
         y = O.trimul_forward_functional(
             z.to(dtype), direction, mask, wd.ln_pair_weight, wd.ln_pair_bias,
