@@ -577,6 +577,13 @@ __device__ __forceinline__ uint32_t gate2_bf16(float hp0, float hg0, float hp1, 
     return f2_to_bf16x2(f2_fma(hp, f2_pack(tanh_fast(hg0), tanh_fast(hg1)), hp));
 }
 
+// the same from UNHALVED p and g (kernels that stream their weights and cannot halve them once)
+__device__ __forceinline__ uint32_t gate2_full_bf16(float p0, float g0, float p1, float g1) {
+    const f32x2 half2 = f2_pack(0.5f, 0.5f);
+    const f32x2 hp = f2_mul(f2_pack(p0, p1), half2);
+    return f2_to_bf16x2(f2_fma(hp, f2_pack(tanh_fast(0.5f * g0), tanh_fast(0.5f * g1)), hp));
+}
+
 // Multiply `nbytes` of bf16 data in shared memory by 0.5 in place (exact: only the exponent
 // changes), work split over `nthreads` cooperating threads with rank `tid`.
 __device__ __forceinline__ void halve_bf16_smem(uint8_t* base, int nbytes, int tid, int nthreads) {
@@ -663,8 +670,11 @@ __device__ __forceinline__ void ln_half_row_inplace(uint8_t* tile, int sub_bytes
 // this variant moves about a third of the shared-memory wavefronts of the two-thread one, which
 // matters because these kernels are bound by shared-memory bandwidth, not by arithmetic.
 // ---------------------------------------------------------------------------------------
+template <int kSub = 2>
 __device__ __forceinline__ void ln_row_inplace(uint8_t* tile, int sub_bytes, int row, const float* sGamma,
                                                const float* sBeta, float eps, bool zero_row) {
+    // kSub = number of 64-channel sub-tiles of a row (2: 128 channels, 4: 256 channels)
+    constexpr float kInvC = 1.0f / (64.0f * kSub);
     const uint32_t swz = (uint32_t)(row & 7);
     uint8_t* rowp = tile + row * 128;
     const uint32_t first = *reinterpret_cast<const uint32_t*>(rowp + (swz << 4));
@@ -673,7 +683,7 @@ __device__ __forceinline__ void ln_row_inplace(uint8_t* tile, int sub_bytes, int
     // four independent accumulator pairs keep the dependent add/fma chains short
     f32x2 s1[4] = {0ull, 0ull, 0ull, 0ull}, s2[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll 1
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kSub; ++s) {
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             const uint4 v = *reinterpret_cast<const uint4*>(rowp + s * sub_bytes + ((((uint32_t)j) ^ swz) << 4));
@@ -686,14 +696,14 @@ __device__ __forceinline__ void ln_row_inplace(uint8_t* tile, int sub_bytes, int
             }
         }
     }
-    const float m1 = f2_hsum(f2_add(f2_add(s1[0], s1[1]), f2_add(s1[2], s1[3]))) * (1.0f / 128.0f);
+    const float m1 = f2_hsum(f2_add(f2_add(s1[0], s1[1]), f2_add(s1[2], s1[3]))) * kInvC;
     const float q1 = f2_hsum(f2_add(f2_add(s2[0], s2[1]), f2_add(s2[2], s2[3])));
-    const float var = fmaxf(fmaf(-m1, m1, q1 * (1.0f / 128.0f)), 0.f);
+    const float var = fmaxf(fmaf(-m1, m1, q1 * kInvC), 0.f);
     const float rstd = rsqrtf(var + eps);
     const float nmr = -(shift + m1) * rstd;
     const f32x2 rstd2 = f2_pack(rstd, rstd), nmr2 = f2_pack(nmr, nmr);
 #pragma unroll 1
-    for (int s = 0; s < 2; ++s) {
+    for (int s = 0; s < kSub; ++s) {
 #pragma unroll 4
         for (int j = 0; j < 8; ++j) {
             uint4* p = reinterpret_cast<uint4*>(rowp + s * sub_bytes + ((((uint32_t)j) ^ swz) << 4));

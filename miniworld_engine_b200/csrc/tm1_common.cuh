@@ -1,0 +1,45 @@
+// Constants and launch parameters shared by the stage-1 kernels (tm1_sm100.cuh, the default, and
+// tm1_direct_sm100.cuh, the thread-per-position variant).
+#pragma once
+
+#include "ptx_sm100.cuh"
+
+namespace trimul {
+
+constexpr int kT1C = 128;                 // channels
+constexpr int kT1P = 128;                 // positions per tile
+constexpr int kT1SubTile = 128 * 64 * 2;  // 16 KB: 128 rows x 64 bf16, one swizzle-row wide
+constexpr int kT1XBytes = 2 * kT1SubTile; // one z tile
+constexpr int kStageIdTm1 = 1;
+
+// Where one side's planes go (thread-per-position variant, which stores with plain pointers):
+// element (plane, r, q) of the logical [planes][rows][cols] array lies at
+//   base + (r / row_chunk) * chunk_stride + plane * plane_stride + (r % row_chunk) * pitch + q      (row-chunked)
+//   base + (q / col_chunk) * chunk_stride + plane * plane_stride + r * pitch + (q % col_chunk)      (col-chunked)
+// in elements (at most one of the two is chunked; an unchunked extent has chunk == extent).
+struct Tm1Dest {
+    __nv_bfloat16* base[8];   // one per destination buffer (index 0 only unless scattering)
+    long long plane_stride, chunk_stride;
+    int pitch, row_chunk, col_chunk;
+};
+
+struct Tm1Params {
+    int B, c;
+    int n_fixed;          // extent of the tile's fixed index (outgoing: rows, incoming: N)
+    int n_run;            // extent of the running index     (outgoing: N,    incoming: rows)
+    int tiles_per_fixed;  // ceil(n_run / 128)
+    int total_tiles;      // B * n_fixed * tiles_per_fixed
+    int incoming;         // 0 / 1
+    int N, row0;          // full token count and global index of the slab's first z row
+    int mask_kind;
+    const uint8_t* mask;
+    const float* gamma;
+    const float* beta;
+    float eps;
+    int a_row_chunk, a_col_chunk, b_row_chunk, b_col_chunk;
+    int planes_per_dest;  // scatter variants: planes of one destination (a multiple of 16; divides or is a multiple of 128)
+    int32_t* status;
+    Tm1Dest dest[2];      // a, b (thread-per-position variant only)
+};
+
+}  // namespace trimul

@@ -37,6 +37,10 @@
 // Before the first tile the epilogue threads fold gamma and 1/2 into Wg and Wo in shared memory
 // and leave per-channel (rowsum, bias) pairs for the epilogue.
 //
+// kDropScale: the row-broadcast dropout scale of the reference module in training mode multiplies
+// the block output before the residual (a template parameter: the inference instantiations carry
+// no trace of it).
+//
 // kKH = 2 is the last stage of the BIDIRECTIONAL block (bidirectional.py:150-156): tri has 256
 // channel planes per batch ([outgoing | incoming]), LayerNorm_out runs over all 256 and Wo is
 // [128, 256].  The tri tile then arrives as two 128-channel halves, each in one slot of the tri
@@ -74,7 +78,7 @@ struct Tm2FoldParams {
                                        // (module.py:332-337), applied before the residual; or null
 };
 
-template <bool kResidualIsZ, int kKH>
+template <bool kResidualIsZ, int kKH, bool kDropScale>
 __global__ void __launch_bounds__(kG2Threads, 1)
 tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWg,
                       const __grid_constant__ CUtensorMap tmWo, const __grid_constant__ CUtensorMap tmOut,
@@ -327,7 +331,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             uint8_t* tile_row = sZ + zs * kT2XBytes + grp * kT2SubTile + row * 128;
             // this position's 64 drop-scale values (it is column j0 + row of z row r, any r)
             const __nv_bfloat16* ds_row = nullptr;
-            if (fp.drop_scale != nullptr) {
+            if (kDropScale) {
                 const int j0 = (tile % p.tiles_per_row) * kT2P;
                 const int b = (tile / p.tiles_per_row) / p.rows;
                 if (j0 + row < p.N) ds_row = fp.drop_scale + ((size_t)b * p.N + j0 + row) * kT2C + grp * 64;
@@ -343,7 +347,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                     res[0] = rv.x; res[1] = rv.y; res[2] = rv.z; res[3] = rv.w;
                 }
                 uint32_t dsw[4] = {0u, 0u, 0u, 0u};
-                if (ds_row != nullptr) {
+                if (kDropScale && ds_row != nullptr) {
                     const uint4 dv = __ldg(reinterpret_cast<const uint4*>(ds_row + c8 * 8));
                     dsw[0] = dv.x; dsw[1] = dv.y; dsw[2] = dv.z; dsw[3] = dv.w;
                 }
@@ -358,7 +362,7 @@ tm2_fold_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                     float g0, g1;
                     f2_unpack(hg, g0, g1);
                     o[k] = f2_to_bf16x2(f2_fma(ho, f2_pack(tanh_fast(g0), tanh_fast(g1)), ho));
-                    if (ds_row != nullptr)   // the scale multiplies the rounded block output, like `out * scale`
+                    if (kDropScale && ds_row != nullptr)   // the scale multiplies the rounded block output, like `out * scale`
                         o[k] = f2_to_bf16x2(f2_mul(f2_from_bf16x2(o[k]), f2_from_bf16x2(dsw[k])));
                     if (kResidualIsZ)   // the reference rounds the block output to bf16 before `out + pair`
                         o[k] = f2_to_bf16x2(f2_add(f2_from_bf16x2(o[k]), f2_from_bf16x2(res[k])));

@@ -23,9 +23,11 @@
 #include "peer_barrier.cuh"
 #include "plain_kernels.cuh"
 #include "tm1_sm100.cuh"
-#include "tm1_staged_sm100.cuh"
+#include "tm1_direct_sm100.cuh"
 #include "tm2_sm100.cuh"
 #include "tm2_fold_sm100.cuh"
+#include "tm1_wide_sm100.cuh"
+#include "tm2_wide_sm100.cuh"
 #include "wmma_kernels.cuh"
 
 using namespace trimul;
@@ -208,6 +210,12 @@ bool tensor_core_path(const trimul_desc* d) {
     return d->dtype == TRIMUL_DTYPE_BF16 && d->c == 128 && (d->flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0;
 }
 
+// bf16 with c = h = 256: the streamed-weight tensor-core kernels of stages 1 and 3
+bool wide_tensor_core_path(const trimul_desc* d) {
+    return d->dtype == TRIMUL_DTYPE_BF16 && d->c == 256 && d->c_hidden == 256 &&
+           (d->flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0;
+}
+
 int launch_status() { return cudaGetLastError() == cudaSuccess ? TRIMUL_OK : TRIMUL_E_CUDA; }
 
 // Launch of a tensor-core stage kernel.  `overlap` asks for programmatic dependent launch: the
@@ -332,25 +340,84 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     }
     const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
     const bool overlap = overlap_launches(d->flags);
-    if ((d->flags & TRIMUL_FLAG_SMEM_STORE_STAGE1) != 0 && n_dest == 0) {
-        // cross-check variant: transposed projections, results staged in shared memory and TMA-stored
-        CUtensorMap tmA, tmB;
-        if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
-        if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
-        ScatterMaps scA{}, scB{};
-        if (!ensure_smem(tm1_staged_sm100_kernel<false>, kS1SmemBytes)) return TRIMUL_E_CUDA;
-        tm1_staged_sm100_kernel<false><<<grid, kS1Threads, kS1SmemBytes, st>>>(tmZ, tmW[0], tmW[1], tmW[2], tmW[3], tmA,
-                                                                             tmB, p, scA, scB);
-        return launch_status();
+    if ((d->flags & TRIMUL_FLAG_DIRECT_STORE_STAGE1) != 0) {
+        // variant: 8 UMMAs of full width per side, thread = position, direct global stores
+        if (n_dest > 0) {
+            if (!ensure_smem(tm1_direct_sm100_kernel<true>, kD1SmemBytes)) return TRIMUL_E_CUDA;
+            return launch_stage(tm1_direct_sm100_kernel<true>, grid, kD1Threads, kD1SmemBytes, st, overlap, tmZ, tmW[0],
+                                tmW[1], tmW[2], tmW[3], p);
+        }
+        if (!ensure_smem(tm1_direct_sm100_kernel<false>, kD1SmemBytes)) return TRIMUL_E_CUDA;
+        return launch_stage(tm1_direct_sm100_kernel<false>, grid, kD1Threads, kD1SmemBytes, st, overlap, tmZ, tmW[0],
+                            tmW[1], tmW[2], tmW[3], p);
     }
+    // default: transposed projections, results staged in shared memory and TMA-stored
+    CUtensorMap tmA, tmB;
+    ScatterMaps scA{}, scB{};
     if (n_dest > 0) {
+        // stores of a and b: 64 positions x one destination's share of the 128 planes per box
+        const uint32_t seg = planes_per_dest < 128 ? planes_per_dest : 128;
+        for (int k = 0; k < n_dest; ++k) {
+            if (!encode_planes(&scA.map[k], a[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
+            if (!encode_planes(&scB.map[k], b[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
+        }
+        tmA = scA.map[0];
+        tmB = scB.map[0];
         if (!ensure_smem(tm1_sm100_kernel<true>, kT1SmemBytes)) return TRIMUL_E_CUDA;
         return launch_stage(tm1_sm100_kernel<true>, grid, kT1Threads, kT1SmemBytes, st, overlap, tmZ, tmW[0], tmW[1],
-                            tmW[2], tmW[3], p);
+                            tmW[2], tmW[3], tmA, tmB, p, scA, scB);
     }
+    // stores of a and b: 64 positions x 128 planes per box
+    if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
     if (!ensure_smem(tm1_sm100_kernel<false>, kT1SmemBytes)) return TRIMUL_E_CUDA;
     return launch_stage(tm1_sm100_kernel<false>, grid, kT1Threads, kT1SmemBytes, st, overlap, tmZ, tmW[0], tmW[1],
-                        tmW[2], tmW[3], p);
+                        tmW[2], tmW[3], tmA, tmB, p, scA, scB);
+}
+
+// c = h = 256: weights streamed through shared memory (tm1_wide_sm100.cuh)
+int run_wide_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
+                 const trimul_planes* a, const trimul_planes* b, cudaStream_t st, int32_t* status) {
+    const bool inc = d->direction == TRIMUL_INCOMING;
+    CUtensorMap tmZ, tmW[4], tmA, tmB;
+    {
+        const uint64_t dims[4] = {kW1C, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
+        const uint64_t strides[3] = {kW1C, (uint64_t)d->N * kW1C, (uint64_t)d->rows * d->N * kW1C};
+        const uint32_t box_out[4] = {64, 128, 1, 1};
+        const uint32_t box_in[4] = {64, 1, 128, 1};
+        if (!encode_bf16(&tmZ, z, 4, dims, strides, inc ? box_in : box_out, 128)) return TRIMUL_E_CUDA;
+    }
+    const void* ws[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
+    for (int m = 0; m < 4; ++m) {
+        const uint64_t dims[2] = {kW1C, kW1C};
+        const uint64_t strides[1] = {kW1C};
+        const uint32_t box[2] = {64, 128};
+        if (!encode_bf16(&tmW[m], ws[m], 2, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    }
+    const int planes = d->B * kW1C;
+    if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
+    Tm1Params p = {};
+    p.B = d->B; p.c = kW1C;
+    p.n_fixed = inc ? d->N : d->rows;
+    p.n_run = inc ? d->rows : d->N;
+    p.tiles_per_fixed = (p.n_run + kT1P - 1) / kT1P;
+    const int64_t total = (int64_t)d->B * p.n_fixed * p.tiles_per_fixed;
+    if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
+    p.total_tiles = (int)total;
+    p.incoming = inc;
+    p.N = d->N; p.row0 = d->row0;
+    p.mask_kind = mask ? d->mask_kind : 0;
+    p.mask = mask;
+    p.gamma = w->ln_in_weight; p.beta = w->ln_in_bias; p.eps = d->eps_in;
+    p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_col_chunk = eff_chunk(a->col_chunk, a->cols);
+    p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
+    p.planes_per_dest = planes;
+    p.status = status;
+    const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+    if (!ensure_smem(tm1_wide_sm100_kernel, kW1SmemBytes)) return TRIMUL_E_CUDA;
+    return launch_stage(tm1_wide_sm100_kernel, grid, kW1Threads, kW1SmemBytes, st, overlap_launches(d->flags), tmZ,
+                        tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -505,19 +572,25 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
         fp.base = p;
         fp.residual_is_z = residual != nullptr;
         fp.drop_scale = static_cast<const __nv_bfloat16*>(desc_drop_scale(d));
-#define TRIMUL_LAUNCH_TM2_FOLD(RES, KH)                                                                          \
-    do {                                                                                                          \
-        if (!ensure_smem(tm2_fold_sm100_kernel<RES, KH>, G2Layout<KH>::kSmemBytes)) return TRIMUL_E_CUDA;          \
-        return launch_stage(tm2_fold_sm100_kernel<RES, KH>, grid, kG2Threads, G2Layout<KH>::kSmemBytes, st,        \
-                            overlap_launches(d->flags), tmZ, tmWg, tmWo, tmOut, tmTri, fp);                       \
+#define TRIMUL_LAUNCH_TM2_FOLD(RES, KH, DS)                                                                       \
+    do {                                                                                                           \
+        if (!ensure_smem(tm2_fold_sm100_kernel<RES, KH, DS>, G2Layout<KH>::kSmemBytes)) return TRIMUL_E_CUDA;       \
+        return launch_stage(tm2_fold_sm100_kernel<RES, KH, DS>, grid, kG2Threads, G2Layout<KH>::kSmemBytes, st,     \
+                            overlap_launches(d->flags), tmZ, tmWg, tmWo, tmOut, tmTri, fp);                        \
+    } while (0)
+#define TRIMUL_LAUNCH_TM2_FOLD_RK(RES, KH)                  \
+    do {                                                    \
+        if (fp.drop_scale != nullptr) TRIMUL_LAUNCH_TM2_FOLD(RES, KH, true); \
+        else TRIMUL_LAUNCH_TM2_FOLD(RES, KH, false);        \
     } while (0)
         if (kh == 2) {
-            if (residual != nullptr) TRIMUL_LAUNCH_TM2_FOLD(true, 2);
-            else TRIMUL_LAUNCH_TM2_FOLD(false, 2);
+            if (residual != nullptr) TRIMUL_LAUNCH_TM2_FOLD_RK(true, 2);
+            else TRIMUL_LAUNCH_TM2_FOLD_RK(false, 2);
         } else {
-            if (residual != nullptr) TRIMUL_LAUNCH_TM2_FOLD(true, 1);
-            else TRIMUL_LAUNCH_TM2_FOLD(false, 1);
+            if (residual != nullptr) TRIMUL_LAUNCH_TM2_FOLD_RK(true, 1);
+            else TRIMUL_LAUNCH_TM2_FOLD_RK(false, 1);
         }
+#undef TRIMUL_LAUNCH_TM2_FOLD_RK
 #undef TRIMUL_LAUNCH_TM2_FOLD
     }
     if (kh != 1) return TRIMUL_E_UNSUPPORTED;      // the in-place variant below is 128 hidden channels only
@@ -525,6 +598,41 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     if (!ensure_smem(tm2_sm100_kernel, kT2SmemBytes)) return TRIMUL_E_CUDA;
     tm2_sm100_kernel<<<grid, kT2Threads, kT2SmemBytes, st>>>(tmZ, tmWg, tmWo, tmOut, tmRes, tmTri, p);
     return launch_status();
+}
+
+// c = h = 256: weights streamed through shared memory (tm2_wide_sm100.cuh)
+int run_wide_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
+                 const void* residual, cudaStream_t st, int32_t* status) {
+    CUtensorMap tmZ, tmWg, tmWo, tmOut, tmTri;
+    const uint64_t dims[4] = {kW2C, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
+    const uint64_t strides[3] = {kW2C, (uint64_t)d->N * kW2C, (uint64_t)d->rows * d->N * kW2C};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    if (!encode_bf16(&tmZ, z, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmOut, out, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    const uint64_t wdims[2] = {kW2C, kW2C};
+    const uint64_t wstrides[1] = {kW2C};
+    const uint32_t wbox[2] = {64, 128};
+    if (!encode_bf16(&tmWg, w->w_gate, 2, wdims, wstrides, wbox, 128)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmWo, w->w_out, 2, wdims, wstrides, wbox, 128)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmTri, *tri, d->B * kW2C, 64, 1, 128)) return TRIMUL_E_CUDA;
+    Tm2WideParams wp = {};
+    Tm2Params& p = wp.base;
+    p.B = d->B; p.rows = d->rows; p.N = d->N;
+    p.tiles_per_row = (d->N + kT2P - 1) / kT2P;
+    const int64_t total = (int64_t)d->B * d->rows * p.tiles_per_row;
+    if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
+    p.total_tiles = (int)total;
+    p.gamma_in = w->ln_in_weight; p.beta_in = w->ln_in_bias;
+    p.gamma_out = w->ln_out_weight; p.beta_out = w->ln_out_bias;
+    p.eps_in = d->eps_in; p.eps_out = d->eps_out;
+    p.has_residual = residual != nullptr;
+    p.status = status;
+    wp.residual = static_cast<const __nv_bfloat16*>(residual);
+    wp.drop_scale = static_cast<const __nv_bfloat16*>(desc_drop_scale(d));
+    const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+    if (!ensure_smem(tm2_wide_sm100_kernel, kW2SmemBytes)) return TRIMUL_E_CUDA;
+    return launch_stage(tm2_wide_sm100_kernel, grid, kW2Threads, kW2SmemBytes, st, overlap_launches(d->flags), tmZ, tmWg,
+                        tmWo, tmOut, tmTri, wp);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -601,6 +709,7 @@ int trimul_b200_tm1(const trimul_desc* desc, const void* z, const uint8_t* mask,
                            ((reinterpret_cast<uintptr_t>(a->base) | reinterpret_cast<uintptr_t>(b->base)) & 127u) == 0;
     if (tensor_core_path(desc) && desc->c_hidden == 128 && chunks_ok)
         return run_fast_tm1(desc, z, mask, w, a, b, st, status);
+    if (wide_tensor_core_path(desc) && chunks_ok) return run_wide_tm1(desc, z, mask, w, a, b, st, status);
     const void* mats[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
     if (wmma_ok(desc, mats, 4)) return run_wmma_tm1(desc, z, mask, w, a, b, st);
     return run_plain_tm1<__nv_bfloat16>(desc, z, mask, w, a, b, st);
@@ -713,6 +822,7 @@ int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes*
         const bool folded_ok = (desc->flags & TRIMUL_FLAG_INPLACE_NORM_STAGE3) == 0 && (residual == nullptr || residual == z);
         if (!wide || folded_ok) return run_fast_tm2(desc, z, tri, w, out, residual, st, status);
     }
+    if (wide_tensor_core_path(desc) && plain_layout) return run_wide_tm2(desc, z, tri, w, out, residual, st, status);
     const void* mats[2] = {w->w_gate, w->w_out};
     if (wmma_ok(desc, mats, 2)) return run_wmma_tm2(desc, z, tri, w, out, residual, st);
     return run_plain_tm2<__nv_bfloat16>(desc, z, tri, w, out, residual, st);
