@@ -102,10 +102,12 @@ typedef struct trimul_desc {
                                 multiple of 8, at most 256; the reference module only ever builds
                                 h == c (reference.py:51-59), the functional op and the bidirectional
                                 block (bidirectional.py:73-84, where this field is 2 * d_hidden) also
-                                other widths.  The tcgen05 kernels cover c == 128 with h == 128
-                                (stage 1) and h == 128 or 256 (stage 3); other bf16 widths that are
+                                other widths.  tcgen05 kernels exist for bf16 with c == 128 (stage 1:
+                                h == 128; stage 3: h == 128 or 256) and, for the reference's d_pair
+                                sweep, c == h == 64 and c == h == 256; other bf16 widths that are
                                 multiples of 16 run that stage on warp-MMA kernels, the rest (and
-                                fp32) on CUDA-core kernels                                           */
+                                fp32) on CUDA-core kernels; the contraction is on tcgen05 at every
+                                bf16 width                                                          */
     int32_t  dtype;          /* TRIMUL_DTYPE_*                                                      */
     int32_t  direction;      /* TRIMUL_OUTGOING / TRIMUL_INCOMING                                   */
     int32_t  mask_kind;      /* TRIMUL_MASK_*                                                       */

@@ -28,6 +28,8 @@
 #include "tm2_fold_sm100.cuh"
 #include "tm1_wide_sm100.cuh"
 #include "tm2_wide_sm100.cuh"
+#include "tm1_narrow_sm100.cuh"
+#include "tm2_narrow_sm100.cuh"
 #include "wmma_kernels.cuh"
 
 using namespace trimul;
@@ -216,6 +218,12 @@ bool wide_tensor_core_path(const trimul_desc* d) {
            (d->flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0;
 }
 
+// bf16 with c = h = 64: the stacked-operand tensor-core kernels of stages 1 and 3
+bool narrow_tensor_core_path(const trimul_desc* d) {
+    return d->dtype == TRIMUL_DTYPE_BF16 && d->c == 64 && d->c_hidden == 64 &&
+           (d->flags & TRIMUL_FLAG_PLAIN_KERNELS) == 0;
+}
+
 int launch_status() { return cudaGetLastError() == cudaSuccess ? TRIMUL_OK : TRIMUL_E_CUDA; }
 
 // Launch of a tensor-core stage kernel.  `overlap` asks for programmatic dependent launch: the
@@ -373,6 +381,51 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     if (!ensure_smem(tm1_sm100_kernel<false>, kT1SmemBytes)) return TRIMUL_E_CUDA;
     return launch_stage(tm1_sm100_kernel<false>, grid, kT1Threads, kT1SmemBytes, st, overlap, tmZ, tmW[0], tmW[1],
                         tmW[2], tmW[3], tmA, tmB, p, scA, scB);
+}
+
+// c = h = 64: left and right weights stacked into one UMMA operand (tm1_narrow_sm100.cuh)
+int run_narrow_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const trimul_weights* w,
+                   const trimul_planes* a, const trimul_planes* b, cudaStream_t st, int32_t* status) {
+    const bool inc = d->direction == TRIMUL_INCOMING;
+    CUtensorMap tmZ, tmW[4], tmA, tmB;
+    {
+        const uint64_t dims[4] = {kN1C, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
+        const uint64_t strides[3] = {kN1C, (uint64_t)d->N * kN1C, (uint64_t)d->rows * d->N * kN1C};
+        const uint32_t box_out[4] = {64, 128, 1, 1};
+        const uint32_t box_in[4] = {64, 1, 128, 1};
+        if (!encode_bf16(&tmZ, z, 4, dims, strides, inc ? box_in : box_out, 128)) return TRIMUL_E_CUDA;
+    }
+    const void* ws[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
+    for (int m = 0; m < 4; ++m) {
+        const uint64_t dims[2] = {kN1C, kN1C};
+        const uint64_t strides[1] = {kN1C};
+        const uint32_t box[2] = {64, 64};
+        if (!encode_bf16(&tmW[m], ws[m], 2, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    }
+    const int planes = d->B * kN1C;
+    if (!encode_planes(&tmA, *a, planes, 64, 1, 64)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmB, *b, planes, 64, 1, 64)) return TRIMUL_E_CUDA;
+    Tm1Params p = {};
+    p.B = d->B; p.c = kN1C;
+    p.n_fixed = inc ? d->N : d->rows;
+    p.n_run = inc ? d->rows : d->N;
+    p.tiles_per_fixed = (p.n_run + kT1P - 1) / kT1P;
+    const int64_t total = (int64_t)d->B * p.n_fixed * p.tiles_per_fixed;
+    if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
+    p.total_tiles = (int)total;
+    p.incoming = inc;
+    p.N = d->N; p.row0 = d->row0;
+    p.mask_kind = mask ? d->mask_kind : 0;
+    p.mask = mask;
+    p.gamma = w->ln_in_weight; p.beta = w->ln_in_bias; p.eps = d->eps_in;
+    p.a_row_chunk = eff_chunk(a->row_chunk, a->rows); p.a_col_chunk = eff_chunk(a->col_chunk, a->cols);
+    p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
+    p.planes_per_dest = planes;
+    p.status = status;
+    const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+    if (!ensure_smem(tm1_narrow_sm100_kernel, kN1SmemBytes)) return TRIMUL_E_CUDA;
+    return launch_stage(tm1_narrow_sm100_kernel, grid, kN1Threads, kN1SmemBytes, st, overlap_launches(d->flags), tmZ,
+                        tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p);
 }
 
 // c = h = 256: weights streamed through shared memory (tm1_wide_sm100.cuh)
@@ -600,6 +653,43 @@ int run_fast_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, 
     return launch_status();
 }
 
+// c = h = 64 (tm2_narrow_sm100.cuh)
+int run_narrow_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
+                   const void* residual, cudaStream_t st, int32_t* status) {
+    CUtensorMap tmZ, tmWg, tmWo, tmOut, tmTri;
+    const uint64_t dims[4] = {kN2C, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
+    const uint64_t strides[3] = {kN2C, (uint64_t)d->N * kN2C, (uint64_t)d->rows * d->N * kN2C};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    if (!encode_bf16(&tmZ, z, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmOut, out, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    const uint64_t wdims[2] = {kN2C, kN2C};
+    const uint64_t wstrides[1] = {kN2C};
+    const uint32_t wbox[2] = {64, 64};
+    if (!encode_bf16(&tmWg, w->w_gate, 2, wdims, wstrides, wbox, 128)) return TRIMUL_E_CUDA;
+    if (!encode_bf16(&tmWo, w->w_out, 2, wdims, wstrides, wbox, 128)) return TRIMUL_E_CUDA;
+    if (!encode_planes(&tmTri, *tri, d->B * kN2C, 64, 1, 64)) return TRIMUL_E_CUDA;
+    CUtensorMap tmRes;
+    if (!encode_bf16(&tmRes, residual ? residual : z, 4, dims, strides, box, 128)) return TRIMUL_E_CUDA;
+    Tm2NarrowParams np = {};
+    Tm2Params& p = np.base;
+    p.B = d->B; p.rows = d->rows; p.N = d->N;
+    p.tiles_per_row = (d->N + kT2P - 1) / kT2P;
+    const int64_t total = (int64_t)d->B * d->rows * p.tiles_per_row;
+    if (total > 0x7fffffff) return TRIMUL_E_UNSUPPORTED;
+    p.total_tiles = (int)total;
+    p.gamma_in = w->ln_in_weight; p.beta_in = w->ln_in_bias;
+    p.gamma_out = w->ln_out_weight; p.beta_out = w->ln_out_bias;
+    p.eps_in = d->eps_in; p.eps_out = d->eps_out;
+    p.has_residual = residual != nullptr;
+    p.status = status;
+    np.residual = static_cast<const __nv_bfloat16*>(residual);
+    np.drop_scale = static_cast<const __nv_bfloat16*>(desc_drop_scale(d));
+    const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
+    if (!ensure_smem(tm2_narrow_sm100_kernel, kN2SmemBytes)) return TRIMUL_E_CUDA;
+    return launch_stage(tm2_narrow_sm100_kernel, grid, kN2Threads, kN2SmemBytes, st, overlap_launches(d->flags), tmZ,
+                        tmWg, tmWo, tmOut, tmTri, tmRes, np);
+}
+
 // c = h = 256: weights streamed through shared memory (tm2_wide_sm100.cuh)
 int run_wide_tm2(const trimul_desc* d, const void* z, const trimul_planes* tri, const trimul_weights* w, void* out,
                  const void* residual, cudaStream_t st, int32_t* status) {
@@ -710,6 +800,7 @@ int trimul_b200_tm1(const trimul_desc* desc, const void* z, const uint8_t* mask,
     if (tensor_core_path(desc) && desc->c_hidden == 128 && chunks_ok)
         return run_fast_tm1(desc, z, mask, w, a, b, st, status);
     if (wide_tensor_core_path(desc) && chunks_ok) return run_wide_tm1(desc, z, mask, w, a, b, st, status);
+    if (narrow_tensor_core_path(desc) && chunks_ok) return run_narrow_tm1(desc, z, mask, w, a, b, st, status);
     const void* mats[4] = {w->w_left, w->w_left_gate, w->w_right, w->w_right_gate};
     if (wmma_ok(desc, mats, 4)) return run_wmma_tm1(desc, z, mask, w, a, b, st);
     return run_plain_tm1<__nv_bfloat16>(desc, z, mask, w, a, b, st);
@@ -823,6 +914,7 @@ int trimul_b200_tm2(const trimul_desc* desc, const void* z, const trimul_planes*
         if (!wide || folded_ok) return run_fast_tm2(desc, z, tri, w, out, residual, st, status);
     }
     if (wide_tensor_core_path(desc) && plain_layout) return run_wide_tm2(desc, z, tri, w, out, residual, st, status);
+    if (narrow_tensor_core_path(desc) && plain_layout) return run_narrow_tm2(desc, z, tri, w, out, residual, st, status);
     const void* mats[2] = {w->w_gate, w->w_out};
     if (wmma_ok(desc, mats, 2)) return run_wmma_tm2(desc, z, tri, w, out, residual, st);
     return run_plain_tm2<__nv_bfloat16>(desc, z, tri, w, out, residual, st);
