@@ -100,7 +100,10 @@ PUBLISHED_TFLOPS = {k: WORKLOADS[k][0] * (2.0 * WORKLOADS[k][1] ** 3 * WORKLOADS
 # DRAM bytes per launch measured with ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the
 # n768_outgoing workload, as multiples of S = B*N*N*c*2 bytes; other sizes are scaled by S
 # (all three kernels stream their operands once, so traffic grows in proportion).
-NCU_TRAFFIC_PER_S = {"tm1": 2.62, "contract": 2.82, "tm2": 2.77}
+NCU_TRAFFIC_PER_S = {"tm1": 2.62, "contract": 2.81, "tm2": 2.77}
+# c = 256 kernels: captured at N=384 only (profiles/ncu_full_n384_c256_wide_stage1_stage3.md), where
+# part of the operands stay in L2 between the stages, so these bytes are quoted for that workload only
+NCU_TRAFFIC_BYTES = {"n384_outgoing_c256": {"tm1": 169.6e6, "contract": None, "tm2": 193.1e6}}
 
 
 def block_flops(B, N, c):
@@ -493,7 +496,8 @@ def run_b200(args):
         for k, v in stage_info.items():
             v["frac"] = v["achieved"] / v["peak"]
             # bytes per launch, from the ncu capture of the c = 128 kernels (none for the other widths)
-            v["traffic"] = NCU_TRAFFIC_PER_S[k] * S_bytes if c == 128 else None
+            v["traffic"] = (NCU_TRAFFIC_PER_S[k] * S_bytes if c == 128 else
+                            NCU_TRAFFIC_BYTES.get(args.workload, {}).get(k))
         dom = max(stage_info, key=lambda k: stage_info[k]["ms"])
         roof = dict(stage_info[dom])
         roof.update(kernel=dom, peak_source=peaks["source"],

@@ -34,7 +34,7 @@ def find_nvcc() -> str:
     return nvcc
 
 
-def sources() -> list[str]:
+def sources() -> list[str]:  # microbench_sm100.cu is a separate program (build_microbench)
     return [os.path.join(CSRC, "trimul_api.cu")]
 
 
@@ -62,6 +62,24 @@ def build(force: bool = False, verbose: bool = False, extra: list[str] | None = 
     return LIB_PATH
 
 
+def build_microbench(verbose: bool = True) -> str:
+    """Compile ``csrc/microbench_sm100.cu`` (hardware micro-benchmarks behind the kernels' tile shapes)
+    into ``miniworld_engine_b200/microbench_sm100``; it is not part of the library."""
+    out = os.path.join(PKG_DIR, "microbench_sm100")
+    cmd = [find_nvcc(), "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-o", out,
+           os.path.join(CSRC, "microbench_sm100.cu")]
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError(f"nvcc failed with exit code {res.returncode}")
+    return out
+
+
 if __name__ == "__main__":
+    if "--microbench" in sys.argv:
+        print(build_microbench())
+        sys.exit(0)
     print(build(force="--force" in sys.argv, verbose=True,
                 extra=["-Xptxas", "-v"] if "--ptxas-v" in sys.argv else None))

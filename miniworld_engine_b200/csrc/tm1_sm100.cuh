@@ -23,13 +23,15 @@
 // All worker warps first halve the weight matrices in shared memory (exact in bf16), so the
 // accumulators hold p/2 and g/2 and p*sigmoid(g) = (p/2)*tanh(g/2) + p/2 is one MUFU + one FMA.
 //
-// What bounds the stage (measured on a B200): draining the accumulators (tcgen05.ld delivers about
-// 64 bytes per cycle and SM; p and g are 8 bytes per output, 2.1 us per tile), the UMMAs themselves
-// (a tcgen05.mma of this shape is bound by its operand fetch from shared memory, about 75 bytes per
-// cycle: 107 cycles each, 1.7 us per tile) and HBM (2.2 us per tile) are all of the same size, and
-// every warp of the CTA shares four schedulers, so the achieved tile period (3.1 us) is set by how
-// well these overlap, not by any one of them.  tm1_direct_sm100.cuh is the variant that halves
-// the number of UMMAs (N = 256) at the price of a thread-per-position epilogue; it is slower.
+// What bounds the stage (measured on a B200, csrc/microbench_sm100.cu): a tcgen05.mma of this shape
+// is bound by its operand fetch from shared memory (about 75 bytes per cycle: 107 cycles instead of
+// the ideal 64, 1.7 us of UMMAs per tile) and the z ring is only two tiles deep beside 128 KB of
+// weights, so the tile period is half the life of a ring slot — load (2.0 us under load), LayerNorm
+// (2.3 us), the UMMAs of both sides (2.0 us including their waits for the accumulators): 3.1 us
+// against 2.2 us for the HBM traffic of a tile.  Neither tensor memory reads (130-320 bytes per
+// cycle and SM) nor the hardware tanh (16 per cycle and SM, 1.0 us per tile) are the limit.
+// tm1_direct_sm100.cuh is the variant that halves the number of UMMAs (N = 256) and has a
+// three-deep ring at the price of a thread-per-position epilogue; it is slower.
 //
 // kScatter = true: the 128 channel planes of a tile are stored in segments of planes_per_dest
 // planes, segment k through destination map (first plane of the segment) / planes_per_dest — the

@@ -621,3 +621,20 @@ def test_contraction_refuses_a_ragged_last_k_chunk_on_the_tensor_cores(dev):
     ref = torch.einsum("pik,pjk->pij", a_d.float(), b_d.float())
     assert not torch.isnan(got).any()
     assert O.rel_rms(got.cpu(), ref.cpu()) <= 5e-3
+
+
+def test_serial_launch_gives_the_same_result(dev):
+    """Programmatic dependent launch only moves the start of a stage's set-up: with it (default) and
+    without it (TRIMUL_FLAG_SERIAL_LAUNCH) the block output is bit-identical, also when calls follow
+    each other back to back and reuse the same workspace."""
+    from miniworld_engine_b200 import read_status, trimul_forward
+    for c, N in ((128, 200), (256, 72), (64, 136)):
+        w = O.make_weights(c, 0, affine="random")
+        z = O.make_input(1, N, c, 1).bfloat16().to(dev)
+        m = O.make_token_mask(1, N, "tail9").to(dev)
+        kw = forward_kwargs(w, torch.bfloat16, dev)
+        outs = [trimul_forward(z, m, outgoing=(i % 2 == 0), **kw, residual=z) for i in range(6)]
+        for i, y in enumerate(outs):
+            y_serial = trimul_forward(z, m, outgoing=(i % 2 == 0), **kw, residual=z, serial_launch=True)
+            assert torch.equal(y, y_serial), (c, N, i)
+    assert read_status(dev)[0] == 0
