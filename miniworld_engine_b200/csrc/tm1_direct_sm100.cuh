@@ -307,14 +307,10 @@ tm1_direct_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_co
                 for (int e = 0; e < 4; ++e) {
                     const uint32_t w = gate2_bf16(__uint_as_float(rp[2 * e]), __uint_as_float(rg[2 * e]),
                                                   __uint_as_float(rp[2 * e + 1]), __uint_as_float(rg[2 * e + 1]));
-#ifdef TRIMUL_T1_NO_STORE
-                    if (valid && w == 0x12345678u) o[0] = (unsigned short)w;      // timing experiment: no stores
-#else
                     if (valid) {
                         o[(long long)(2 * e) * pstride] = (unsigned short)w;
                         o[(long long)(2 * e + 1) * pstride] = (unsigned short)(w >> 16);
                     }
-#endif
                 }
             };
             uint32_t rpA[8], rgA[8], rpB[8], rgB[8];
