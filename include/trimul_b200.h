@@ -69,12 +69,12 @@ extern "C" {
                                          (cross-checking aid; same layouts, same rounding points)   */
 #define TRIMUL_FLAG_SINGLE_CTA_CONTRACT 2u /* contraction on lone CTAs (128x256 tiles) instead of CTA
                                          pairs (256x256 tiles, cta_group::2); cross-checking aid    */
-#define TRIMUL_FLAG_DIRECT_STORE_STAGE1 4u /* stage 1 in its untransposed form (D[position][proj | gate],
-                                         8 UMMAs of full width per side instead of 16 narrower ones,
-                                         epilogue thread = position storing straight to global
-                                         memory) instead of the default kernel (D[channel][position],
-                                         results staged in shared memory and TMA-stored); same
-                                         results to the last bf16 bit of a few elements; slower     */
+#define TRIMUL_FLAG_SINGLE_CTA_STAGE1 4u /* stage 1 (c = 128) on lone CTAs (all four weight matrices and a
+                                         two-deep tile ring per SM) instead of CTA pairs (cta_group::2:
+                                         each CTA holds one side's weights and normalises half of a
+                                         tile); same arithmetic, results equal to the last bf16 bit of
+                                         a few elements; slower; the scattering entry point always
+                                         runs this form                                              */
 #define TRIMUL_FLAG_INPLACE_NORM_STAGE3 16u /* stage 3 with both LayerNorms applied in place in shared
                                          memory before the projections (rounds LN(x) to bf16 like the
                                          reference) instead of the default kernel, which folds them

@@ -23,7 +23,7 @@ OUTGOING, INCOMING = 0, 1
 MASK_NONE, MASK_TOKEN, MASK_PAIR = 0, 1, 2
 FLAG_PLAIN_KERNELS = 1
 FLAG_SINGLE_CTA_CONTRACT = 2
-FLAG_DIRECT_STORE_STAGE1 = 4
+FLAG_SINGLE_CTA_STAGE1 = 4
 FLAG_INPLACE_NORM_STAGE3 = 16
 FLAG_SERIAL_LAUNCH = 32
 

@@ -473,6 +473,13 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
+// The same with release semantics at CTA scope only (what the instruction defaults to): enough when
+// what the arrival publishes is this CTA's own shared or tensor memory, which the pair's UMMAs read in
+// place, and far cheaper than a cluster-scope release (measured: the latter costs a warp more than a
+// microsecond per arrival).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
 // TMA load of a CTA pair: data lands in this CTA, completion is signalled on `bar_cluster_addr`
 // (a shared::cluster address, here always the leader's barrier).  No multicast.
 __device__ __forceinline__ void tma_load_4d_pair(void* dst, const CUtensorMap* map, uint32_t bar_cluster_addr, int c0,

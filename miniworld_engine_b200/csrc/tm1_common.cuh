@@ -1,5 +1,5 @@
-// Constants and launch parameters shared by the stage-1 kernels (tm1_sm100.cuh, the default, and
-// tm1_direct_sm100.cuh, the thread-per-position variant).
+// Constants and launch parameters shared by the c = 128 stage-1 kernels (tm1_pair_sm100.cuh, the
+// default, and tm1_sm100.cuh, the lone-CTA form that also scatters).
 #pragma once
 
 #include "ptx_sm100.cuh"
@@ -11,17 +11,6 @@ constexpr int kT1P = 128;                 // positions per tile
 constexpr int kT1SubTile = 128 * 64 * 2;  // 16 KB: 128 rows x 64 bf16, one swizzle-row wide
 constexpr int kT1XBytes = 2 * kT1SubTile; // one z tile
 constexpr int kStageIdTm1 = 1;
-
-// Where one side's planes go (thread-per-position variant, which stores with plain pointers):
-// element (plane, r, q) of the logical [planes][rows][cols] array lies at
-//   base + (r / row_chunk) * chunk_stride + plane * plane_stride + (r % row_chunk) * pitch + q      (row-chunked)
-//   base + (q / col_chunk) * chunk_stride + plane * plane_stride + r * pitch + (q % col_chunk)      (col-chunked)
-// in elements (at most one of the two is chunked; an unchunked extent has chunk == extent).
-struct Tm1Dest {
-    __nv_bfloat16* base[8];   // one per destination buffer (index 0 only unless scattering)
-    long long plane_stride, chunk_stride;
-    int pitch, row_chunk, col_chunk;
-};
 
 struct Tm1Params {
     int B, c;
@@ -39,7 +28,6 @@ struct Tm1Params {
     int a_row_chunk, a_col_chunk, b_row_chunk, b_col_chunk;
     int planes_per_dest;  // scatter variants: planes of one destination (a multiple of 16; divides or is a multiple of 128)
     int32_t* status;
-    Tm1Dest dest[2];      // a, b (thread-per-position variant only)
 };
 
 }  // namespace trimul

@@ -13,11 +13,11 @@
 //   warp 0        TMA producer: the four weight matrices once, then z tiles into a 2-stage ring
 //   warp 1        UMMA issuer: per tile, left pair (proj, gate) then right pair, 128x128x16 each,
 //                 into four 128-column TMEM accumulators
-//   warps 2..9    LayerNorm: two groups of four warps on alternate tiles, one thread per position
-//                 normalises its 128 channels in place inside
-//                 the swizzled tile (the TMA SWIZZLE_128B image is the UMMA K-major layout) and
-//                 round to bf16; a masked position is written as a zero row, which makes both
-//                 projections of that position exactly zero, so the epilogue needs no mask
+//   warps 2..9    LayerNorm: two groups of four warps on alternate tiles, eight lanes per position,
+//                 normalise the 128 channels in place inside the swizzled tile (the TMA SWIZZLE_128B
+//                 image is the UMMA K-major layout) and round to bf16; a masked position is written
+//                 as a zero row, which makes both projections of that position exactly zero, so the
+//                 epilogue needs no mask
 //   warps 10..13  epilogue of the left side, warps 14..17 of the right side:
 //                 TMEM -> p * sigmoid(g) -> bf16 -> swizzled staging -> TMA store
 // All worker warps first halve the weight matrices in shared memory (exact in bf16), so the
@@ -54,13 +54,11 @@ constexpr int kT1XStages = 2;
 constexpr int kT1StagingBytes = 2 * kT1SubTile;   // one [128 channels][64 positions] store box per side
 constexpr int kT1OffX = kT1WBytes;
 constexpr int kT1OffStaging = kT1OffX + kT1XStages * kT1XBytes;
-constexpr int kT1OffAffine = kT1OffStaging + kT1StagingBytes;      // gamma[128], beta[128] fp32
-constexpr int kT1OffBars = kT1OffAffine + 2 * kT1C * 4;
+constexpr int kT1OffBars = kT1OffStaging + kT1StagingBytes;
 constexpr int kT1SmemBytes = kT1OffBars + 192;
 constexpr int kT1LnBarrier = 2;
 constexpr int kT1EpiBarrier = 3;       // 3: left side, 4: right side
 constexpr int kT1LnBarrier2 = 5;       // second LayerNorm group
-constexpr int kT1AffineBarrier = 6;    // all LayerNorm warps, once
 
 template <bool kScatter>
 __global__ void __launch_bounds__(kT1Threads, 1)
@@ -77,8 +75,6 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     uint8_t* sW = smem;
     uint8_t* sX = smem + kT1OffX;
     uint8_t* sOut = smem + kT1OffStaging;
-    float* sGamma = reinterpret_cast<float*>(smem + kT1OffAffine);
-    float* sBeta = sGamma + kT1C;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kT1OffBars);
     uint64_t* w_full = bars;            // weights landed
     uint64_t* x_full = bars + 1;        // [2] z tile landed
@@ -122,15 +118,6 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     // predecessor in the stream may have written.
     griddep_wait();
     griddep_launch_dependents();
-
-    if (warp >= 2 && warp < 10) {
-        // the LayerNorm warps bring gamma and beta into shared memory for themselves
-        if (threadIdx.x < 64 + kT1C) {
-            sGamma[threadIdx.x - 64] = p.gamma[threadIdx.x - 64];
-            sBeta[threadIdx.x - 64] = p.beta[threadIdx.x - 64];
-        }
-        named_barrier_sync(kT1AffineBarrier, kT1LnThreads);
-    }
 
     if (warp >= 2) {
         // every worker thread: halve its share of the weights once they have landed
@@ -211,33 +198,57 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
     } else if (warp < 10) {
         // ------------------------------------------------------------------ LayerNorm (+ mask)
         // two groups of four warps; group g takes the tiles with (local tile index & 1) == g, which
-        // are the ones in stage g; one thread per position
+        // are the ones in stage g; warp lw of a group owns rows [32 lw, 32 lw + 32): lane l row
+        // 32 lw + 4 i + (l >> 3) in iteration i, 16-byte chunk l & 7 of both 64-channel sub-tiles
+        // (the same summation order as the CTA-pair kernel, so the two give identical results)
         const int g = (warp - 2) >> 2;
-        const int pos = threadIdx.x - 64 - g * 128;    // 0..127, row of the tile
+        const int lw = (warp - 2) & 3;
+        const int rr = lane >> 3;
+        const int j = lane & 7;
         const int bar_id = g == 0 ? kT1LnBarrier : kT1LnBarrier2;
+        f32x2 gb[16];
+        {
+            const float4 g0 = __ldg(reinterpret_cast<const float4*>(p.gamma + 8 * j));
+            const float4 g1 = __ldg(reinterpret_cast<const float4*>(p.gamma + 8 * j + 4));
+            const float4 g2 = __ldg(reinterpret_cast<const float4*>(p.gamma + 64 + 8 * j));
+            const float4 g3 = __ldg(reinterpret_cast<const float4*>(p.gamma + 64 + 8 * j + 4));
+            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.beta + 8 * j));
+            const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.beta + 8 * j + 4));
+            const float4 b2 = __ldg(reinterpret_cast<const float4*>(p.beta + 64 + 8 * j));
+            const float4 b3 = __ldg(reinterpret_cast<const float4*>(p.beta + 64 + 8 * j + 4));
+            gb[0] = f2_pack(g0.x, g0.y); gb[1] = f2_pack(g0.z, g0.w); gb[2] = f2_pack(g1.x, g1.y); gb[3] = f2_pack(g1.z, g1.w);
+            gb[4] = f2_pack(g2.x, g2.y); gb[5] = f2_pack(g2.z, g2.w); gb[6] = f2_pack(g3.x, g3.y); gb[7] = f2_pack(g3.z, g3.w);
+            gb[8] = f2_pack(b0.x, b0.y); gb[9] = f2_pack(b0.z, b0.w); gb[10] = f2_pack(b1.x, b1.y); gb[11] = f2_pack(b1.z, b1.w);
+            gb[12] = f2_pack(b2.x, b2.y); gb[13] = f2_pack(b2.z, b2.w); gb[14] = f2_pack(b3.x, b3.y); gb[15] = f2_pack(b3.z, b3.w);
+        }
         uint32_t it = g;
         for (int tile = blockIdx.x + g * gridDim.x; tile < p.total_tiles; tile += 2 * gridDim.x, it += 2) {
             const uint32_t ph = (it >> 1) & 1u;
-            // pair-mask value of this position (independent of the tile data: do it first)
-            bool keep = true;
+            // pair-mask bits of this lane's eight rows (independent of the tile data: do it first)
+            uint32_t zero_bits = 0u;
             if (p.mask_kind != 0) {
                 const int t0 = (tile % p.tiles_per_fixed) * kT1P;
                 const int bf = tile / p.tiles_per_fixed;
                 const int f = bf % p.n_fixed;
                 const int b = bf / p.n_fixed;
-                const int run = t0 + pos;
-                keep = false;
-                if (run < p.n_run) {
-                    const int zr = p.row0 + (p.incoming ? run : f);   // global z row
-                    const int zc = p.incoming ? f : run;              // z column
-                    if (p.mask_kind == 1)
-                        keep = (p.mask[(size_t)b * p.N + zr] != 0) && (p.mask[(size_t)b * p.N + zc] != 0);
-                    else
-                        keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const int run = t0 + 32 * lw + 4 * i + rr;
+                    bool keep = false;
+                    if (run < p.n_run) {
+                        const int zr = p.row0 + (p.incoming ? run : f);   // global z row
+                        const int zc = p.incoming ? f : run;              // z column
+                        if (p.mask_kind == 1)
+                            keep = (p.mask[(size_t)b * p.N + zr] != 0) && (p.mask[(size_t)b * p.N + zc] != 0);
+                        else
+                            keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
+                    }
+                    if (!keep) zero_bits |= 1u << i;
                 }
             }
-            if (!group_wait(&x_full[g], ph, pos == 0, bar_id, 128, abort_flag, p.status, kStageIdTm1, 300 + g)) break;
-            ln_row_inplace(sX + g * kT1XBytes, kT1SubTile, pos, sGamma, sBeta, p.eps, !keep);
+            if (!group_wait(&x_full[g], ph, lw == 0 && lane == 0, bar_id, 128, abort_flag, p.status, kStageIdTm1, 300 + g))
+                break;
+            ln_rows_warp<8>(sX + g * kT1XBytes, kT1SubTile, 32 * lw, lane, gb, p.eps, zero_bits);
             fence_proxy_async_smem();   // normalised tile -> visible to the UMMA (async proxy)
             mbar_arrive(&xn_ready[g]);
         }

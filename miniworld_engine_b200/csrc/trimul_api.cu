@@ -23,7 +23,7 @@
 #include "peer_barrier.cuh"
 #include "plain_kernels.cuh"
 #include "tm1_sm100.cuh"
-#include "tm1_direct_sm100.cuh"
+#include "tm1_pair_sm100.cuh"
 #include "tm2_sm100.cuh"
 #include "tm2_fold_sm100.cuh"
 #include "tm1_wide_sm100.cuh"
@@ -335,31 +335,25 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     p.b_row_chunk = eff_chunk(b->row_chunk, b->rows); p.b_col_chunk = eff_chunk(b->col_chunk, b->cols);
     p.planes_per_dest = planes_per_dest;
     p.status = status;
-    const trimul_planes* sides[2] = {a, b};
-    for (int sd = 0; sd < 2; ++sd) {
-        Tm1Dest& dd = p.dest[sd];
-        for (int k = 0; k < 8; ++k)
-            dd.base[k] = static_cast<__nv_bfloat16*>(k < (n_dest > 0 ? n_dest : 1) ? sides[sd][k].base : nullptr);
-        dd.plane_stride = sides[sd]->plane_stride;
-        dd.chunk_stride = sides[sd]->chunk_stride;
-        dd.pitch = (int)sides[sd]->pitch;
-        dd.row_chunk = eff_chunk(sides[sd]->row_chunk, sides[sd]->rows);
-        dd.col_chunk = eff_chunk(sides[sd]->col_chunk, sides[sd]->cols);
-    }
     const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
     const bool overlap = overlap_launches(d->flags);
-    if ((d->flags & TRIMUL_FLAG_DIRECT_STORE_STAGE1) != 0) {
-        // variant: 8 UMMAs of full width per side, thread = position, direct global stores
-        if (n_dest > 0) {
-            if (!ensure_smem(tm1_direct_sm100_kernel<true>, kD1SmemBytes)) return TRIMUL_E_CUDA;
-            return launch_stage(tm1_direct_sm100_kernel<true>, grid, kD1Threads, kD1SmemBytes, st, overlap, tmZ, tmW[0],
-                                tmW[1], tmW[2], tmW[3], p);
-        }
-        if (!ensure_smem(tm1_direct_sm100_kernel<false>, kD1SmemBytes)) return TRIMUL_E_CUDA;
-        return launch_stage(tm1_direct_sm100_kernel<false>, grid, kD1Threads, kD1SmemBytes, st, overlap, tmZ, tmW[0],
-                            tmW[1], tmW[2], tmW[3], p);
+    if ((d->flags & TRIMUL_FLAG_SINGLE_CTA_STAGE1) == 0 && n_dest == 0 && sm_count() >= 2) {
+        // CTA pairs: each CTA holds one side's weights and normalises 64 positions of a tile
+        CUtensorMap tmZh, tmA, tmB;
+        const uint64_t dims[4] = {128, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
+        const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
+        const uint32_t box_out[4] = {64, 64, 1, 1};
+        const uint32_t box_in[4] = {64, 1, 64, 1};
+        if (!encode_bf16(&tmZh, z, 4, dims, strides, inc ? box_in : box_out, 128)) return TRIMUL_E_CUDA;
+        // one epilogue warp stores 64 positions x 32 planes
+        if (!encode_planes(&tmA, *a, planes, 64, 1, 32)) return TRIMUL_E_CUDA;
+        if (!encode_planes(&tmB, *b, planes, 64, 1, 32)) return TRIMUL_E_CUDA;
+        const int pairs = p.total_tiles < sm_count() / 2 ? p.total_tiles : sm_count() / 2;
+        if (!ensure_smem(tm1_pair_sm100_kernel, kP1SmemBytes)) return TRIMUL_E_CUDA;
+        return launch_stage(tm1_pair_sm100_kernel, 2 * pairs, kP1Threads, kP1SmemBytes, st, overlap, tmZh, tmW[0],
+                            tmW[1], tmW[2], tmW[3], tmA, tmB, p);
     }
-    // default: transposed projections, results staged in shared memory and TMA-stored
+    // lone CTAs: all four weight matrices per SM, results staged in shared memory and TMA-stored
     CUtensorMap tmA, tmB;
     ScatterMaps scA{}, scB{};
     if (n_dest > 0) {

@@ -97,14 +97,14 @@ def dense_to_planes(spec: PlaneSpec, dense: torch.Tensor) -> None:
         spec.buf[: P * spec.plane_stride].view(P, spec.rows, spec.pitch)[..., :spec.cols].copy_(dense)
 
 
-def _desc(x, N, outgoing, mask_kind, eps_in, eps_out, plain, row0, direct_store=False, inplace_norm=False,
+def _desc(x, N, outgoing, mask_kind, eps_in, eps_out, plain, row0, single_cta=False, inplace_norm=False,
           c_hidden=None, serial_launch=False):
     B, rows, _, c = x.shape
     return _lib.make_desc(B, N, c, c_hidden=c_hidden, dtype=_dtype_code(x),
                           direction=_lib.OUTGOING if outgoing else _lib.INCOMING, mask_kind=mask_kind,
                           eps_in=eps_in, eps_out=eps_out,
                           flags=(_lib.FLAG_PLAIN_KERNELS if plain else 0) |
-                          (_lib.FLAG_DIRECT_STORE_STAGE1 if direct_store else 0) |
+                          (_lib.FLAG_SINGLE_CTA_STAGE1 if single_cta else 0) |
                           (_lib.FLAG_INPLACE_NORM_STAGE3 if inplace_norm else 0) |
                           (_lib.FLAG_SERIAL_LAUNCH if serial_launch else 0),
                           rows=rows, row0=row0)
@@ -123,16 +123,16 @@ def _mask_arg(mask, B, N):
 
 
 def tm1(z_slab: torch.Tensor, mask, weights: dict, a: PlaneSpec, b: PlaneSpec, *, outgoing: bool,
-        row0: int = 0, eps: float = 1e-5, plain_kernels: bool = False, direct_store: bool = False,
+        row0: int = 0, eps: float = 1e-5, plain_kernels: bool = False, single_cta: bool = False,
         serial_launch: bool = False) -> None:
     """Stage 1 on a ``[B, rows, N, c]`` slab of z (rows ``row0 .. row0+rows`` of the grid).
-    ``direct_store`` selects the cross-checking variant of the tensor-core kernel;
+    ``single_cta`` selects the lone-CTA form of the tensor-core kernel instead of the CTA-pair one;
     ``serial_launch`` (on every stage) turns programmatic dependent launch off."""
     _require_cuda(z_slab, "z")
     B, rows, N, c = z_slab.shape
     kind, mask_u8 = _mask_arg(mask, B, N)
     hp = int(weights["w_left"].shape[0])      # operand planes per batch element (d_hidden)
-    d = _desc(z_slab, N, outgoing, kind, eps, eps, plain_kernels, row0, direct_store, c_hidden=hp,
+    d = _desc(z_slab, N, outgoing, kind, eps, eps, plain_kernels, row0, single_cta, c_hidden=hp,
               serial_launch=serial_launch)
     w, keep = _weights_struct(c, z_slab.dtype, device=z_slab.device, c_proj=hp,
                               c_hidden=int(weights["w_out"].shape[1]), **weights)
