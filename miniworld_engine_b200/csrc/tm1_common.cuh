@@ -30,4 +30,14 @@ struct Tm1Params {
     int32_t* status;
 };
 
+// Tile index -> (batch element, fixed index f, first running position t0); the running index is the
+// fast one.  (Walking the tiles from the end of the tensor, to start on whatever the previous kernel
+// left in L2, was measured and changed nothing.)
+__device__ __forceinline__ void tm1_decode_tile(const Tm1Params& p, int tile, int& b, int& f, int& t0) {
+    t0 = (tile % p.tiles_per_fixed) * kT1P;
+    const int bf = tile / p.tiles_per_fixed;
+    f = bf % p.n_fixed;
+    b = bf / p.n_fixed;
+}
+
 }  // namespace trimul

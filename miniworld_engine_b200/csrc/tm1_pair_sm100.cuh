@@ -151,10 +151,9 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 const int s = it % kP1Stages;
                 const uint32_t ph = (it / kP1Stages) & 1u;
                 if (!mbar_wait<true>(&x_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm1, 1100 + s)) break;
-                const int t0 = (tile % p.tiles_per_fixed) * kT1P + (int)rank * kP1HalfPos;
-                const int bf = tile / p.tiles_per_fixed;
-                const int f = bf % p.n_fixed;
-                const int b = bf / p.n_fixed;
+                int b, f, t0;
+                tm1_decode_tile(p, tile, b, f, t0);
+                t0 += (int)rank * kP1HalfPos;
                 if (is_leader) TRIMUL_STAMP(0, it, 0);
                 mbar_arrive_expect_tx(&x_full[s], kP1XBytes);
                 uint8_t* dst = sX + s * kP1XBytes;
@@ -233,10 +232,9 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             // pair-mask bits of this lane's four rows (independent of the tile data: do it first)
             uint32_t zero_bits = 0u;
             if (p.mask_kind != 0) {
-                const int t0 = (tile % p.tiles_per_fixed) * kT1P + (int)rank * kP1HalfPos;
-                const int bf = tile / p.tiles_per_fixed;
-                const int f = bf % p.n_fixed;
-                const int b = bf / p.n_fixed;
+                int b, f, t0;
+                tm1_decode_tile(p, tile, b, f, t0);
+                t0 += (int)rank * kP1HalfPos;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const int run = t0 + 16 * lw + 4 * i + rr;
@@ -281,10 +279,8 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         const uint32_t t_p = tmem_base + eb * 256 + half * 64 + ((uint32_t)(q * 32) << 16);
         uint32_t it = eb;
         for (int tile = cluster_id + (int)eb * num_clusters; tile < p.total_tiles; tile += 2 * num_clusters, it += 2) {
-            const int t0 = (tile % p.tiles_per_fixed) * kT1P;
-            const int bf = tile / p.tiles_per_fixed;
-            const int f = bf % p.n_fixed;
-            const int b = bf / p.n_fixed;
+            int b, f, t0;
+            tm1_decode_tile(p, tile, b, f, t0);
             bool ok = true;
             if (lane == 0) {
                 tma_store_wait_read<0>();              // this warp's previous store has read the box

@@ -141,10 +141,8 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                 const int s = it & 1;
                 const uint32_t ph = (it >> 1) & 1u;
                 if (!mbar_wait(&x_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm1, 100 + s)) break;
-                const int t0 = (tile % p.tiles_per_fixed) * kT1P;
-                const int bf = tile / p.tiles_per_fixed;
-                const int f = bf % p.n_fixed;
-                const int b = bf / p.n_fixed;
+                int b, f, t0;
+                tm1_decode_tile(p, tile, b, f, t0);
                 mbar_arrive_expect_tx(&x_full[s], kT1XBytes);
                 uint8_t* dst = sX + s * kT1XBytes;
                 // z viewed as (channel, column, row, batch); outgoing box = 128 columns of row f,
@@ -227,10 +225,8 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
             // pair-mask bits of this lane's eight rows (independent of the tile data: do it first)
             uint32_t zero_bits = 0u;
             if (p.mask_kind != 0) {
-                const int t0 = (tile % p.tiles_per_fixed) * kT1P;
-                const int bf = tile / p.tiles_per_fixed;
-                const int f = bf % p.n_fixed;
-                const int b = bf / p.n_fixed;
+                int b, f, t0;
+                tm1_decode_tile(p, tile, b, f, t0);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
                     const int run = t0 + 32 * lw + 4 * i + rr;
@@ -267,10 +263,8 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         const uint32_t t_p = tmem_base + side * 256 + ((uint32_t)(q * 32) << 16);
         uint32_t it = 0;
         for (int tile = blockIdx.x; tile < p.total_tiles; tile += gridDim.x, ++it) {
-            const int t0 = (tile % p.tiles_per_fixed) * kT1P;
-            const int bf = tile / p.tiles_per_fixed;
-            const int f = bf % p.n_fixed;
-            const int b = bf / p.n_fixed;
+            int b, f, t0;
+            tm1_decode_tile(p, tile, b, f, t0);
             if (!group_wait(&acc_full[side], it & 1u, leader, bar_id, kT1EpiThreads, abort_flag, p.status,
                             kStageIdTm1, 400 + side))
                 break;
