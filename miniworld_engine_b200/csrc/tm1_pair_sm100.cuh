@@ -50,6 +50,7 @@ constexpr int kP1OffStaging = kP1OffX + kP1Stages * kP1XBytes;
 constexpr int kP1OffBars = kP1OffStaging + kP1EpiWarps * kP1WarpBoxBytes;
 constexpr int kP1SmemBytes = kP1OffBars + 320;
 constexpr int kP1LnBarrier = 2;        // 2, 3: the two LayerNorm groups
+constexpr int kP1EpiBarrier = 4;       // 4, 5: the eight epilogue warps of accumulator set 0, 1
 static_assert(kP1SmemBytes <= 232448, "stage 1 shared memory exceeds the 227 KB a CTA may use");
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kP1Threads, 1)
@@ -263,7 +264,7 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         }
     } else {
         // ------------------------------------------------------------------ epilogue of this CTA's side
-        // Sixteen independent warps, no barrier between them.  Warp = (accumulator set eb, position half,
+        // Sixteen warps that meet only where a set's eight wait for its accumulators.  Warp = (accumulator set eb, position half,
         // TMEM lane quarter q): it drains 32 channels x 64 positions of every second tile into its own
         // 4 KB store box ([32 channels][64 positions], swizzled) and issues its own TMA store, so two
         // tiles are in the epilogue at any time and a slow warp delays nobody else.
@@ -281,12 +282,12 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         for (int tile = cluster_id + (int)eb * num_clusters; tile < p.total_tiles; tile += 2 * num_clusters, it += 2) {
             int b, f, t0;
             tm1_decode_tile(p, tile, b, f, t0);
-            bool ok = true;
-            if (lane == 0) {
-                tma_store_wait_read<0>();              // this warp's previous store has read the box
-                ok = mbar_wait<true>(&acc_full[eb], (it >> 1) & 1u, abort_flag, p.status, kStageIdTm1, 1400 + ew);
-            }
-            if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) break;
+            if (lane == 0) tma_store_wait_read<0>();   // this warp's previous store has read the box
+            // ONE thread of the set's eight warps polls (every poller costs the working warps issue slots);
+            // the others park at the set's named barrier
+            if (!group_wait<true>(&acc_full[eb], (it >> 1) & 1u, (ew & 7) == 0 && lane == 0, kP1EpiBarrier + (int)eb, 256,
+                                  abort_flag, p.status, kStageIdTm1, 1400 + (int)eb))
+                break;
             tcgen05_fence_after();
             if (ew == 0 && lane == 0 && is_leader) TRIMUL_STAMP(3, it, 0);
             // 8 positions at a time; the TMEM loads of the next 8 are in flight while the current 8 are
