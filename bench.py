@@ -354,6 +354,29 @@ def run_b200(args):
     if st[0] != 0:
         raise SystemExit(f"bench.py: device status {st}: a bounded wait expired, timing is invalid")
 
+    # each stage once more by itself: an L2 flush (a 256 MB fill) before every launch, which is also a
+    # pause — kernels repeated without one run 10-18 % slower on this part, as the sustained GEMM peak
+    # sits below the burst peak; the in-step durations above are what the roofline line uses
+    alone_ms = None
+    if rank == 0:
+        flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+        calls = (lambda: S.tm1(z, m, wd, a, b, outgoing=outgoing), lambda: S.contract(a, b, tri),
+                 lambda: S.tm2(z, tri, wd))
+        alone_ms = []
+        n_alone = max(5, min(args.steps, 20))
+        for fn in calls:
+            tot = 0.0
+            for _ in range(n_alone):
+                flush.zero_()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                fn()
+                e1.record()
+                torch.cuda.synchronize(dev)
+                tot += e0.elapsed_time(e1)
+            alone_ms.append(tot / n_alone)
+        del flush
+
     # the same step with the residual fused into the output stage (what the reference MODULE returns)
     step_res = lambda: step(residual=z)
     for _ in range(3):
@@ -499,8 +522,11 @@ def run_b200(args):
                     "unit": "GB/s", "peak": peaks["hbm_gbs"]},
         }
         stage_info["contract"]["frac_of_sustained"] = stage_info["contract"]["achieved"] / peaks["bf16_tflops_sustained"]
-        for k, v in stage_info.items():
+        for i, (k, v) in enumerate(stage_info.items()):
             v["frac"] = v["achieved"] / v["peak"]
+            if alone_ms is not None:      # the same launch by itself after an L2 flush
+                v["ms_alone"] = alone_ms[i]
+                v["frac_alone"] = v["frac"] * v["ms"] / alone_ms[i]
             # bytes per launch, from the ncu capture of the c = 128 kernels (none for the other widths)
             v["traffic"] = (NCU_TRAFFIC_PER_S[k] * S_bytes if c == 128 else
                             NCU_TRAFFIC_BYTES.get(args.workload, {}).get(k))

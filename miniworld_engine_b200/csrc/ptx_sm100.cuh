@@ -470,13 +470,10 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
     return r;
 }
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-// The same with release semantics at CTA scope only (what the instruction defaults to): enough when
-// what the arrival publishes is this CTA's own shared or tensor memory, which the pair's UMMAs read in
-// place, and far cheaper than a cluster-scope release (measured: the latter costs a warp more than a
-// microsecond per arrival).
+// Arrive on a barrier of the PEER CTA, with release semantics at CTA scope (what the instruction
+// defaults to).  That is enough when what the arrival publishes is this CTA's own shared or tensor
+// memory, which the pair's UMMAs read in place, and far cheaper than `.release.cluster`, which was
+// measured to hold the arriving warp for more than a microsecond.
 __device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }

@@ -132,7 +132,7 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         if (threadIdx.x == 64) {
             // one thread reports this CTA's weights to the leader's UMMA issuer
             mbar_wait<true>(w_ready, 0, abort_flag, p.status, kStageIdTm1, 1151);
-            mbar_arrive_cluster(map_to_cta(smem_u32(w_all), 0));
+            mbar_arrive_remote(map_to_cta(smem_u32(w_all), 0));
         }
         __syncwarp();
     }
@@ -148,13 +148,13 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 tma_load_2d(sW + (2 + kh) * kP1WSub, wg, w_full, kh * 64, 0);
             }
             uint32_t it = 0;
-            for (int tile = cluster_id; tile < p.total_tiles; tile += num_clusters, ++it) {
+            Tm1Cursor cur;
+            cur.init(p, cluster_id);
+            for (int tile = cluster_id; tile < p.total_tiles; tile += num_clusters, ++it, cur.next(p, 0)) {
                 const int s = it % kP1Stages;
                 const uint32_t ph = (it / kP1Stages) & 1u;
                 if (!mbar_wait<true>(&x_empty[s], ph ^ 1u, abort_flag, p.status, kStageIdTm1, 1100 + s)) break;
-                int b, f, t0;
-                tm1_decode_tile(p, tile, b, f, t0);
-                t0 += (int)rank * kP1HalfPos;
+                const int b = cur.b, f = cur.f, t0 = cur.t0() + (int)rank * kP1HalfPos;
                 if (is_leader) TRIMUL_STAMP(0, it, 0);
                 mbar_arrive_expect_tx(&x_full[s], kP1XBytes);
                 uint8_t* dst = sX + s * kP1XBytes;
@@ -227,34 +227,33 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             gb[12] = f2_pack(b2.x, b2.y); gb[13] = f2_pack(b2.z, b2.w); gb[14] = f2_pack(b3.x, b3.y); gb[15] = f2_pack(b3.z, b3.w);
         }
         uint32_t it = lg;
+        Tm1Cursor cur;
+        cur.init(p, cluster_id + lg * num_clusters);
+        // Pair mask: lane l < 16 looks up position 16 lw + l of the half tile — one or two byte loads,
+        // issued ONE TILE AHEAD so that their latency (the mask of a large pair tensor streams from L2
+        // or DRAM) hides behind the LayerNorm of the current tile — and a ballot hands every lane the
+        // bits of its own rows.
+        const int my_pos = (int)rank * kP1HalfPos + 16 * lw + lane;
+        bool keep_next = true;
+        if (p.mask_kind != 0 && lane < 16 && cluster_id + lg * num_clusters < p.total_tiles)
+            keep_next = tm1_keep(p, cur.b, cur.f, cur.t0() + my_pos);
         for (int tile = cluster_id + lg * num_clusters; tile < p.total_tiles; tile += 2 * num_clusters, it += 2) {
             const int s = it % kP1Stages;
             const uint32_t ph = (it / kP1Stages) & 1u;
-            // pair-mask bits of this lane's four rows (independent of the tile data: do it first)
-            uint32_t zero_bits = 0u;
-            if (p.mask_kind != 0) {
-                int b, f, t0;
-                tm1_decode_tile(p, tile, b, f, t0);
-                t0 += (int)rank * kP1HalfPos;
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int run = t0 + 16 * lw + 4 * i + rr;
-                    bool keep = false;
-                    if (run < p.n_run) {
-                        const int zr = p.row0 + (p.incoming ? run : f);   // global z row
-                        const int zc = p.incoming ? f : run;              // z column
-                        if (p.mask_kind == 1)
-                            keep = (p.mask[(size_t)b * p.N + zr] != 0) && (p.mask[(size_t)b * p.N + zc] != 0);
-                        else
-                            keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
-                    }
-                    if (!keep) zero_bits |= 1u << i;
-                }
-            }
+            const bool keep = keep_next;
+            cur.next(p, 1);
+            if (p.mask_kind != 0 && lane < 16 && tile + 2 * num_clusters < p.total_tiles)
+                keep_next = tm1_keep(p, cur.b, cur.f, cur.t0() + my_pos);
             // ONE thread of the group's four warps polls; the others park at the group's named barrier
             if (!group_wait<true>(&x_full[s], ph, lw == 0 && lane == 0, kP1LnBarrier + lg, 128, abort_flag, p.status,
                                   kStageIdTm1, 1300 + s))
                 break;
+            uint32_t zero_bits = 0u;
+            if (p.mask_kind != 0) {
+                const uint32_t drop = ~__ballot_sync(0xffffffffu, keep);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) zero_bits |= ((drop >> (4 * i + rr)) & 1u) << i;
+            }
             if (lw == 0 && lane == 0 && is_leader) TRIMUL_STAMP(2, it, 0);
             ln_rows_warp<4>(sX + s * kP1XBytes, kP1SubTile, 16 * lw, lane, gb, p.eps, zero_bits);
             fence_proxy_async_smem();   // normalised rows -> visible to the UMMA (async proxy)
@@ -279,9 +278,11 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         const int cc = is_leader ? p.a_col_chunk : p.b_col_chunk;
         const uint32_t t_p = tmem_base + eb * 256 + half * 64 + ((uint32_t)(q * 32) << 16);
         uint32_t it = eb;
-        for (int tile = cluster_id + (int)eb * num_clusters; tile < p.total_tiles; tile += 2 * num_clusters, it += 2) {
-            int b, f, t0;
-            tm1_decode_tile(p, tile, b, f, t0);
+        Tm1Cursor cur;
+        cur.init(p, cluster_id + (int)eb * num_clusters);
+        for (int tile = cluster_id + (int)eb * num_clusters; tile < p.total_tiles;
+             tile += 2 * num_clusters, it += 2, cur.next(p, 1)) {
+            const int b = cur.b, f = cur.f, t0 = cur.t0();
             if (lane == 0) tma_store_wait_read<0>();   // this warp's previous store has read the box
             // ONE thread of the set's eight warps polls (every poller costs the working warps issue slots);
             // the others park at the set's named barrier

@@ -222,28 +222,23 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         uint32_t it = g;
         for (int tile = blockIdx.x + g * gridDim.x; tile < p.total_tiles; tile += 2 * gridDim.x, it += 2) {
             const uint32_t ph = (it >> 1) & 1u;
-            // pair-mask bits of this lane's eight rows (independent of the tile data: do it first)
-            uint32_t zero_bits = 0u;
+            // pair-mask bits of this lane's eight rows (independent of the tile data: do it first).  Lane l
+            // looks up position 32 lw + l of the tile — one or two byte loads — and a ballot hands every
+            // lane the bits of its own rows.
+            bool keep = true;
             if (p.mask_kind != 0) {
                 int b, f, t0;
                 tm1_decode_tile(p, tile, b, f, t0);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    const int run = t0 + 32 * lw + 4 * i + rr;
-                    bool keep = false;
-                    if (run < p.n_run) {
-                        const int zr = p.row0 + (p.incoming ? run : f);   // global z row
-                        const int zc = p.incoming ? f : run;              // z column
-                        if (p.mask_kind == 1)
-                            keep = (p.mask[(size_t)b * p.N + zr] != 0) && (p.mask[(size_t)b * p.N + zc] != 0);
-                        else
-                            keep = p.mask[((size_t)b * p.N + zr) * p.N + zc] != 0;
-                    }
-                    if (!keep) zero_bits |= 1u << i;
-                }
+                keep = tm1_keep(p, b, f, t0 + 32 * lw + lane);
             }
             if (!group_wait(&x_full[g], ph, lw == 0 && lane == 0, bar_id, 128, abort_flag, p.status, kStageIdTm1, 300 + g))
                 break;
+            uint32_t zero_bits = 0u;
+            if (p.mask_kind != 0) {
+                const uint32_t drop = ~__ballot_sync(0xffffffffu, keep);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) zero_bits |= ((drop >> (4 * i + rr)) & 1u) << i;
+            }
             ln_rows_warp<8>(sX + g * kT1XBytes, kT1SubTile, 32 * lw, lane, gb, p.eps, zero_bits);
             fence_proxy_async_smem();   // normalised tile -> visible to the UMMA (async proxy)
             mbar_arrive(&xn_ready[g]);

@@ -349,6 +349,10 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
         if (!encode_planes(&tmA, *a, planes, 64, 1, 32)) return TRIMUL_E_CUDA;
         if (!encode_planes(&tmB, *b, planes, 64, 1, 32)) return TRIMUL_E_CUDA;
         const int pairs = p.total_tiles < sm_count() / 2 ? p.total_tiles : sm_count() / 2;
+        for (int k = 0; k < 2; ++k) {
+            p.step_q[k] = (k + 1) * pairs / p.tiles_per_fixed;
+            p.step_r[k] = (k + 1) * pairs % p.tiles_per_fixed;
+        }
         if (!ensure_smem(tm1_pair_sm100_kernel, kP1SmemBytes)) return TRIMUL_E_CUDA;
         return launch_stage(tm1_pair_sm100_kernel, 2 * pairs, kP1Threads, kP1SmemBytes, st, overlap, tmZh, tmW[0],
                             tmW[1], tmW[2], tmW[3], tmA, tmB, p);
