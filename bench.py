@@ -282,6 +282,9 @@ def run_b200(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # stdout carries the one JSON line and nothing else: the collective library's own messages
+        # (its version banner, anything NCCL_DEBUG asks for) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
     B, N, c, outgoing, mask_kind = WORKLOADS[args.workload]
@@ -803,6 +806,9 @@ def run_sharded_pair(args):
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
+        # stdout carries the one JSON line and nothing else: the collective library's own messages
+        # (its version banner, anything NCCL_DEBUG asks for) go to stderr
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
     elif args.shard_mode == "peer":
         dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29533", rank=0, world_size=1, device_id=dev)

@@ -31,17 +31,20 @@ __device__ __forceinline__ void report_timeout(int32_t* status, int stage, int d
 
 // ---------------------------------------------------------------------------------------
 // optional timeline tracing (compiled in only with -DTRIMUL_TRACE): block 0 stamps the global
-// nanosecond timer for local tile indices 8..23 into a device array that a debug entry point
+// nanosecond timer for sixteen local tile indices (from 8 unless TRIMUL_TRACE_FIRST says otherwise) into a device array that a debug entry point
 // copies out.  Layout: [role][tile - 8][event], 8 roles x 16 tiles x 4 events.
 // ---------------------------------------------------------------------------------------
 #ifdef TRIMUL_TRACE
+#ifndef TRIMUL_TRACE_FIRST
+#define TRIMUL_TRACE_FIRST 8u
+#endif
 __device__ unsigned long long g_trace[8 * 16 * 4];
 #define TRIMUL_STAMP(role, it, ev)                                                             \
     do {                                                                                       \
-        if (blockIdx.x == 0 && (it) >= 8u && (it) < 24u) {                                     \
+        if (blockIdx.x == 0 && (it) >= TRIMUL_TRACE_FIRST && (it) < TRIMUL_TRACE_FIRST + 16u) { \
             unsigned long long t_;                                                             \
             asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                             \
-            g_trace[((role) * 16 + ((it) - 8u)) * 4 + (ev)] = t_;                              \
+            g_trace[((role) * 16 + ((it) - TRIMUL_TRACE_FIRST)) * 4 + (ev)] = t_;              \
         }                                                                                      \
     } while (0)
 #else

@@ -82,6 +82,7 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) TRIMUL_STAMP(7, TRIMUL_TRACE_FIRST, 0);
     const uint32_t rank = cluster_ctarank();             // 0 = leader = left side, 1 = right side
     const bool is_leader = rank == 0;
 
@@ -117,6 +118,7 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
     // predecessor in the stream may have written.
     griddep_wait();
     griddep_launch_dependents();
+    if (threadIdx.x == 0) TRIMUL_STAMP(7, TRIMUL_TRACE_FIRST, 1);
 
     // pair tiles: 128 positions (this CTA: 64 of them) along the running index
     const int cluster_id = blockIdx.x >> 1;
@@ -172,6 +174,7 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
         if (lane == 0 && is_leader) {
             constexpr uint32_t idesc = umma_idesc_bf16(256, 128);
             bool ok = mbar_wait<true>(w_all, 0, abort_flag, p.status, kStageIdTm1, 1200);
+            TRIMUL_STAMP(7, TRIMUL_TRACE_FIRST, 2);
             tcgen05_fence_after();
             const uint32_t wp = smem_u32(sW), wg = smem_u32(sW + 2 * kP1WSub);
             uint32_t it = 0;
