@@ -133,7 +133,7 @@ class ClockSampler:
     """SM clock and throttle reasons sampled through NVML (read-only queries) from a
     background thread while the timed region runs."""
 
-    def __init__(self, gpu_index: int, period_s: float = 0.001):
+    def __init__(self, gpu_index: int, period_s: float = 0.005):
         import threading
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -339,12 +339,21 @@ def run_b200(args):
         barrier()
         return t0.elapsed_time(t1)
 
+    # the clock sampler and the first collective (communicator set-up) start BEFORE the warm-up steps, so
+    # that their start-up cost on the host — on an 8-GPU node it was seen to double the first timed
+    # region of a short run — falls into the warm-up and not into the timed region
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    barrier()
     for _ in range(max(args.warmup, 3)):
         step()
     barrier()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
     # the timed region: exactly K steps, stages launched back to back
     total_ms = timed(step, args.steps)
+    rank_ms = None
+    if world > 1:      # every rank's own figure beside the maximum, so that a straggler shows
+        g = [torch.zeros(1, device=dev, dtype=torch.float64) for _ in range(world)]
+        dist.all_gather(g, torch.tensor([total_ms / args.steps], device=dev, dtype=torch.float64))
+        rank_ms = [float(v) for v in torch.cat(g).cpu()]
     # the same K steps again with events between the stages (per-stage durations for the roofline)
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     barrier()
@@ -368,6 +377,7 @@ def run_b200(args):
         alone_ms = []
         n_alone = max(5, min(args.steps, 20))
         for fn in calls:
+            fn()                      # (a variant without the residual may not have run yet: module load)
             tot = 0.0
             for _ in range(n_alone):
                 flush.zero_()
@@ -553,6 +563,7 @@ def run_b200(args):
             "cuda_graph_replay": {"ms_per_step": graph_ms, "value": flops * world / (graph_ms * 1e-3) / 1e12,
                                   "unit": UNIT, "what": "the with_residual step captured once and replayed"},
             "staged_ms_per_step": staged_ms,
+            "rank_ms_per_step": rank_ms,
             "dtype": "bf16",
             "data": "synthetic (seeded randn pair tensor and weights, all-ones LayerNorm gamma)",
             "frac_of_bf16_peak": value / world / peaks["bf16_tflops"],
