@@ -732,61 +732,92 @@ __device__ __forceinline__ void ln_row_inplace(uint8_t* tile, int sub_bytes, int
 }
 
 // ---------------------------------------------------------------------------------------
-// LayerNorm of 4 * kIters consecutive rows (first row `row0`, a multiple of 8) of a
-// [128 rows][128 channels] tile by ONE WARP, in place, same tile layout as above.  Eight lanes
-// share a row: lane l works on row row0 + 4 i + (l >> 3) in iteration i and owns 16-byte chunk
-// l & 7 of both sub-tiles, i.e. channels [8 j, 8 j + 8) and [64 + 8 j, 64 + 8 j + 8), j = l & 7.
-// Every value is read from shared memory ONCE and stays in registers between the statistics and
-// the normalisation; gamma and beta of the lane's 16 channels live in registers (`gb`: gamma
-// pairs [0,8), beta pairs [8,16)), so no affine vector is fetched per row; the row sums are
-// combined by a three-step butterfly over the eight lanes.  A quarter warp reads or writes one
-// whole 128-byte swizzled row segment: conflict-free.  Bit i of `zero_bits` set -> the lane's
-// row of iteration i is a masked position and is written as zeros.
+// LayerNorm of 4 * kIters consecutive rows (first row `row0`, a multiple of 8) of a tile of
+// 64 * kSub channels (kSub swizzled 64-channel sub-tiles, `sub_bytes` apart) by ONE WARP, in place.
+// Eight lanes share a row: lane l works on row row0 + 4 i + (l >> 3) in iteration i and owns 16-byte
+// chunk l & 7 of every sub-tile, i.e. channels [64 s + 8 j, 64 s + 8 j + 8), j = l & 7.  Every value
+// is read from shared memory ONCE and stays in registers between the statistics and the
+// normalisation; gamma and beta of the lane's channels live in registers (`gb`: gamma pairs
+// [0, 4 kSub), beta pairs [4 kSub, 8 kSub), see ln_load_affine), so no affine vector is fetched per
+// row; the row sums are combined by a three-step butterfly over the eight lanes.  A quarter warp
+// reads or writes one whole 128-byte swizzled row segment: conflict-free.  Bit i of `zero_bits` set
+// -> the lane's row of iteration i is a masked position and is written as zeros.
 // ---------------------------------------------------------------------------------------
-template <int kIters>
-__device__ __forceinline__ void ln_rows_warp(uint8_t* tile, int sub_bytes, int row0, int lane, const f32x2 (&gb)[16],
-                                             float eps, uint32_t zero_bits) {
+template <int kIters, int kSub = 2>
+__device__ __forceinline__ void ln_rows_warp(uint8_t* tile, int sub_bytes, int row0, int lane,
+                                             const f32x2 (&gb)[8 * kSub], float eps, uint32_t zero_bits) {
     const int rr = lane >> 3;
     const uint32_t j = (uint32_t)lane & 7u;
+    constexpr float kInvC = 1.0f / (64.0f * kSub);
 #pragma unroll 2
     for (int i = 0; i < kIters; ++i) {
         const int r = row0 + 4 * i + rr;
         const uint32_t off = (uint32_t)r * 128u + ((j ^ ((uint32_t)r & 7u)) << 4);
-        uint4* p0 = reinterpret_cast<uint4*>(tile + off);
-        uint4* p1 = reinterpret_cast<uint4*>(tile + sub_bytes + off);
-        const uint4 v0 = *p0, v1 = *p1;
+        uint4 v[kSub];
+#pragma unroll
+        for (int s = 0; s < kSub; ++s) v[s] = *reinterpret_cast<const uint4*>(tile + s * sub_bytes + off);
         // common shift of the row: its channel 0 (held by the lane with j == 0)
-        const float shift = bf16_lo(__shfl_sync(0xffffffffu, v0.x, lane & 24));
+        const float shift = bf16_lo(__shfl_sync(0xffffffffu, v[0].x, lane & 24));
         const f32x2 ns = f2_pack(-shift, -shift);
-        f32x2 d[8];
-        d[0] = f2_add(f2_from_bf16x2(v0.x), ns); d[1] = f2_add(f2_from_bf16x2(v0.y), ns);
-        d[2] = f2_add(f2_from_bf16x2(v0.z), ns); d[3] = f2_add(f2_from_bf16x2(v0.w), ns);
-        d[4] = f2_add(f2_from_bf16x2(v1.x), ns); d[5] = f2_add(f2_from_bf16x2(v1.y), ns);
-        d[6] = f2_add(f2_from_bf16x2(v1.z), ns); d[7] = f2_add(f2_from_bf16x2(v1.w), ns);
-        const f32x2 sa = f2_add(f2_add(d[0], d[1]), f2_add(d[2], d[3]));
-        const f32x2 sb = f2_add(f2_add(d[4], d[5]), f2_add(d[6], d[7]));
-        const f32x2 qa = f2_fma(d[0], d[0], f2_fma(d[1], d[1], f2_fma(d[2], d[2], f2_fma(d[3], d[3], 0ull))));
-        const f32x2 qb = f2_fma(d[4], d[4], f2_fma(d[5], d[5], f2_fma(d[6], d[6], f2_fma(d[7], d[7], 0ull))));
-        float t1 = f2_hsum(f2_add(sa, sb)), t2 = f2_hsum(f2_add(qa, qb));
+        f32x2 d[4 * kSub];
+#pragma unroll
+        for (int s = 0; s < kSub; ++s) {
+            d[4 * s + 0] = f2_add(f2_from_bf16x2(v[s].x), ns);
+            d[4 * s + 1] = f2_add(f2_from_bf16x2(v[s].y), ns);
+            d[4 * s + 2] = f2_add(f2_from_bf16x2(v[s].z), ns);
+            d[4 * s + 3] = f2_add(f2_from_bf16x2(v[s].w), ns);
+        }
+        // per 64-channel sub-tile: a short sum tree and a four-deep FMA chain, then the sub-tiles added up
+        // (for two sub-tiles this is the order (s0 + s1), the same in every kernel that normalises 128 channels)
+        f32x2 sum = 0ull, sq = 0ull;
+#pragma unroll
+        for (int s = 0; s < kSub; ++s) {
+            const f32x2 sa = f2_add(f2_add(d[4 * s], d[4 * s + 1]), f2_add(d[4 * s + 2], d[4 * s + 3]));
+            const f32x2 qa = f2_fma(d[4 * s], d[4 * s],
+                                    f2_fma(d[4 * s + 1], d[4 * s + 1],
+                                           f2_fma(d[4 * s + 2], d[4 * s + 2], f2_fma(d[4 * s + 3], d[4 * s + 3], 0ull))));
+            sum = s == 0 ? sa : f2_add(sum, sa);
+            sq = s == 0 ? qa : f2_add(sq, qa);
+        }
+        float t1 = f2_hsum(sum), t2 = f2_hsum(sq);
 #pragma unroll
         for (int o = 4; o >= 1; o >>= 1) {
             t1 += __shfl_xor_sync(0xffffffffu, t1, o);
             t2 += __shfl_xor_sync(0xffffffffu, t2, o);
         }
-        const float m1 = t1 * (1.0f / 128.0f);
-        const float var = fmaxf(fmaf(-m1, m1, t2 * (1.0f / 128.0f)), 0.f);
+        const float m1 = t1 * kInvC;
+        const float var = fmaxf(fmaf(-m1, m1, t2 * kInvC), 0.f);
         const float rstd = rsqrtf(var + eps);
         const float nm = -m1 * rstd;                       // y = d * rstd + nm
         const f32x2 r2 = f2_pack(rstd, rstd), n2 = f2_pack(nm, nm);
-        uint32_t o[8];
+        const bool zero = (zero_bits >> i) & 1u;
 #pragma unroll
-        for (int k = 0; k < 8; ++k) o[k] = f2_to_bf16x2(f2_fma(f2_fma(d[k], r2, n2), gb[k], gb[8 + k]));
-        if ((zero_bits >> i) & 1u) {
+        for (int s = 0; s < kSub; ++s) {
+            uint32_t o[4];
 #pragma unroll
-            for (int k = 0; k < 8; ++k) o[k] = 0u;
+            for (int k = 0; k < 4; ++k)
+                o[k] = zero ? 0u
+                            : f2_to_bf16x2(f2_fma(f2_fma(d[4 * s + k], r2, n2), gb[4 * s + k], gb[4 * kSub + 4 * s + k]));
+            *reinterpret_cast<uint4*>(tile + s * sub_bytes + off) = make_uint4(o[0], o[1], o[2], o[3]);
         }
-        *p0 = make_uint4(o[0], o[1], o[2], o[3]);
-        *p1 = make_uint4(o[4], o[5], o[6], o[7]);
+    }
+}
+
+// gamma and beta of a lane's channels for ln_rows_warp, from global memory: lane chunk j = lane & 7 owns
+// channels [64 s + 8 j, 64 s + 8 j + 8) of every sub-tile s.
+template <int kSub>
+__device__ __forceinline__ void ln_load_affine(f32x2 (&gb)[8 * kSub], const float* gamma, const float* beta, int lane) {
+    const int j = lane & 7;
+#pragma unroll
+    for (int s = 0; s < kSub; ++s) {
+        const float4 g0 = __ldg(reinterpret_cast<const float4*>(gamma + 64 * s + 8 * j));
+        const float4 g1 = __ldg(reinterpret_cast<const float4*>(gamma + 64 * s + 8 * j + 4));
+        const float4 b0 = __ldg(reinterpret_cast<const float4*>(beta + 64 * s + 8 * j));
+        const float4 b1 = __ldg(reinterpret_cast<const float4*>(beta + 64 * s + 8 * j + 4));
+        gb[4 * s + 0] = f2_pack(g0.x, g0.y); gb[4 * s + 1] = f2_pack(g0.z, g0.w);
+        gb[4 * s + 2] = f2_pack(g1.x, g1.y); gb[4 * s + 3] = f2_pack(g1.z, g1.w);
+        gb[4 * kSub + 4 * s + 0] = f2_pack(b0.x, b0.y); gb[4 * kSub + 4 * s + 1] = f2_pack(b0.z, b0.w);
+        gb[4 * kSub + 4 * s + 2] = f2_pack(b1.x, b1.y); gb[4 * kSub + 4 * s + 3] = f2_pack(b1.z, b1.w);
     }
 }
 

@@ -202,23 +202,9 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         const int g = (warp - 2) >> 2;
         const int lw = (warp - 2) & 3;
         const int rr = lane >> 3;
-        const int j = lane & 7;
         const int bar_id = g == 0 ? kT1LnBarrier : kT1LnBarrier2;
         f32x2 gb[16];
-        {
-            const float4 g0 = __ldg(reinterpret_cast<const float4*>(p.gamma + 8 * j));
-            const float4 g1 = __ldg(reinterpret_cast<const float4*>(p.gamma + 8 * j + 4));
-            const float4 g2 = __ldg(reinterpret_cast<const float4*>(p.gamma + 64 + 8 * j));
-            const float4 g3 = __ldg(reinterpret_cast<const float4*>(p.gamma + 64 + 8 * j + 4));
-            const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.beta + 8 * j));
-            const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.beta + 8 * j + 4));
-            const float4 b2 = __ldg(reinterpret_cast<const float4*>(p.beta + 64 + 8 * j));
-            const float4 b3 = __ldg(reinterpret_cast<const float4*>(p.beta + 64 + 8 * j + 4));
-            gb[0] = f2_pack(g0.x, g0.y); gb[1] = f2_pack(g0.z, g0.w); gb[2] = f2_pack(g1.x, g1.y); gb[3] = f2_pack(g1.z, g1.w);
-            gb[4] = f2_pack(g2.x, g2.y); gb[5] = f2_pack(g2.z, g2.w); gb[6] = f2_pack(g3.x, g3.y); gb[7] = f2_pack(g3.z, g3.w);
-            gb[8] = f2_pack(b0.x, b0.y); gb[9] = f2_pack(b0.z, b0.w); gb[10] = f2_pack(b1.x, b1.y); gb[11] = f2_pack(b1.z, b1.w);
-            gb[12] = f2_pack(b2.x, b2.y); gb[13] = f2_pack(b2.z, b2.w); gb[14] = f2_pack(b3.x, b3.y); gb[15] = f2_pack(b3.z, b3.w);
-        }
+        ln_load_affine<2>(gb, p.gamma, p.beta, lane);
         uint32_t it = g;
         for (int tile = blockIdx.x + g * gridDim.x; tile < p.total_tiles; tile += 2 * gridDim.x, it += 2) {
             const uint32_t ph = (it >> 1) & 1u;
