@@ -73,8 +73,7 @@ extern "C" {
                                          two-deep tile ring per SM) instead of CTA pairs (cta_group::2:
                                          each CTA holds one side's weights and normalises half of a
                                          tile); same arithmetic, results equal to the last bf16 bit of
-                                         a few elements; slower; the scattering entry point always
-                                         runs this form                                              */
+                                         a few elements; slower                                      */
 #define TRIMUL_FLAG_INPLACE_NORM_STAGE3 16u /* stage 3 with both LayerNorms applied in place in shared
                                          memory before the projections (rounds LN(x) to bf16 like the
                                          reference) instead of the default kernel, which folds them

@@ -1,5 +1,5 @@
 // Constants and launch parameters shared by the c = 128 stage-1 kernels (tm1_pair_sm100.cuh, the
-// default, and tm1_sm100.cuh, the lone-CTA form that also scatters).
+// default, and tm1_sm100.cuh, the lone-CTA form).
 #pragma once
 
 #include "ptx_sm100.cuh"

@@ -29,6 +29,10 @@
 //   acc_full[b]   in each CTA: commit multicast
 //   acc_empty[b]  in the leader, 16 arrivals: the set's eight epilogue warps of each CTA (remote arrive)
 //   w_all         in the leader, 2 arrivals: each CTA's weights are loaded and halved
+//
+// kScatter = true: a warp's 32 planes are stored in segments of planes_per_dest planes (16 or 32),
+// each through the tensor map of the destination buffer that holds those planes — the multi-GPU
+// exchange of the channel-sharded contraction, done by this kernel's own TMA stores.
 #pragma once
 
 #include "tm1_common.cuh"
@@ -53,11 +57,13 @@ constexpr int kP1LnBarrier = 2;        // 2, 3: the two LayerNorm groups
 constexpr int kP1EpiBarrier = 4;       // 4, 5: the eight epilogue warps of accumulator set 0, 1
 static_assert(kP1SmemBytes <= 232448, "stage 1 shared memory exceeds the 227 KB a CTA may use");
 
+template <bool kScatter>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kP1Threads, 1)
 tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWl,
                       const __grid_constant__ CUtensorMap tmWlg, const __grid_constant__ CUtensorMap tmWr,
                       const __grid_constant__ CUtensorMap tmWrg, const __grid_constant__ CUtensorMap tmA,
-                      const __grid_constant__ CUtensorMap tmB, const __grid_constant__ Tm1Params p) {
+                      const __grid_constant__ CUtensorMap tmB, const __grid_constant__ Tm1Params p,
+                      const __grid_constant__ ScatterMaps scA, const __grid_constant__ ScatterMaps scB) {
     extern __shared__ __align__(1024) uint8_t smem[];
     if ((smem_u32(smem) & 1023u) != 0u) {
         // both CTAs of a pair see the same offset, so both leave here and nobody waits for the other
@@ -318,7 +324,19 @@ tm1_pair_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             if (lane == 0) {
                 const int col0 = t0 + half * 64;
                 if (col0 < p.n_run) {
-                    tma_store_4d(om, box, col0 % cc, f % rc, b * kT1C + q * 32, col0 / cc + f / rc);
+                    if (kScatter) {
+                        // the warp's 32 planes in segments of one destination's share
+                        const ScatterMaps* sm = is_leader ? &scA : &scB;
+                        const int seg = p.planes_per_dest < 32 ? p.planes_per_dest : 32;
+                        for (int k0 = 0; k0 < 32; k0 += seg) {
+                            const int plane = b * kT1C + q * 32 + k0;
+                            const int d = plane / p.planes_per_dest;
+                            tma_store_4d(&sm->map[d], box + k0 * 128, col0 % cc, f % rc, plane - d * p.planes_per_dest,
+                                         col0 / cc + f / rc);
+                        }
+                    } else {
+                        tma_store_4d(om, box, col0 % cc, f % rc, b * kT1C + q * 32, col0 / cc + f / rc);
+                    }
                     tma_store_commit();
                 }
                 if (ew == 0 && is_leader) TRIMUL_STAMP(3, it, 2);

@@ -337,25 +337,39 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
     p.status = status;
     const int grid = p.total_tiles < sm_count() ? p.total_tiles : sm_count();
     const bool overlap = overlap_launches(d->flags);
-    if ((d->flags & TRIMUL_FLAG_SINGLE_CTA_STAGE1) == 0 && n_dest == 0 && sm_count() >= 2) {
+    if ((d->flags & TRIMUL_FLAG_SINGLE_CTA_STAGE1) == 0 && sm_count() >= 2) {
         // CTA pairs: each CTA holds one side's weights and normalises 64 positions of a tile
         CUtensorMap tmZh, tmA, tmB;
+        ScatterMaps scA{}, scB{};
         const uint64_t dims[4] = {128, (uint64_t)d->N, (uint64_t)d->rows, (uint64_t)d->B};
         const uint64_t strides[3] = {128, (uint64_t)d->N * 128, (uint64_t)d->rows * d->N * 128};
         const uint32_t box_out[4] = {64, 64, 1, 1};
         const uint32_t box_in[4] = {64, 1, 64, 1};
         if (!encode_bf16(&tmZh, z, 4, dims, strides, inc ? box_in : box_out, 128)) return TRIMUL_E_CUDA;
-        // one epilogue warp stores 64 positions x 32 planes
-        if (!encode_planes(&tmA, *a, planes, 64, 1, 32)) return TRIMUL_E_CUDA;
-        if (!encode_planes(&tmB, *b, planes, 64, 1, 32)) return TRIMUL_E_CUDA;
         const int pairs = p.total_tiles < sm_count() / 2 ? p.total_tiles : sm_count() / 2;
         for (int k = 0; k < 2; ++k) {
             p.step_q[k] = (k + 1) * pairs / p.tiles_per_fixed;
             p.step_r[k] = (k + 1) * pairs % p.tiles_per_fixed;
         }
-        if (!ensure_smem(tm1_pair_sm100_kernel, kP1SmemBytes)) return TRIMUL_E_CUDA;
-        return launch_stage(tm1_pair_sm100_kernel, 2 * pairs, kP1Threads, kP1SmemBytes, st, overlap, tmZh, tmW[0],
-                            tmW[1], tmW[2], tmW[3], tmA, tmB, p);
+        if (n_dest > 0) {
+            // one epilogue warp stores 64 positions x 32 planes, in segments of one destination's share
+            const uint32_t seg = planes_per_dest < 32 ? planes_per_dest : 32;
+            for (int k = 0; k < n_dest; ++k) {
+                if (!encode_planes(&scA.map[k], a[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
+                if (!encode_planes(&scB.map[k], b[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
+            }
+            tmA = scA.map[0];
+            tmB = scB.map[0];
+            if (!ensure_smem(tm1_pair_sm100_kernel<true>, kP1SmemBytes)) return TRIMUL_E_CUDA;
+            return launch_stage(tm1_pair_sm100_kernel<true>, 2 * pairs, kP1Threads, kP1SmemBytes, st, overlap, tmZh,
+                                tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p, scA, scB);
+        }
+        // one epilogue warp stores 64 positions x 32 planes
+        if (!encode_planes(&tmA, *a, planes, 64, 1, 32)) return TRIMUL_E_CUDA;
+        if (!encode_planes(&tmB, *b, planes, 64, 1, 32)) return TRIMUL_E_CUDA;
+        if (!ensure_smem(tm1_pair_sm100_kernel<false>, kP1SmemBytes)) return TRIMUL_E_CUDA;
+        return launch_stage(tm1_pair_sm100_kernel<false>, 2 * pairs, kP1Threads, kP1SmemBytes, st, overlap, tmZh,
+                            tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p, scA, scB);
     }
     // lone CTAs: all four weight matrices per SM, results staged in shared memory and TMA-stored
     CUtensorMap tmA, tmB;
