@@ -33,10 +33,6 @@
 // tm1_direct_sm100.cuh is the variant that halves the number of UMMAs (N = 256) and has a
 // three-deep ring at the price of a thread-per-position epilogue; it is slower.
 //
-// kScatter = true: the 128 channel planes of a tile are stored in segments of planes_per_dest
-// planes, segment k through destination map (first plane of the segment) / planes_per_dest — the
-// multi-GPU exchange of the channel-sharded contraction, done by this kernel's own TMA stores.
-//
 // A tile is 128 consecutive positions along the index that becomes the contraction's k: for the
 // outgoing direction z row f, columns t0..t0+127; for the incoming direction z column f, rows
 // t0..t0+127 (a strided TMA box), so both directions store plane element (f, t0+p).
@@ -60,13 +56,11 @@ constexpr int kT1LnBarrier = 2;
 constexpr int kT1EpiBarrier = 3;       // 3: left side, 4: right side
 constexpr int kT1LnBarrier2 = 5;       // second LayerNorm group
 
-template <bool kScatter>
 __global__ void __launch_bounds__(kT1Threads, 1)
 tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant__ CUtensorMap tmWl,
                  const __grid_constant__ CUtensorMap tmWlg, const __grid_constant__ CUtensorMap tmWr,
                  const __grid_constant__ CUtensorMap tmWrg, const __grid_constant__ CUtensorMap tmA,
-                 const __grid_constant__ CUtensorMap tmB, const Tm1Params p,
-                 const __grid_constant__ ScatterMaps scA, const __grid_constant__ ScatterMaps scB) {
+                 const __grid_constant__ CUtensorMap tmB, const Tm1Params p) {
     extern __shared__ __align__(1024) uint8_t smem[];
     if ((smem_u32(smem) & 1023u) != 0u) {
         if (threadIdx.x == 0) report_timeout(p.status, kStageIdTm1, 900);
@@ -238,7 +232,6 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
         const int bar_id = kT1EpiBarrier + side;
         uint8_t* stg = sOut + side * kT1SubTile;
         const CUtensorMap* om = side == 0 ? &tmA : &tmB;
-        const ScatterMaps* sm = side == 0 ? &scA : &scB;
         const int rc = side == 0 ? p.a_row_chunk : p.b_row_chunk;
         const int cc = side == 0 ? p.a_col_chunk : p.b_col_chunk;
         const uint32_t t_p = tmem_base + side * 256 + ((uint32_t)(q * 32) << 16);
@@ -297,17 +290,7 @@ tm1_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_constant_
                 if (leader) {
                     const int col0 = t0 + half * 64;
                     if (col0 < p.n_run) {
-                        if (kScatter) {
-                            const int seg = p.planes_per_dest < kT1C ? p.planes_per_dest : kT1C;
-                            for (int k0 = 0; k0 < kT1C; k0 += seg) {
-                                const int plane = b * kT1C + k0;
-                                const int d = plane / p.planes_per_dest;
-                                tma_store_4d(&sm->map[d], stg + k0 * 128, col0 % cc, f % rc,
-                                             plane - d * p.planes_per_dest, col0 / cc + f / rc);
-                            }
-                        } else {
-                            tma_store_4d(om, stg, col0 % cc, f % rc, b * kT1C, col0 / cc + f / rc);
-                        }
+                        tma_store_4d(om, stg, col0 % cc, f % rc, b * kT1C, col0 / cc + f / rc);
                         tma_store_commit();
                     }
                 }

@@ -372,27 +372,14 @@ int run_fast_tm1(const trimul_desc* d, const void* z, const uint8_t* mask, const
                             tmW[0], tmW[1], tmW[2], tmW[3], tmA, tmB, p, scA, scB);
     }
     // lone CTAs: all four weight matrices per SM, results staged in shared memory and TMA-stored
+    if (n_dest > 0) return TRIMUL_E_UNSUPPORTED;       // only the pair kernel scatters
     CUtensorMap tmA, tmB;
-    ScatterMaps scA{}, scB{};
-    if (n_dest > 0) {
-        // stores of a and b: 64 positions x one destination's share of the 128 planes per box
-        const uint32_t seg = planes_per_dest < 128 ? planes_per_dest : 128;
-        for (int k = 0; k < n_dest; ++k) {
-            if (!encode_planes(&scA.map[k], a[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
-            if (!encode_planes(&scB.map[k], b[k], planes_per_dest, 64, 1, seg)) return TRIMUL_E_CUDA;
-        }
-        tmA = scA.map[0];
-        tmB = scB.map[0];
-        if (!ensure_smem(tm1_sm100_kernel<true>, kT1SmemBytes)) return TRIMUL_E_CUDA;
-        return launch_stage(tm1_sm100_kernel<true>, grid, kT1Threads, kT1SmemBytes, st, overlap, tmZ, tmW[0], tmW[1],
-                            tmW[2], tmW[3], tmA, tmB, p, scA, scB);
-    }
     // stores of a and b: 64 positions x 128 planes per box
     if (!encode_planes(&tmA, *a, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
     if (!encode_planes(&tmB, *b, planes, 64, 1, 128)) return TRIMUL_E_CUDA;
-    if (!ensure_smem(tm1_sm100_kernel<false>, kT1SmemBytes)) return TRIMUL_E_CUDA;
-    return launch_stage(tm1_sm100_kernel<false>, grid, kT1Threads, kT1SmemBytes, st, overlap, tmZ, tmW[0], tmW[1],
-                        tmW[2], tmW[3], tmA, tmB, p, scA, scB);
+    if (!ensure_smem(tm1_sm100_kernel, kT1SmemBytes)) return TRIMUL_E_CUDA;
+    return launch_stage(tm1_sm100_kernel, grid, kT1Threads, kT1SmemBytes, st, overlap, tmZ, tmW[0], tmW[1], tmW[2],
+                        tmW[3], tmA, tmB, p);
 }
 
 // c = h = 64: left and right weights stacked into one UMMA operand (tm1_narrow_sm100.cuh)
