@@ -637,3 +637,45 @@ def test_serial_launch_gives_the_same_result(dev):
             y_serial = trimul_forward(z, m, outgoing=(i % 2 == 0), **kw, residual=z, serial_launch=True)
             assert torch.equal(y, y_serial), (c, N, i)
     assert read_status(dev)[0] == 0
+
+
+def test_randomised_shapes_kernel_variants_agree_bit_for_bit(dev):
+    """Random batch sizes, token counts (multiples of nothing in particular), mask kinds and directions:
+    the CTA-pair and lone-CTA forms of stage 1 and of the contraction give identical bits, repeated calls
+    reproduce themselves, nothing but the planes is written (NaN-filled scratch), every value is finite
+    and no bounded wait expires."""
+    import random
+    from miniworld_engine_b200 import read_status, stages as S
+    from tests._util import weights_dict
+    rng = random.Random(7)
+    gen = torch.Generator().manual_seed(7)
+    w = O.make_weights(128, 0, affine="random")
+    wd = weights_dict(w, torch.bfloat16, dev)
+    for _ in range(16):
+        B, N = rng.choice([1, 1, 2, 3]), rng.choice([16, 33, 64, 100, 128, 191, 256, 300, 384])
+        z = torch.randn(B, N, N, 128, generator=gen).bfloat16().to(dev)
+        kind = rng.choice(["none", "token", "pair"])
+        m = None if kind == "none" else (torch.rand((B, N) if kind == "token" else (B, N, N), generator=gen) > 0.2).to(dev)
+        outgoing = rng.choice([True, False])
+        res = []
+        for single_cta in (False, True, False):
+            a = S.alloc_planes(B * 128, N, N, torch.bfloat16, dev, fill=float("nan"))
+            b = S.alloc_planes(B * 128, N, N, torch.bfloat16, dev, fill=float("nan"))
+            S.tm1(z, m, wd, a, b, outgoing=outgoing, single_cta=single_cta)
+            res.append((S.planes_to_dense(a).clone(), S.planes_to_dense(b).clone(), a, b))
+        for k in (1, 2):
+            assert torch.equal(res[0][0], res[k][0]) and torch.equal(res[0][1], res[k][1]), (B, N, kind, outgoing, k)
+        assert bool(torch.isfinite(res[0][0].float()).all()) and bool(torch.isfinite(res[0][1].float()).all())
+        t1 = S.alloc_planes(B * 128, N, N, torch.bfloat16, dev, fill=float("nan"))
+        t2 = S.alloc_planes(B * 128, N, N, torch.bfloat16, dev, fill=float("nan"))
+        S.contract(res[0][2], res[0][3], t1)
+        S.contract(res[0][2], res[0][3], t2, single_cta=True)
+        assert torch.equal(S.planes_to_dense(t1), S.planes_to_dense(t2)), (B, N, kind, outgoing)
+        y = S.tm2(z, t1, wd)
+        assert torch.equal(y, S.tm2(z, t1, wd))
+        if N <= 128:      # the oracle is quick at these sizes: the stage calls above ARE the block
+            w16 = w.to(torch.bfloat16)
+            ref = O.trimul_stages(z.cpu(), None if kind != "token" else m.cpu(), w16, outgoing,
+                                  pair_mask=m.cpu() if kind == "pair" else None)["out"]
+            assert O.rel_rms(y.float().cpu(), ref.float()) <= TOL_BF16, (B, N, kind, outgoing)
+    assert read_status(dev)[0] == 0
