@@ -175,6 +175,7 @@ tm1_wide_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                 const uint32_t ph = (it >> 1) & 1u;
                 if (!mbar_wait<true>(&xn_ready[s], ph, abort_flag, p.status, kStageIdTm1, 210 + s)) break;
                 tcgen05_fence_after();
+                TRIMUL_STAMP(1, it, 0);
                 const uint32_t xs = smem_u32(sX + s * kW1XBytes);
                 for (int u = 0; ok && u < 4; ++u) {
                     // accumulator pair u & 1; its use counter is 2 * it + (u >> 1)
@@ -185,6 +186,7 @@ tm1_wide_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                         break;
                     }
                     tcgen05_fence_after();
+                    TRIMUL_STAMP(3, it, u);
                     const uint32_t d_p = tmem_base + acc * 256;
                     const uint32_t d_g = d_p + 128;
                     for (int ks = 0; ks < kW1Sub; ++ks, cnt += 2) {
@@ -212,6 +214,7 @@ tm1_wide_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
                     }
                     if (!ok) break;
                     umma_commit(&acc_full[acc]);
+                    if (u != 2) TRIMUL_STAMP(1, it, u == 3 ? 3 : u + 1);
                 }
                 if (!ok) break;
                 umma_commit(&x_empty[s]);   // every UMMA that reads the tile has retired when this fires
@@ -245,9 +248,11 @@ tm1_wide_sm100_kernel(const __grid_constant__ CUtensorMap tmZ, const __grid_cons
             if (!group_wait<true>(&x_full[g], ph, pos == 0, kW1LnBarrier + g, 128, abort_flag, p.status, kStageIdTm1,
                                   300 + g))
                 break;
+            if (pos == 0) TRIMUL_STAMP(2, it, 0);
             ln_row_inplace<kW1Sub>(sX + g * kW1XBytes, kT1SubTile, pos, sGamma, sBeta, p.eps, !keep);
             fence_proxy_async_smem();   // normalised tile -> visible to the UMMA (async proxy)
             mbar_arrive(&xn_ready[g]);
+            if (pos == 0) TRIMUL_STAMP(2, it, 1);
         }
     } else {
         // ------------------------------------------------------------------ epilogue, one channel half per group
